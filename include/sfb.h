@@ -1,0 +1,207 @@
+/*
+ * sfb.h — C ABI of the B200 (sm_100a) attention hot-path library, libsfb.so.
+ *
+ * One thin C surface for the operators LLM-CompileForge routes through its HAL
+ * `OpExecutor.execute(op_name, inputs, **kwargs)` seam
+ * (python_runtime/hal/interface.py:51-61) and that its Rust runtime reaches
+ * through `Executable::execute(op_name, stream, &[SfaMemRef], &mut [SfaMemRef])`
+ * (runtime/src/hal/traits.rs:115-137).  Tensors travel as the reference's own
+ * descriptors (include/sfa.h:41-99): MLIR memref layout, element strides.
+ *
+ * Conventions
+ *   - Every pointer inside a descriptor is a DEVICE pointer (`device` must be
+ *     SFB_DEVICE_CUDA); `aligned + offset*elem_size` is element 0.
+ *   - Strides are in elements.  The innermost dimension must be contiguous;
+ *     all other strides are honoured, so a layer view of the engine's
+ *     `[NB, layers, bs, heads, dim]` slab
+ *     (python_runtime/engine/cache_manager.py:106-113) is consumed in place.
+ *   - Element types are passed out of band as SFBDType (elem_size alone cannot
+ *     tell fp16 from bf16, or e4m3 codes from bytes).
+ *   - The caller owns every buffer, including the workspace.  The library
+ *     allocates no device memory (the `_mlir_ciface_*` shims excepted, which
+ *     follow the reference's callee-allocates convention).
+ *   - Calls enqueue work on `stream` (a cudaStream_t, NULL = default stream)
+ *     and return without synchronising.  Return value: SFB_OK or a negative
+ *     SFBStatus; `sfb_last_error()` gives the text for the calling thread.
+ *   - Functions are re-entrant for distinct workspaces.
+ */
+#ifndef SFB_H
+#define SFB_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SFB_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define SFB_API __attribute__((visibility("default")))
+#else
+#define SFB_API
+#endif
+
+/* ── Tensor descriptors: binary-identical to include/sfa.h:41-99 ─────────── */
+#ifdef SFA_H
+typedef SFATensorRaw1 SFBMemRef1;
+typedef SFATensorRaw2 SFBMemRef2;
+typedef SFATensorRaw3 SFBMemRef3;
+typedef SFATensorRaw4 SFBMemRef4;
+typedef SFATensor SFBTensor;
+#define SFB_DEVICE_CPU SFA_CPU
+#define SFB_DEVICE_CUDA SFA_CUDA
+#else
+#define SFB_MEMREF(R)                                                                  \
+    struct {                                                                           \
+        void* allocated;                                                               \
+        void* aligned;                                                                 \
+        int64_t offset;                                                                \
+        int64_t sizes[R];                                                              \
+        int64_t strides[R];                                                            \
+    }
+typedef SFB_MEMREF(1) SFBMemRef1; /* 40 bytes */
+typedef SFB_MEMREF(2) SFBMemRef2; /* 56 bytes */
+typedef SFB_MEMREF(3) SFBMemRef3; /* 72 bytes */
+typedef SFB_MEMREF(4) SFBMemRef4; /* 88 bytes */
+enum { SFB_DEVICE_CPU = 1, SFB_DEVICE_CUDA = 2 };
+typedef struct {
+    int32_t device;    /* SFB_DEVICE_CUDA */
+    int32_t rank;      /* 1..4 */
+    int32_t elem_size; /* bytes per element */
+    union {
+        SFBMemRef1 r1;
+        SFBMemRef2 r2;
+        SFBMemRef3 r3;
+        SFBMemRef4 r4;
+    };
+} SFBTensor; /* 104 bytes, union at offset 16 */
+#endif
+
+typedef enum {
+    SFB_OK = 0,
+    SFB_ERR_INVALID_ARG = -1,  /* bad descriptor, shape, stride or dtype combination */
+    SFB_ERR_UNSUPPORTED = -2,  /* valid request this build has no kernel for */
+    SFB_ERR_WORKSPACE = -3,    /* workspace missing or too small */
+    SFB_ERR_CUDA = -4,         /* a CUDA runtime/driver call failed */
+    SFB_ERR_DEVICE_STATUS = -5 /* a kernel flagged bad data (sfb_read_status) */
+} SFBStatus;
+
+typedef enum {
+    SFB_F32 = 0,
+    SFB_BF16 = 1,
+    SFB_F16 = 2,
+    SFB_F8E4M3 = 3 /* torch.float8_e4m3fn codes, one byte each */
+} SFBDType;
+
+/* Bits a kernel may set in the workspace status word. */
+enum {
+    SFB_STATUS_BAD_BLOCK_ID = 1, /* block-table entry outside [0, NB): block skipped */
+    SFB_STATUS_EMPTY_REQUEST = 2, /* seq_len <= 0: output row zero-filled */
+    SFB_STATUS_WAIT_TIMEOUT = 4  /* a bounded device-side wait gave up */
+};
+
+SFB_API int sfb_abi_version(void);
+SFB_API const char* sfb_last_error(void);
+SFB_API const char* sfb_status_string(int status);
+
+/* ── Paged-attention decode ─────────────────────────────────────────────────
+ * Replaces kernels/paged_attention.py:200-227 `paged_attention` (CPU path
+ * :21-73) and is the kernel behind the HAL op name `paged_attention` that
+ * sf-dialect/include/Sf/HALOps.td:184-189 reserves.
+ *
+ *   q            [B, H, D]            q_dtype (F32 | BF16 | F16)
+ *   k_cache      [NB, bs, Hkv, D]     kv_dtype; F32/BF16/F16 must equal q_dtype,
+ *   v_cache      [NB, bs, Hkv, D]       F8E4M3 pairs with a BF16/F16 q
+ *   k_scale      [NB, Hkv] float32    F8E4M3 only (else NULL): dequantised value
+ *   v_scale      [NB, Hkv] float32      = code * scale (fp8_kv_cache.py:95-105)
+ *   block_tables [B, max_blocks] int32  row r lists request r's physical blocks
+ *   seq_lens     [B] int32            attended tokens; clamped to max_blocks*bs
+ *                                       like paged_attention.py:37-48
+ *   out          [B, H, D]            q_dtype
+ *
+ * Query head h reads kv head h / (H / Hkv) (paged_attention.py:57-60); no mask;
+ * one query token per request.  Entries of a table row past ceil(L/bs) are
+ * never dereferenced.  `scale` <= 0 selects 1/sqrt(D) (:31-32).
+ *
+ * The KV length of a request is cut into chunks of `chunk_tokens` tokens
+ * (multiple of bs; 0 = library default) processed by different thread blocks;
+ * when max_blocks*bs > chunk_tokens the partial results go through `workspace`
+ * (size from sfb_paged_attention_workspace_bytes) and a combine kernel.  The
+ * first 4 bytes of a non-NULL workspace are the status word (zeroed by each
+ * call before its kernels run). */
+SFB_API int64_t sfb_paged_attention_workspace_bytes(int64_t batch, int64_t n_heads, int64_t head_dim,
+                                            int64_t max_blocks, int64_t block_size, int64_t chunk_tokens);
+
+SFB_API int sfb_paged_attention_decode(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
+                               const SFBTensor* k_scale, const SFBTensor* v_scale,
+                               const SFBTensor* block_tables, const SFBTensor* seq_lens, SFBTensor* out,
+                               int q_dtype, int kv_dtype, float scale, int64_t chunk_tokens,
+                               void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Copies the workspace status word to the host (synchronises `stream`).
+ * Returns SFB_OK when it is zero, SFB_ERR_DEVICE_STATUS otherwise; *bits (may
+ * be NULL) receives the SFB_STATUS_* mask. */
+SFB_API int sfb_read_status(const void* workspace, int32_t* bits, void* stream);
+
+/* ── KV cache write / FP8 quantise-on-append ───────────────────────────────
+ * Replaces CacheManager.write_paged (python_runtime/engine/cache_manager.py:139-171;
+ * Rust twin BlockManager::write_kv, runtime/src/cache/block.rs:348-403) for the
+ * HAL op name `cache_write` (HALOps.td:195-199), fused with
+ * FP8KVCacheQuantizer.quantize_block (compiler/quantize/fp8_kv_cache.py:66-93)
+ * when the pool holds e4m3 codes.
+ *
+ *   k_new, v_new [T, Hkv, D]  src_dtype; tokens packed request after request
+ *   cu_tokens    [B+1] int32  request r owns rows cu_tokens[r] .. cu_tokens[r+1]-1
+ *   start_pos    [B] int32    position of request r's first new token
+ *   block_tables [B, max_blocks] int32
+ *   k_cache, v_cache [NB, bs, Hkv, D]  kv_dtype (== src_dtype, or F8E4M3)
+ *   k_scale, v_scale [NB, Hkv] float32 (F8E4M3 only)
+ *   k_tail, v_tail   [B, bs, Hkv, D] src_dtype (F8E4M3 only): unquantised copy of
+ *                    each request's open (partially filled) block, owned by the
+ *                    caller, read and updated by this call
+ *
+ * Token at position p goes to slot (table[p / bs], p % bs) (cache_manager.py:154-159).
+ * FP8: after the call every touched (block, kv_head) slice holds exactly
+ * quantize_block(slice contents, unwritten slots = 0): scale = amax/448
+ * (1.0 when amax == 0, at least 1e-12), codes = e4m3(x / scale), bit-exact.
+ * `max_new_tokens` >= max_r (cu_tokens[r+1]-cu_tokens[r]) sizes the launch. */
+SFB_API int sfb_cache_write(const SFBTensor* k_new, const SFBTensor* v_new, const SFBTensor* cu_tokens,
+                    const SFBTensor* start_pos, const SFBTensor* block_tables, SFBTensor* k_cache,
+                    SFBTensor* v_cache, SFBTensor* k_scale, SFBTensor* v_scale, SFBTensor* k_tail,
+                    SFBTensor* v_tail, int src_dtype, int kv_dtype, int64_t max_new_tokens, void* stream);
+
+/* ── FP8 quantise / dequantise ──────────────────────────────────────────────
+ * Replaces FP8KVCacheQuantizer.quantize_block / dequantize_block
+ * (compiler/quantize/fp8_kv_cache.py:66-105); HAL op names `quantize` /
+ * `dequantize` (HALOps.td:202-211).
+ *
+ *   x      [N0, N1, N2, N3]  x_dtype (F32 | BF16 | F16)
+ *   codes  [N0, N1, N2, N3]  uint8 e4m3
+ *   scales float32: SFB_QUANT_PER_TENSOR -> [1] (the reference's single scale for
+ *          the tensor passed in); SFB_QUANT_PER_BLOCK_HEAD -> [N0, N2], one per
+ *          x[b, :, h, :] slice (the KV pool layout [NB, bs, Hkv, D]). */
+enum { SFB_QUANT_PER_TENSOR = 0, SFB_QUANT_PER_BLOCK_HEAD = 1 };
+
+SFB_API int sfb_quantize_fp8(const SFBTensor* x, SFBTensor* codes, SFBTensor* scales, int x_dtype, int granularity,
+                     void* stream);
+SFB_API int sfb_dequantize_fp8(const SFBTensor* codes, const SFBTensor* scales, SFBTensor* out, int out_dtype,
+                       int granularity, void* stream);
+
+/* ── RMSNorm (optionally fused with a residual add) ─────────────────────────
+ * Replaces the HAL op `rms_norm` (python_runtime/hal/pytorch_backend/_ops_norm.py:30-45)
+ * and kernels/rms_norm.py:85-106 `fused_rms_norm_add`.
+ *
+ *   x, out   [rows, hidden] dtype;  residual [rows, hidden] dtype or NULL
+ *   weight   [hidden] dtype or NULL
+ *   out = s * rsqrt(mean(s^2) + eps) * weight,  s = x (+ residual)
+ * Arithmetic is float32 with one final rounding to `dtype` (the HAL op's rule,
+ * _ops_norm.py:35-45). */
+SFB_API int sfb_rms_norm(const SFBTensor* x, const SFBTensor* residual, const SFBTensor* weight, SFBTensor* out,
+                 int dtype, float eps, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SFB_H */

@@ -1,0 +1,315 @@
+// C-ABI entry points of libsfb.so: descriptor validation, error text, dispatch.
+// The kernels live in the sibling .cu files; nothing here touches device data.
+
+#include <cstring>
+
+#include "sfb_common.cuh"
+
+namespace sfb {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+int fail(int status, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+int make_view(const SFBTensor* t, const char* what, int min_rank, int max_rank, int elem_size, View* v) {
+    if (!t) return fail(SFB_ERR_INVALID_ARG, "%s: descriptor is NULL", what);
+    if (t->device != SFB_DEVICE_CUDA)
+        return fail(SFB_ERR_INVALID_ARG, "%s: device %d is not SFB_DEVICE_CUDA (no CPU path exists)", what, t->device);
+    if (t->rank < min_rank || t->rank > max_rank)
+        return fail(SFB_ERR_INVALID_ARG, "%s: rank %d outside [%d, %d]", what, t->rank, min_rank, max_rank);
+    if (elem_size > 0 && t->elem_size != elem_size)
+        return fail(SFB_ERR_INVALID_ARG, "%s: elem_size %d, expected %d", what, t->elem_size, elem_size);
+    // Every per-rank layout starts {allocated, aligned, offset, sizes[R], strides[R]}.
+    const int64_t* tail = t->r4.sizes;  // same address for every rank
+    const int r = t->rank;
+    const int64_t* sizes = tail;
+    const int64_t* strides = tail + r;
+    v->rank = r;
+    v->elem = t->elem_size;
+    for (int i = 0; i < 4; ++i) { v->size[i] = 1; v->stride[i] = 0; }
+    for (int i = 0; i < r; ++i) {
+        if (sizes[i] < 0) return fail(SFB_ERR_INVALID_ARG, "%s: negative size", what);
+        v->size[4 - r + i] = sizes[i];
+        v->stride[4 - r + i] = strides[i];
+    }
+    if (v->numel() > 0 && !t->r1.aligned) return fail(SFB_ERR_INVALID_ARG, "%s: data pointer is NULL", what);
+    if (v->size[3] > 1 && v->stride[3] != 1)
+        return fail(SFB_ERR_INVALID_ARG, "%s: innermost dimension must be contiguous (stride %lld)", what,
+                    (long long)v->stride[3]);
+    v->base = static_cast<char*>(t->r1.aligned) + t->r1.offset * (int64_t)t->elem_size;
+    return SFB_OK;
+}
+
+static bool aligned16(const View& v, int first_dim) {
+    if (reinterpret_cast<uintptr_t>(v.base) % 16) return false;
+    for (int i = first_dim; i < 3; ++i)
+        if (v.size[i] > 1 && (v.stride[i] * v.elem) % 16) return false;
+    return true;
+}
+
+}  // namespace sfb
+
+using namespace sfb;
+
+extern "C" {
+
+int sfb_abi_version(void) { return SFB_ABI_VERSION; }
+
+const char* sfb_last_error(void) { return g_error; }
+
+const char* sfb_status_string(int status) {
+    switch (status) {
+        case SFB_OK: return "ok";
+        case SFB_ERR_INVALID_ARG: return "invalid argument";
+        case SFB_ERR_UNSUPPORTED: return "unsupported configuration";
+        case SFB_ERR_WORKSPACE: return "workspace missing or too small";
+        case SFB_ERR_CUDA: return "CUDA call failed";
+        case SFB_ERR_DEVICE_STATUS: return "kernel flagged bad data";
+        default: return "unknown status";
+    }
+}
+
+int64_t sfb_paged_attention_workspace_bytes(int64_t batch, int64_t n_heads, int64_t head_dim, int64_t max_blocks,
+                                            int64_t block_size, int64_t chunk_tokens) {
+    if (batch < 0 || n_heads <= 0 || head_dim <= 0 || max_blocks < 0 || block_size <= 0) return SFB_ERR_INVALID_ARG;
+    return decode_split(batch, n_heads, head_dim, max_blocks, block_size, chunk_tokens).total_bytes;
+}
+
+int sfb_paged_attention_decode(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
+                               const SFBTensor* k_scale, const SFBTensor* v_scale, const SFBTensor* block_tables,
+                               const SFBTensor* seq_lens, SFBTensor* out, int q_dtype, int kv_dtype, float scale,
+                               int64_t chunk_tokens, void* workspace, int64_t workspace_bytes, void* stream) {
+    const int qe = dtype_size(q_dtype), kve = dtype_size(kv_dtype);
+    if (!qe || q_dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "decode: q dtype %d", q_dtype);
+    if (!kve) return fail(SFB_ERR_INVALID_ARG, "decode: kv dtype %d", kv_dtype);
+    if (kv_dtype != SFB_F8E4M3 && kv_dtype != q_dtype)
+        return fail(SFB_ERR_INVALID_ARG, "decode: kv dtype %d must equal q dtype %d (or be e4m3)", kv_dtype, q_dtype);
+    if (kv_dtype == SFB_F8E4M3 && q_dtype == SFB_F32)
+        return fail(SFB_ERR_UNSUPPORTED, "decode: e4m3 pools need a bf16 or fp16 query");
+    View vq, vk, vv, vks, vvs, vt, vl, vo;
+    int rc;
+    if ((rc = make_view(q, "q", 3, 3, qe, &vq))) return rc;
+    if ((rc = make_view(out, "out", 3, 3, qe, &vo))) return rc;
+    if ((rc = make_view(k_cache, "k_cache", 4, 4, kve, &vk))) return rc;
+    if ((rc = make_view(v_cache, "v_cache", 4, 4, kve, &vv))) return rc;
+    if ((rc = make_view(block_tables, "block_tables", 2, 2, 4, &vt))) return rc;
+    if ((rc = make_view(seq_lens, "seq_lens", 1, 1, 4, &vl))) return rc;
+    const int64_t B = vq.size[1], H = vq.size[2], D = vq.size[3];
+    const int64_t NB = vk.size[0], bs = vk.size[1], Hkv = vk.size[2];
+    if (vk.size[3] != D || vv.size[3] != D) return fail(SFB_ERR_INVALID_ARG, "decode: head_dim of q (%lld) and pools differ", (long long)D);
+    for (int i = 0; i < 4; ++i)
+        if (vk.size[i] != vv.size[i]) return fail(SFB_ERR_INVALID_ARG, "decode: k_cache and v_cache shapes differ");
+    if (vo.size[1] != B || vo.size[2] != H || vo.size[3] != D) return fail(SFB_ERR_INVALID_ARG, "decode: out shape differs from q");
+    if (Hkv <= 0 || H % Hkv) return fail(SFB_ERR_INVALID_ARG, "decode: %lld query heads not a multiple of %lld kv heads", (long long)H, (long long)Hkv);
+    if (vt.size[2] != B || vl.size[3] != B) return fail(SFB_ERR_INVALID_ARG, "decode: block_tables/seq_lens rows != batch %lld", (long long)B);
+    if (vl.size[3] > 1 && vl.stride[3] != 1) return fail(SFB_ERR_INVALID_ARG, "decode: seq_lens must be contiguous");
+    if (bs <= 0 || (D * kve) % 16) return fail(SFB_ERR_UNSUPPORTED, "decode: head_dim*elem (%lld B) must be a multiple of 16", (long long)(D * kve));
+    if (!aligned16(vk, 0) || !aligned16(vv, 0)) return fail(SFB_ERR_UNSUPPORTED, "decode: pool base and strides must be 16-byte aligned");
+    const int64_t max_blocks = vt.size[3];
+    if (B == 0) return SFB_OK;
+
+    DecodeArgs a{};
+    a.q = vq.base; a.k = vk.base; a.v = vv.base; a.out = vo.base;
+    a.tables = reinterpret_cast<const int32_t*>(vt.base);
+    a.seq_lens = reinterpret_cast<const int32_t*>(vl.base);
+    a.q_dtype = q_dtype; a.kv_dtype = kv_dtype;
+    a.batch = (int)B; a.n_heads = (int)H; a.n_kv_heads = (int)Hkv; a.head_dim = (int)D;
+    a.block_size = (int)bs; a.max_blocks = (int)max_blocks; a.n_pool_blocks = NB;
+    a.q_stride[0] = vq.stride[1]; a.q_stride[1] = vq.stride[2];
+    a.out_stride[0] = vo.stride[1]; a.out_stride[1] = vo.stride[2];
+    for (int i = 0; i < 3; ++i) { a.k_stride[i] = vk.stride[i]; a.v_stride[i] = vv.stride[i]; }
+    a.table_stride = vt.stride[2];
+    a.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
+    if (kv_dtype == SFB_F8E4M3) {
+        if ((rc = make_view(k_scale, "k_scale", 2, 2, 4, &vks))) return rc;
+        if ((rc = make_view(v_scale, "v_scale", 2, 2, 4, &vvs))) return rc;
+        if (vks.size[2] != NB || vks.size[3] != Hkv || vvs.size[2] != NB || vvs.size[3] != Hkv)
+            return fail(SFB_ERR_INVALID_ARG, "decode: scales must be [NB, Hkv]");
+        a.k_scale = reinterpret_cast<const float*>(vks.base);
+        a.v_scale = reinterpret_cast<const float*>(vvs.base);
+        a.ks_stride[0] = vks.stride[2]; a.ks_stride[1] = vks.stride[3];
+        a.vs_stride[0] = vvs.stride[2]; a.vs_stride[1] = vvs.stride[3];
+    } else if (k_scale || v_scale) {
+        return fail(SFB_ERR_INVALID_ARG, "decode: scales given for a non-e4m3 pool");
+    }
+    a.split = decode_split(B, H, D, max_blocks, bs, chunk_tokens);
+    if (a.split.n_chunks > 1) {
+        if (!workspace || workspace_bytes < a.split.total_bytes)
+            return fail(SFB_ERR_WORKSPACE, "decode: workspace of %lld B needed, %lld given", (long long)a.split.total_bytes,
+                        (long long)(workspace ? workspace_bytes : 0));
+    } else if (workspace && workspace_bytes < kWorkspaceHeader) {
+        workspace = nullptr;
+    }
+    a.workspace = static_cast<char*>(workspace);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (a.workspace) SFB_CUDA_CHECK(cudaMemsetAsync(a.workspace, 0, 4, st));
+    if (max_blocks == 0) {
+        // every request is empty: zero rows, flag it
+        return fail(SFB_ERR_INVALID_ARG, "decode: block_tables has zero columns");
+    }
+    rc = launch_decode_tma(a, st);  // returns SFB_ERR_UNSUPPORTED (without error text change) when not applicable
+    if (rc == SFB_ERR_UNSUPPORTED) rc = launch_decode_generic(a, st);
+    if (rc) return rc;
+    return launch_decode_combine(a, st);
+}
+
+int sfb_read_status(const void* workspace, int32_t* bits, void* stream) {
+    if (!workspace) return fail(SFB_ERR_INVALID_ARG, "read_status: workspace is NULL");
+    int32_t host = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    SFB_CUDA_CHECK(cudaMemcpyAsync(&host, workspace, 4, cudaMemcpyDeviceToHost, st));
+    SFB_CUDA_CHECK(cudaStreamSynchronize(st));
+    if (bits) *bits = host;
+    if (host) return fail(SFB_ERR_DEVICE_STATUS, "device status bits 0x%x", host);
+    return SFB_OK;
+}
+
+int sfb_cache_write(const SFBTensor* k_new, const SFBTensor* v_new, const SFBTensor* cu_tokens,
+                    const SFBTensor* start_pos, const SFBTensor* block_tables, SFBTensor* k_cache, SFBTensor* v_cache,
+                    SFBTensor* k_scale, SFBTensor* v_scale, SFBTensor* k_tail, SFBTensor* v_tail, int src_dtype,
+                    int kv_dtype, int64_t max_new_tokens, void* stream) {
+    const int se = dtype_size(src_dtype), kve = dtype_size(kv_dtype);
+    if (!se || src_dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "cache_write: source dtype %d", src_dtype);
+    if (!kve) return fail(SFB_ERR_INVALID_ARG, "cache_write: pool dtype %d", kv_dtype);
+    const bool fp8 = kv_dtype == SFB_F8E4M3;
+    if (!fp8 && kv_dtype != src_dtype) return fail(SFB_ERR_INVALID_ARG, "cache_write: pool dtype must equal the source dtype or be e4m3");
+    View kn, vn, cu, sp, bt, kc, vc, ks, vs, kt, vt;
+    int rc;
+    if ((rc = make_view(k_new, "k_new", 3, 3, se, &kn))) return rc;
+    if ((rc = make_view(v_new, "v_new", 3, 3, se, &vn))) return rc;
+    if ((rc = make_view(cu_tokens, "cu_tokens", 1, 1, 4, &cu))) return rc;
+    if ((rc = make_view(start_pos, "start_pos", 1, 1, 4, &sp))) return rc;
+    if ((rc = make_view(block_tables, "block_tables", 2, 2, 4, &bt))) return rc;
+    if ((rc = make_view(k_cache, "k_cache", 4, 4, kve, &kc))) return rc;
+    if ((rc = make_view(v_cache, "v_cache", 4, 4, kve, &vc))) return rc;
+    const int64_t B = sp.size[3], Hkv = kc.size[2], D = kc.size[3], bs = kc.size[1];
+    if (cu.size[3] != B + 1) return fail(SFB_ERR_INVALID_ARG, "cache_write: cu_tokens must have batch+1 = %lld entries", (long long)(B + 1));
+    if (bt.size[2] != B) return fail(SFB_ERR_INVALID_ARG, "cache_write: block_tables rows != batch");
+    for (int i = 0; i < 4; ++i)
+        if (kc.size[i] != vc.size[i]) return fail(SFB_ERR_INVALID_ARG, "cache_write: k_cache and v_cache shapes differ");
+    if (kn.size[2] != Hkv || kn.size[3] != D || vn.size[2] != Hkv || vn.size[3] != D || vn.size[1] != kn.size[1])
+        return fail(SFB_ERR_INVALID_ARG, "cache_write: k_new/v_new must be [T, %lld, %lld]", (long long)Hkv, (long long)D);
+    if ((D * se) % 16 || (D * kve) % 16) return fail(SFB_ERR_UNSUPPORTED, "cache_write: head_dim rows must be multiples of 16 bytes");
+    if (!aligned16(kn, 1) || !aligned16(vn, 1) || !aligned16(kc, 0) || !aligned16(vc, 0))
+        return fail(SFB_ERR_UNSUPPORTED, "cache_write: tensors must be 16-byte aligned");
+    if (B == 0 || max_new_tokens <= 0) return SFB_OK;
+
+    AppendArgs a{};
+    a.k_new = kn.base; a.v_new = vn.base;
+    a.cu_tokens = reinterpret_cast<const int32_t*>(cu.base);
+    a.start_pos = reinterpret_cast<const int32_t*>(sp.base);
+    a.tables = reinterpret_cast<const int32_t*>(bt.base);
+    a.table_stride = bt.stride[2];
+    a.max_blocks = (int)bt.size[3];
+    a.k_cache = kc.base; a.v_cache = vc.base;
+    a.src_dtype = src_dtype; a.kv_dtype = kv_dtype;
+    a.batch = (int)B; a.n_kv_heads = (int)Hkv; a.head_dim = (int)D; a.block_size = (int)bs;
+    a.n_pool_blocks = kc.size[0];
+    a.max_new_tokens = (int)max_new_tokens;
+    a.new_stride[0] = kn.stride[1]; a.new_stride[1] = kn.stride[2];
+    a.vnew_stride[0] = vn.stride[1]; a.vnew_stride[1] = vn.stride[2];
+    for (int i = 0; i < 3; ++i) { a.k_stride[i] = kc.stride[i]; a.v_stride[i] = vc.stride[i]; }
+    if (fp8) {
+        if ((rc = make_view(k_scale, "k_scale", 2, 2, 4, &ks))) return rc;
+        if ((rc = make_view(v_scale, "v_scale", 2, 2, 4, &vs))) return rc;
+        if ((rc = make_view(k_tail, "k_tail", 4, 4, se, &kt))) return rc;
+        if ((rc = make_view(v_tail, "v_tail", 4, 4, se, &vt))) return rc;
+        if (ks.size[2] != kc.size[0] || ks.size[3] != Hkv || vs.size[2] != kc.size[0] || vs.size[3] != Hkv)
+            return fail(SFB_ERR_INVALID_ARG, "cache_write: scales must be [NB, Hkv]");
+        if (kt.size[0] < B || kt.size[1] != bs || kt.size[2] != Hkv || kt.size[3] != D)
+            return fail(SFB_ERR_INVALID_ARG, "cache_write: k_tail must be [>=batch, bs, Hkv, D]");
+        for (int i = 0; i < 4; ++i)
+            if (kt.size[i] != vt.size[i]) return fail(SFB_ERR_INVALID_ARG, "cache_write: k_tail and v_tail shapes differ");
+        if (!aligned16(kt, 0) || !aligned16(vt, 0)) return fail(SFB_ERR_UNSUPPORTED, "cache_write: tails must be 16-byte aligned");
+        a.k_scale = reinterpret_cast<float*>(ks.base); a.v_scale = reinterpret_cast<float*>(vs.base);
+        a.ks_stride[0] = ks.stride[2]; a.ks_stride[1] = ks.stride[3];
+        a.vs_stride[0] = vs.stride[2]; a.vs_stride[1] = vs.stride[3];
+        a.k_tail = kt.base; a.v_tail = vt.base;
+        for (int i = 0; i < 3; ++i) { a.kt_stride[i] = kt.stride[i]; a.vt_stride[i] = vt.stride[i]; }
+    }
+    return launch_cache_write(a, static_cast<cudaStream_t>(stream));
+}
+
+static int quant_views(const SFBTensor* x, const SFBTensor* codes, const SFBTensor* scales, int x_dtype, int granularity,
+                       const char* op, View* vx, View* vc, View* vs) {
+    const int xe = dtype_size(x_dtype);
+    if (!xe || x_dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "%s: float dtype %d", op, x_dtype);
+    int rc;
+    if ((rc = make_view(x, "x", 1, 4, xe, vx))) return rc;
+    if ((rc = make_view(codes, "codes", 1, 4, 1, vc))) return rc;
+    for (int i = 0; i < 4; ++i)
+        if (vx->size[i] != vc->size[i]) return fail(SFB_ERR_INVALID_ARG, "%s: float tensor and codes shapes differ", op);
+    if (granularity == SFB_QUANT_PER_TENSOR) {
+        if ((rc = make_view(scales, "scales", 1, 1, 4, vs))) return rc;
+        if (vs->size[3] != 1) return fail(SFB_ERR_INVALID_ARG, "%s: per-tensor scale must have one element", op);
+    } else if (granularity == SFB_QUANT_PER_BLOCK_HEAD) {
+        if (vx->rank != 4) return fail(SFB_ERR_INVALID_ARG, "%s: per-(block, head) needs a rank-4 [NB, bs, Hkv, D] tensor", op);
+        if ((rc = make_view(scales, "scales", 2, 2, 4, vs))) return rc;
+        if (vs->size[2] != vx->size[0] || vs->size[3] != vx->size[2])
+            return fail(SFB_ERR_INVALID_ARG, "%s: scales must be [NB, Hkv]", op);
+    } else {
+        return fail(SFB_ERR_INVALID_ARG, "%s: granularity %d", op, granularity);
+    }
+    return SFB_OK;
+}
+
+int sfb_quantize_fp8(const SFBTensor* x, SFBTensor* codes, SFBTensor* scales, int x_dtype, int granularity, void* stream) {
+    View vx, vc, vs;
+    int rc = quant_views(x, codes, scales, x_dtype, granularity, "quantize", &vx, &vc, &vs);
+    if (rc) return rc;
+    if (vx.numel() == 0) return SFB_OK;
+    return launch_quantize(vx, vc, vs, x_dtype, granularity, static_cast<cudaStream_t>(stream));
+}
+
+int sfb_dequantize_fp8(const SFBTensor* codes, const SFBTensor* scales, SFBTensor* out, int out_dtype, int granularity,
+                       void* stream) {
+    View vx, vc, vs;
+    int rc = quant_views(out, codes, scales, out_dtype, granularity, "dequantize", &vx, &vc, &vs);
+    if (rc) return rc;
+    if (vx.numel() == 0) return SFB_OK;
+    return launch_dequantize(vc, vs, vx, out_dtype, granularity, static_cast<cudaStream_t>(stream));
+}
+
+int sfb_rms_norm(const SFBTensor* x, const SFBTensor* residual, const SFBTensor* weight, SFBTensor* out, int dtype,
+                 float eps, void* stream) {
+    const int e = dtype_size(dtype);
+    if (!e || dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "rms_norm: dtype %d", dtype);
+    View vx, vr, vw, vo;
+    int rc;
+    if ((rc = make_view(x, "x", 1, 2, e, &vx))) return rc;
+    if ((rc = make_view(out, "out", 1, 2, e, &vo))) return rc;
+    const int64_t rows = vx.size[2], hidden = vx.size[3];
+    if (vo.size[2] != rows || vo.size[3] != hidden) return fail(SFB_ERR_INVALID_ARG, "rms_norm: out shape differs from x");
+    if (residual) {
+        if ((rc = make_view(residual, "residual", 1, 2, e, &vr))) return rc;
+        if (vr.size[2] != rows || vr.size[3] != hidden) return fail(SFB_ERR_INVALID_ARG, "rms_norm: residual shape differs from x");
+    }
+    if (weight) {
+        if ((rc = make_view(weight, "weight", 1, 1, e, &vw))) return rc;
+        if (vw.size[3] != hidden) return fail(SFB_ERR_INVALID_ARG, "rms_norm: weight must have %lld elements", (long long)hidden);
+    }
+    if (rows == 0 || hidden == 0) return SFB_OK;
+    NormArgs a{};
+    a.x = vx.base; a.out = vo.base;
+    a.residual = residual ? vr.base : nullptr;
+    a.weight = weight ? vw.base : nullptr;
+    a.rows = rows; a.hidden = hidden;
+    a.x_stride = vx.stride[2]; a.out_stride = vo.stride[2]; a.res_stride = residual ? vr.stride[2] : 0;
+    a.dtype = dtype; a.eps = eps;
+    return launch_rms_norm(a, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,222 @@
+// Shared host/device helpers for libsfb.so (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/sfb.h"
+
+namespace sfb {
+
+// ---------------------------------------------------------------------------
+// Host side: error text per calling thread, descriptor views.
+// ---------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int fail(int status, const char* fmt, ...);
+
+#define SFB_CUDA_CHECK(expr)                                                          \
+    do {                                                                              \
+        cudaError_t err__ = (expr);                                                   \
+        if (err__ != cudaSuccess)                                                     \
+            return ::sfb::fail(SFB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__)); \
+    } while (0)
+
+// A descriptor flattened to rank 4 (leading dimensions of size 1, stride 0).
+struct View {
+    char* base = nullptr;  // element 0
+    int rank = 0;
+    int elem = 0;
+    int64_t size[4] = {1, 1, 1, 1};
+    int64_t stride[4] = {0, 0, 0, 0};  // elements
+    int64_t numel() const { return size[0] * size[1] * size[2] * size[3]; }
+};
+
+// Fills `v` from `t`; checks device, rank range and element size.  `what` names
+// the argument in the error text.
+int make_view(const SFBTensor* t, const char* what, int min_rank, int max_rank, int elem_size, View* v);
+
+inline int dtype_size(int dt) {
+    switch (dt) {
+        case SFB_F32: return 4;
+        case SFB_BF16: return 2;
+        case SFB_F16: return 2;
+        case SFB_F8E4M3: return 1;
+        default: return 0;
+    }
+}
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---------------------------------------------------------------------------
+// Workspace layout of the decode path (shared by the kernels and the size query):
+//   [0, 256)                     status word + padding
+//   part_ml [B][n_chunks][H][2]  float32 (running max in log2 units, denominator)
+//   part_o  [B][n_chunks][H][D]  float32 (unnormalised numerator)
+// ---------------------------------------------------------------------------
+constexpr int64_t kWorkspaceHeader = 256;
+constexpr int64_t kDefaultChunkTokens = 512;
+
+struct DecodeSplit {
+    int64_t chunk_tokens;
+    int64_t n_chunks;
+    int64_t ml_offset;
+    int64_t o_offset;
+    int64_t total_bytes;
+};
+
+inline DecodeSplit decode_split(int64_t batch, int64_t n_heads, int64_t head_dim, int64_t max_blocks,
+                                int64_t block_size, int64_t chunk_tokens) {
+    DecodeSplit s;
+    if (chunk_tokens <= 0) chunk_tokens = kDefaultChunkTokens;
+    chunk_tokens = ceil_div(chunk_tokens, block_size) * block_size;
+    s.chunk_tokens = chunk_tokens;
+    s.n_chunks = ceil_div(max_blocks * block_size, chunk_tokens);
+    if (s.n_chunks < 1) s.n_chunks = 1;
+    s.ml_offset = kWorkspaceHeader;
+    int64_t ml_bytes = batch * s.n_chunks * n_heads * 2 * 4;
+    s.o_offset = s.ml_offset + ceil_div(ml_bytes, 256) * 256;
+    s.total_bytes = s.o_offset + batch * s.n_chunks * n_heads * head_dim * 4;
+    if (s.n_chunks == 1) s.total_bytes = kWorkspaceHeader;
+    return s;
+}
+
+// ---------------------------------------------------------------------------
+// Device helpers
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+
+// e4m3 code -> float.  Exact (every e4m3 value is a float16 value).
+__device__ __forceinline__ float e4m3_to_float(uint8_t c) {
+    __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)c, __NV_E4M3);
+    return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+// Two floats -> two e4m3 codes (low byte = a).  Round to nearest even,
+// subnormals kept; magnitudes above 448 clamp to 448 (never reached by
+// x / (amax/448)), NaN stays NaN.
+__device__ __forceinline__ uint16_t float2_to_e4m3x2(float a, float b) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(b), "f"(a));
+    return r;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// 16-byte global load that does not allocate in L1 (streamed KV data).
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+#endif  // __CUDACC__
+
+// ---------------------------------------------------------------------------
+// Kernel launchers (one per .cu file), called from abi.cu after validation.
+// ---------------------------------------------------------------------------
+struct DecodeArgs {
+    const void* q;
+    const void* k;
+    const void* v;
+    const float* k_scale;
+    const float* v_scale;
+    const int32_t* tables;
+    const int32_t* seq_lens;
+    void* out;
+    int q_dtype, kv_dtype;
+    int batch, n_heads, n_kv_heads, head_dim, block_size, max_blocks;
+    int64_t n_pool_blocks;
+    int64_t q_stride[2];    // request, head (elements)
+    int64_t out_stride[2];  // request, head
+    int64_t k_stride[3];    // block, token, head (elements)
+    int64_t v_stride[3];
+    int64_t ks_stride[2];  // block, head
+    int64_t vs_stride[2];
+    int64_t table_stride;  // elements between rows
+    float scale;
+    DecodeSplit split;
+    char* workspace;  // may be null when split.n_chunks == 1
+};
+
+int launch_decode_generic(const DecodeArgs& a, cudaStream_t stream);
+int launch_decode_combine(const DecodeArgs& a, cudaStream_t stream);
+// Returns SFB_ERR_UNSUPPORTED (leaving the error text alone) when the shape is
+// outside what the TMA + tensor-core kernel covers; the caller then falls back
+// to the generic kernel.
+int launch_decode_tma(const DecodeArgs& a, cudaStream_t stream);
+
+struct AppendArgs {
+    const void* k_new;
+    const void* v_new;
+    const int32_t* cu_tokens;
+    const int32_t* start_pos;
+    const int32_t* tables;
+    int64_t table_stride;
+    int max_blocks;
+    void* k_cache;
+    void* v_cache;
+    float* k_scale;
+    float* v_scale;
+    void* k_tail;
+    void* v_tail;
+    int src_dtype, kv_dtype;
+    int batch, n_kv_heads, head_dim, block_size, max_new_tokens;
+    int64_t n_pool_blocks;
+    int64_t new_stride[2];   // token, head (elements)
+    int64_t vnew_stride[2];
+    int64_t k_stride[3];     // block, token, head
+    int64_t v_stride[3];
+    int64_t ks_stride[2];
+    int64_t vs_stride[2];
+    int64_t kt_stride[3];    // request, token, head
+    int64_t vt_stride[3];
+};
+int launch_cache_write(const AppendArgs& a, cudaStream_t stream);
+
+int launch_quantize(const View& x, const View& codes, const View& scales, int x_dtype, int granularity, cudaStream_t stream);
+int launch_dequantize(const View& codes, const View& scales, const View& out, int out_dtype, int granularity,
+                      cudaStream_t stream);
+
+struct NormArgs {
+    const void* x;
+    const void* residual;
+    const void* weight;
+    void* out;
+    int64_t rows, hidden;
+    int64_t x_stride, out_stride, res_stride;
+    int dtype;
+    float eps;
+};
+int launch_rms_norm(const NormArgs& a, cudaStream_t stream);
+
+}  // namespace sfb

@@ -1,0 +1,141 @@
+"""HAL backend: the reference's ``OpExecutor`` surface over libsfb.
+
+``OpExecutor.execute(op_name, inputs, **kwargs)`` is the seam the reference's
+engine calls (python_runtime/hal/interface.py:51-61; caller
+python_runtime/engine/mlir_executor.py:358).  ``B200Backend`` serves the
+attention hot-path operators on the GPU and forwards every other operator name
+to an optional fallback executor, the way the reference's ``TritonBackend``
+chains to the PyTorch backend (python_runtime/hal/triton_backend.py:48-65).
+
+Operator names: ``rms_norm`` is the live HAL name
+(pytorch_backend/_ops_norm.py:70); ``paged_attention``, ``cache_write``,
+``quantize`` and ``dequantize`` are the names sf-dialect/include/Sf/HALOps.td:184-211
+reserves; ``fused_rms_norm_add`` is the kernels-package name.
+"""
+
+from __future__ import annotations
+
+from abc import ABC, abstractmethod
+from collections.abc import Callable
+from typing import Any
+
+import torch
+
+from . import kernels_api, ops
+
+try:  # the reference's own ABC when its package is importable, else a local twin
+    from python_runtime.hal.interface import OpExecutor  # type: ignore
+except Exception:  # noqa: BLE001
+
+    class OpExecutor(ABC):  # type: ignore[no-redef]
+        """Same contract as python_runtime/hal/interface.py:45-74."""
+
+        @abstractmethod
+        def execute(self, op_name: str, inputs: list[Any], **kwargs: Any) -> torch.Tensor: ...
+
+        def async_copy(self, src: Any, dst: Any, byte_count: int) -> None:
+            raise NotImplementedError("async_copy not supported")
+
+        def memory_retrieve(self, key: Any, table: Any) -> torch.Tensor:
+            raise NotImplementedError("memory_retrieve not supported")
+
+        def send_kv_cache(self, blocks: Any, target_device: str) -> None:
+            raise NotImplementedError("send_kv_cache not supported")
+
+
+class B200Backend(OpExecutor):
+    """Attention hot-path operators on one B200.
+
+    Args:
+        fallback: executor for every operator name this backend does not own
+            (for the reference: ``PyTorchBackend("cuda")``).  Without one an
+            unknown name raises ``ValueError`` like the reference backend does
+            (pytorch_backend/__init__.py:112-119).
+        device: CUDA device the inputs are expected on.
+    """
+
+    def __init__(self, fallback: OpExecutor | None = None, device: str | torch.device = "cuda") -> None:
+        self._fallback = fallback
+        self.device = torch.device(device)
+        self._ops: dict[str, Callable[..., Any]] = {
+            "paged_attention": self._op_paged_attention,
+            "cache_write": self._op_cache_write,
+            "quantize": self._op_quantize,
+            "dequantize": self._op_dequantize,
+            "rms_norm": self._op_rms_norm,
+            "fused_rms_norm_add": self._op_fused_rms_norm_add,
+        }
+
+    def supported_ops(self) -> list[str]:
+        return sorted(self._ops)
+
+    def execute(self, op_name: str, inputs: list[Any], **kwargs: Any) -> Any:
+        handler = self._ops.get(op_name)
+        if handler is not None:
+            return handler(inputs, **kwargs)
+        if self._fallback is not None:
+            return self._fallback.execute(op_name, inputs, **kwargs)
+        raise ValueError(f"Unknown op: '{op_name}'")
+
+    # ── handlers ────────────────────────────────────────────────────────────
+    def _op_paged_attention(self, inputs: list[Any], **kw: Any) -> Any:
+        """inputs: ``[query, key_cache, value_cache, block_table]`` (HALOps.td:186-187).
+
+        ``block_table`` is either the reference's dict (then ``seq_lens`` is a
+        dict keyword and the result is a dict, like kernels.paged_attention) or a
+        dense int32 tensor ``[B,max_blocks]`` (then ``seq_lens`` is an int32
+        tensor and the result is ``[B,H,D]``)."""
+        q, k_cache, v_cache, table = inputs[:4]
+        seq_lens = kw.get("seq_lens", inputs[4] if len(inputs) > 4 else None)
+        common = dict(k_scale=kw.get("k_scale"), v_scale=kw.get("v_scale"), scale=kw.get("scale"),
+                      chunk_tokens=kw.get("chunk_tokens", 0))
+        if isinstance(table, dict):
+            return kernels_api.paged_attention(q, k_cache, v_cache, table, seq_lens or {},
+                                               block_size=kw.get("block_size", k_cache.shape[1]), **common)
+        if seq_lens is None:
+            raise ValueError("paged_attention with a dense block table needs seq_lens")
+        return ops.paged_attention_decode(q, k_cache, v_cache, table, seq_lens, workspace=kw.get("workspace"), **common)
+
+    def _op_cache_write(self, inputs: list[Any], **kw: Any) -> None:
+        """inputs: ``[key, value, positions]`` (HALOps.td:197-198) with keywords
+        ``k_cache, v_cache, block_tables`` (dense int32) and, for an e4m3 pool,
+        ``k_scale, v_scale, k_tail, v_tail``.  ``positions`` is either an int32
+        tensor ``[B]`` of start positions plus ``cu_tokens [B+1]``, or - for the
+        one-token-per-request decode step - just ``[B]`` positions."""
+        key, value, positions = inputs[:3]
+        b = positions.shape[0]
+        cu = kw.get("cu_tokens")
+        if cu is None:
+            cu = torch.arange(b + 1, dtype=torch.int32, device=key.device)
+            max_new = 1
+        else:
+            max_new = int(kw["max_new_tokens"])
+        ops.cache_write(key, value, cu, positions, kw["block_tables"], kw["k_cache"], kw["v_cache"],
+                        max_new_tokens=max_new, k_scale=kw.get("k_scale"), v_scale=kw.get("v_scale"),
+                        k_tail=kw.get("k_tail"), v_tail=kw.get("v_tail"))
+
+    def _op_quantize(self, inputs: list[Any], **kw: Any) -> Any:
+        """``quantize(input, dtype="fp8")`` -> ``(codes, scale)`` (HALOps.td:202-206)."""
+        dtype = kw.get("dtype", "fp8")
+        if dtype not in ("fp8", "fp8_e4m3", "float8_e4m3fn"):
+            raise ValueError(f"quantize: dtype {dtype!r} not supported (fp8 e4m3 only)")
+        return ops.quantize_fp8(inputs[0], per_block_head=bool(kw.get("per_block_head", False)))
+
+    def _op_dequantize(self, inputs: list[Any], **kw: Any) -> torch.Tensor:
+        return ops.dequantize_fp8(inputs[0], inputs[1], kw.get("out_dtype", torch.float32))
+
+    def _op_rms_norm(self, inputs: list[Any], **kw: Any) -> torch.Tensor:
+        """Same arguments as pytorch_backend/_ops_norm.py:30-45 (eps default 1e-5)."""
+        weight = inputs[1] if len(inputs) > 1 else None
+        return ops.rms_norm(inputs[0], weight, eps=kw.get("eps", 1e-5))
+
+    def _op_fused_rms_norm_add(self, inputs: list[Any], **kw: Any) -> torch.Tensor:
+        return ops.rms_norm(inputs[0], inputs[2], eps=kw.get("eps", 1e-6), residual=inputs[1])
+
+
+def register(name: str = "b200") -> None:
+    """Register the backend factory with the reference's registry
+    (python_runtime/hal/registry.py:13-21) when that package is importable."""
+    from python_runtime.hal import registry  # type: ignore
+
+    registry.register(name, lambda **kwargs: B200Backend(**kwargs))

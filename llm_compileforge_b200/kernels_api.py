@@ -1,0 +1,108 @@
+"""Drop-ins for the reference's ``kernels`` package and FP8 KV quantiser.
+
+Same names, argument meaning and error behaviour as the reference functions
+they replace; every call runs on the GPU through libsfb (no Triton, no CPU
+fallback: a CPU tensor raises ``ValueError``).
+
+    kernels/paged_attention.py:200-227   paged_attention
+    kernels/flash_attention.py:179-202   flash_attention_fwd
+    kernels/rms_norm.py:85-106           fused_rms_norm_add
+    compiler/quantize/fp8_kv_cache.py    FP8KVCacheQuantizer
+"""
+
+from __future__ import annotations
+
+import math
+from collections.abc import Mapping, Sequence
+
+import torch
+
+from . import ops
+from .tables import dense_block_tables
+
+
+def paged_attention(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_tables: Mapping[str, Sequence[int]],
+    seq_lens: Mapping[str, int],
+    block_size: int = 16,
+    scale: float | None = None,
+    *,
+    k_scale: torch.Tensor | None = None,
+    v_scale: torch.Tensor | None = None,
+    chunk_tokens: int = 0,
+) -> dict[str, torch.Tensor]:
+    """PagedAttention with block-table indirection (paged_attention.py:200-227).
+
+    ``q [B,H,D]``; ``k_cache``/``v_cache`` ``[NB,block_size,Hkv,D]``; returns
+    ``{request_id: [H,D]}``.  ``k_scale``/``v_scale`` (keyword-only, float32
+    ``[NB,Hkv]``) switch to an e4m3 code pool dequantised inside the kernel."""
+    if k_cache.shape[1] != block_size:
+        raise ValueError(f"k_cache block dimension {k_cache.shape[1]} != block_size {block_size}")
+    if not block_tables:
+        return {}
+    dense, lens, rids = dense_block_tables(block_tables, seq_lens, block_size, n_pool_blocks=k_cache.shape[0])
+    if len(rids) > q.shape[0]:
+        raise IndexError(f"{len(rids)} block tables for {q.shape[0]} query rows")
+    dev = q.device
+    out = ops.paged_attention_decode(
+        q[: len(rids)], k_cache, v_cache, dense.to(dev, non_blocking=True), lens.to(dev, non_blocking=True),
+        k_scale=k_scale, v_scale=v_scale, scale=scale, chunk_tokens=chunk_tokens,
+    )
+    return {rid: out[i] for i, rid in enumerate(rids)}
+
+
+def fused_rms_norm_add(
+    input_tensor: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6
+) -> torch.Tensor:
+    """RMSNorm + residual connection, fused (kernels/rms_norm.py:85-106; note the
+    1e-6 default).  Intermediates are float32 with one final rounding."""
+    return ops.rms_norm(input_tensor, weight, eps=eps, residual=residual)
+
+
+class FP8KVCacheQuantizer:
+    """GPU twin of compiler/quantize/fp8_kv_cache.py:19-140."""
+
+    SUPPORTED_HARDWARE: list[str] = ["H100", "H200", "B100", "B200", "MI300", "Ascend 910B", "Ascend 910C"]
+
+    def __init__(self, block_size: int = 16, fp8_max: float = 448.0) -> None:
+        if block_size <= 0:
+            raise ValueError(f"block_size must be positive, got {block_size}")
+        if fp8_max != 448.0:
+            raise ValueError("only the e4m3 range (fp8_max = 448) is implemented")
+        self.block_size = block_size
+        self.fp8_max = fp8_max
+
+    def check_hardware_support(self, device_name: str) -> bool:
+        return any(hw in device_name for hw in self.SUPPORTED_HARDWARE)
+
+    def quantize_block(self, kv_block: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """One scale for the whole tensor passed in (fp8_kv_cache.py:66-93)."""
+        return ops.quantize_fp8(kv_block, per_block_head=False)
+
+    def dequantize_block(self, quant_block: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+        """``quant_block.float() * scale`` (fp8_kv_cache.py:95-105)."""
+        return ops.dequantize_fp8(quant_block, scale, torch.float32)
+
+    def quantize_kv(self, k: torch.Tensor, v: torch.Tensor):
+        k_quant, k_scale = self.quantize_block(k)
+        v_quant, v_scale = self.quantize_block(v)
+        return k_quant, k_scale, v_quant, v_scale
+
+    def dequantize_kv(self, k_quant, k_scale, v_quant, v_scale):
+        return self.dequantize_block(k_quant, k_scale), self.dequantize_block(v_quant, v_scale)
+
+    # per-(block, kv_head) layout used by the paged pool
+    def quantize_pool(self, pool: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """``quantize_block`` applied to every ``pool[b, :, h, :]`` slice of a
+        ``[NB,bs,Hkv,D]`` pool: codes ``[NB,bs,Hkv,D]`` and scales ``[NB,Hkv]``."""
+        return ops.quantize_fp8(pool, per_block_head=True)
+
+    def dequantize_pool(self, codes: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+        return ops.dequantize_fp8(codes, scales, torch.float32)
+
+
+def default_scale(head_dim: int) -> float:
+    return 1.0 / math.sqrt(head_dim)

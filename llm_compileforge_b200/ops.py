@@ -1,0 +1,187 @@
+"""Tensor-level operators: torch CUDA tensors in, one libsfb call each.
+
+These are the device-resident forms (block tables and lengths already dense
+int32 tensors on the GPU) that a serving loop calls every step; the
+dict-based signatures of the reference's ``kernels`` package are in
+``kernels_api.py`` and the HAL ``OpExecutor`` in ``hal.py``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import check, current_stream, desc, dtype_code
+
+BLOCK_SIZE = 16
+
+
+def _as_codes(t: torch.Tensor) -> torch.Tensor:
+    """uint8 and float8_e4m3fn tensors are both accepted for code pools."""
+    return t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t
+
+
+def decode_workspace_bytes(batch: int, n_heads: int, head_dim: int, max_blocks: int, block_size: int = BLOCK_SIZE,
+                           chunk_tokens: int = 0) -> int:
+    n = _lib.load().sfb_paged_attention_workspace_bytes(batch, n_heads, head_dim, max_blocks, block_size, chunk_tokens)
+    if n < 0:
+        raise ValueError("invalid decode workspace query")
+    return int(n)
+
+
+def paged_attention_decode(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    seq_lens: torch.Tensor,
+    *,
+    k_scale: torch.Tensor | None = None,
+    v_scale: torch.Tensor | None = None,
+    scale: float | None = None,
+    chunk_tokens: int = 0,
+    workspace: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Decode attention of ``q [B,H,D]`` over a paged pool ``[NB,bs,Hkv,D]``.
+
+    ``block_tables`` int32 ``[B,max_blocks]``, ``seq_lens`` int32 ``[B]``, both on
+    the device.  An e4m3 pool (uint8 or float8_e4m3fn) needs ``k_scale`` /
+    ``v_scale`` float32 ``[NB,Hkv]``.  ``workspace`` (uint8) is allocated when
+    the split needs one and none is given; pass a persistent one in a serving
+    loop (size from :func:`decode_workspace_bytes`)."""
+    lib = _lib.load()
+    fp8 = k_scale is not None
+    kc, vc = (_as_codes(k_cache), _as_codes(v_cache)) if fp8 else (k_cache, v_cache)
+    kv_code = _lib.SFB_F8E4M3 if fp8 else dtype_code(k_cache.dtype)
+    if out is None:
+        out = torch.empty_like(q)
+    b, h, d = q.shape
+    need = decode_workspace_bytes(b, h, d, block_tables.shape[1], k_cache.shape[1], chunk_tokens)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    elif workspace.numel() * workspace.element_size() < need:
+        raise ValueError(f"decode workspace holds {workspace.numel() * workspace.element_size()} B, {need} needed")
+    check(lib.sfb_paged_attention_decode(
+        desc(q, "q"), desc(kc, "k_cache"), desc(vc, "v_cache"), desc(k_scale, "k_scale"), desc(v_scale, "v_scale"),
+        desc(block_tables, "block_tables"), desc(seq_lens, "seq_lens"), desc(out, "out"),
+        dtype_code(q.dtype), kv_code, float(scale) if scale is not None else 0.0, int(chunk_tokens),
+        workspace.data_ptr(), workspace.numel() * workspace.element_size(), current_stream(q.device),
+    ))
+    return out
+
+
+def read_status(workspace: torch.Tensor) -> int:
+    """Status bits left by the last decode call that used ``workspace``
+    (synchronises the current stream)."""
+    import ctypes
+
+    bits = ctypes.c_int32(0)
+    rc = _lib.load().sfb_read_status(workspace.data_ptr(), ctypes.byref(bits), current_stream(workspace.device))
+    if rc not in (_lib.SFB_OK, _lib.SFB_ERR_DEVICE_STATUS):
+        check(rc)
+    return int(bits.value)
+
+
+def cache_write(
+    k_new: torch.Tensor,
+    v_new: torch.Tensor,
+    cu_tokens: torch.Tensor,
+    start_pos: torch.Tensor,
+    block_tables: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    *,
+    max_new_tokens: int,
+    k_scale: torch.Tensor | None = None,
+    v_scale: torch.Tensor | None = None,
+    k_tail: torch.Tensor | None = None,
+    v_tail: torch.Tensor | None = None,
+) -> None:
+    """Scatter new K/V tokens ``[T,Hkv,D]`` into their paged slots; with scales
+    and tails given the pool holds e4m3 codes and the write quantises on append."""
+    lib = _lib.load()
+    fp8 = k_scale is not None
+    kc, vc = (_as_codes(k_cache), _as_codes(v_cache)) if fp8 else (k_cache, v_cache)
+    check(lib.sfb_cache_write(
+        desc(k_new, "k_new"), desc(v_new, "v_new"), desc(cu_tokens, "cu_tokens"), desc(start_pos, "start_pos"),
+        desc(block_tables, "block_tables"), desc(kc, "k_cache"), desc(vc, "v_cache"), desc(k_scale, "k_scale"),
+        desc(v_scale, "v_scale"), desc(k_tail, "k_tail"), desc(v_tail, "v_tail"), dtype_code(k_new.dtype),
+        _lib.SFB_F8E4M3 if fp8 else dtype_code(k_cache.dtype), int(max_new_tokens), current_stream(k_new.device),
+    ))
+
+
+def quantize_fp8(x: torch.Tensor, per_block_head: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """e4m3 codes (``float8_e4m3fn``, same shape) and float32 scale(s).
+
+    ``per_block_head=False``: one scale for the whole tensor (0-dim), the
+    reference's ``quantize_block``.  ``True``: ``x`` is ``[NB,bs,Hkv,D]`` and
+    scales are ``[NB,Hkv]``."""
+    lib = _lib.load()
+    if x.dim() > 4:
+        raise ValueError("quantize_fp8 takes tensors of rank <= 4")
+    xv = x if x.dim() >= 1 else x.reshape(1)
+    codes = torch.empty(xv.shape, dtype=torch.uint8, device=x.device)
+    if per_block_head:
+        scales = torch.empty((x.shape[0], x.shape[2]), dtype=torch.float32, device=x.device)
+    else:
+        scales = torch.empty((1,), dtype=torch.float32, device=x.device)
+    if xv.stride(-1) != 1:
+        xv = xv.contiguous()
+    check(lib.sfb_quantize_fp8(
+        desc(xv, "x"), desc(codes, "codes"), desc(scales, "scales"), dtype_code(x.dtype),
+        _lib.SFB_QUANT_PER_BLOCK_HEAD if per_block_head else _lib.SFB_QUANT_PER_TENSOR, current_stream(x.device),
+    ))
+    codes = codes.view(torch.float8_e4m3fn).reshape(x.shape)
+    return codes, (scales if per_block_head else scales.reshape(()))
+
+
+def dequantize_fp8(codes: torch.Tensor, scales: torch.Tensor, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """``codes.float() * scale``; scales 0-dim / 1 element (whole tensor) or
+    ``[NB,Hkv]`` for a ``[NB,bs,Hkv,D]`` pool."""
+    lib = _lib.load()
+    cv = _as_codes(codes)
+    if cv.dim() == 0:
+        cv = cv.reshape(1)
+    if cv.stride(-1) != 1:
+        cv = cv.contiguous()
+    per_block_head = scales.dim() == 2
+    sv = scales if per_block_head else scales.reshape(1)
+    out = torch.empty(cv.shape, dtype=out_dtype, device=codes.device)
+    check(lib.sfb_dequantize_fp8(
+        desc(cv, "codes"), desc(sv, "scales"), desc(out, "out"), dtype_code(out_dtype),
+        _lib.SFB_QUANT_PER_BLOCK_HEAD if per_block_head else _lib.SFB_QUANT_PER_TENSOR, current_stream(codes.device),
+    ))
+    return out.reshape(codes.shape)
+
+
+def rms_norm(
+    x: torch.Tensor,
+    weight: torch.Tensor | None,
+    eps: float = 1e-5,
+    residual: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """``s * rsqrt(mean(s^2) + eps) * weight`` with ``s = x (+ residual)``;
+    float32 arithmetic, one rounding to ``x.dtype``."""
+    lib = _lib.load()
+    hidden = x.shape[-1]
+    x2 = x.reshape(-1, hidden)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    r2 = None
+    if residual is not None:
+        if residual.shape != x.shape or residual.dtype != x.dtype:
+            raise ValueError("residual must match x in shape and dtype")
+        r2 = residual.reshape(-1, hidden)
+        if r2.stride(-1) != 1:
+            r2 = r2.contiguous()
+    w = weight
+    if w is not None and w.dtype != x.dtype:
+        w = w.to(x.dtype)
+    if w is not None and not w.is_contiguous():
+        w = w.contiguous()
+    o2 = torch.empty_like(x2) if out is None else out.reshape(-1, hidden)
+    check(lib.sfb_rms_norm(desc(x2, "x"), desc(r2, "residual"), desc(w, "weight"), desc(o2, "out"),
+                           dtype_code(x.dtype), float(eps), current_stream(x.device)))
+    return o2.reshape(x.shape) if out is None else out

@@ -1,0 +1,68 @@
+"""Block-table wire formats: the reference's dicts <-> the dense int32 arrays of the C ABI.
+
+The reference passes ``block_tables: dict[str, list[int]]`` and
+``seq_lens: dict[str, int]`` (kernels/paged_attention.py:25-26); row ``i`` of
+``q`` belongs to the i-th key in insertion order (:36,:54).  The C ABI takes
+``int32 [B, max_blocks]`` and ``int32 [B]``.
+"""
+
+from __future__ import annotations
+
+from collections.abc import Mapping, Sequence
+
+import torch
+
+
+def dense_block_tables(
+    block_tables: Mapping[str, Sequence[int]],
+    seq_lens: Mapping[str, int],
+    block_size: int,
+    n_pool_blocks: int | None = None,
+    min_width: int = 1,
+) -> tuple[torch.Tensor, torch.Tensor, list[str]]:
+    """Dense CPU (pinned when CUDA is available) tables in dict insertion order.
+
+    Follows kernels/paged_attention.py:37-48: a missing length means the whole
+    table (``len(table)*block_size``), a length beyond the table's capacity is
+    truncated to it, blocks past ``ceil(L/bs)`` are dropped.  Raises
+    ``ValueError`` for a request that would attend to zero tokens (the reference
+    fails in ``torch.cat`` there) or a block id outside the pool."""
+    rids = list(block_tables.keys())
+    lens: list[int] = []
+    used: list[Sequence[int]] = []
+    for rid in rids:
+        table = block_tables[rid]
+        length = seq_lens.get(rid, len(table) * block_size)
+        length = min(int(length), len(table) * block_size)
+        if length <= 0:
+            raise ValueError(f"request {rid!r} attends to zero tokens")
+        n = -(-length // block_size)
+        used.append(table[:n])
+        lens.append(length)
+    width = max([min_width] + [len(t) for t in used])
+    pin = torch.cuda.is_available()
+    dense = torch.zeros((len(rids), width), dtype=torch.int32, pin_memory=pin)
+    for i, t in enumerate(used):
+        row = torch.as_tensor(list(t), dtype=torch.int64)
+        if n_pool_blocks is not None and row.numel() and (int(row.min()) < 0 or int(row.max()) >= n_pool_blocks):
+            raise ValueError(f"request {rids[i]!r}: block id outside the pool of {n_pool_blocks} blocks")
+        dense[i, : len(t)] = row.to(torch.int32)
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    if pin:
+        lens_t = lens_t.pin_memory()
+    return dense, lens_t, rids
+
+
+def partition_by_request(lengths: Sequence[int], world_size: int) -> list[list[int]]:
+    """Contiguous request ranges balanced by attended tokens: rank ``g`` gets the
+    requests whose running token sum falls in the g-th equal share.  Contiguity
+    keeps the all-gathered output in request order."""
+    total = sum(lengths)
+    parts: list[list[int]] = [[] for _ in range(world_size)]
+    acc = 0
+    for i, n in enumerate(lengths):
+        mid = acc + n / 2
+        g = min(world_size - 1, int(mid * world_size / total)) if total else i % world_size
+        parts[g].append(i)
+        acc += n
+    return parts

@@ -1,0 +1,141 @@
+"""C-ABI checks that need no GPU: the library loads, exports every symbol the
+header declares, descriptor layouts match the reference's memref contract, and
+argument validation rejects bad calls before any kernel launch."""
+
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from llm_compileforge_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = []
+    inc = os.path.join(ROOT, "include")
+    for f in os.listdir(inc):
+        if f.endswith(".h"):
+            text = open(os.path.join(inc, f)).read()
+            names += re.findall(r"SFB_API\s+[\w\s\*]+?\b(\w+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = declared_symbols()
+    assert "sfb_paged_attention_decode" in names and len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), f"libsfb.so does not export {n}"
+    assert lib.sfb_abi_version() == 1
+
+
+def test_descriptor_layout_matches_memref_contract():
+    # tests/contract/memref_3way.c:26-36 of the reference: 40/56/72/88 bytes, fields at 0/8/16
+    for cls, size in ((_lib.SFBMemRef1, 40), (_lib.SFBMemRef2, 56), (_lib.SFBMemRef3, 72), (_lib.SFBMemRef4, 88)):
+        assert ctypes.sizeof(cls) == size
+        assert (cls.allocated.offset, cls.aligned.offset, cls.offset.offset, cls.sizes.offset) == (0, 8, 16, 24)
+    assert ctypes.sizeof(_lib.SFBTensor) == 104
+    assert _lib.SFBTensor.raw.offset == 16
+
+
+def _fake_desc(shape, elem, device=_lib.SFB_DEVICE_CUDA, ptr=0x1000, strides=None):
+    d = _lib.SFBTensor()
+    d.device, d.rank, d.elem_size = device, len(shape), elem
+    raw = getattr(d, f"r{len(shape)}")
+    raw.allocated = raw.aligned = ptr
+    st = strides
+    if st is None:
+        st, acc = [], 1
+        for s in reversed(shape):
+            st.insert(0, acc)
+            acc *= s
+    for i, s in enumerate(shape):
+        raw.sizes[i] = s
+        raw.strides[i] = st[i]
+    return d
+
+
+def _decode(lib, q, k, v, t, l, o, qd=_lib.SFB_BF16, kvd=_lib.SFB_BF16, ks=None, vs=None, ws=None, ws_bytes=0):
+    r = lambda x: None if x is None else ctypes.byref(x)
+    return lib.sfb_paged_attention_decode(r(q), r(k), r(v), r(ks), r(vs), r(t), r(l), r(o), qd, kvd, 0.0, 0, ws, ws_bytes, None)
+
+
+def test_decode_argument_validation():
+    lib = _lib.load()
+    q = _fake_desc((2, 8, 64), 2)
+    o = _fake_desc((2, 8, 64), 2)
+    k = _fake_desc((10, 16, 2, 64), 2)
+    t = _fake_desc((2, 4), 4)
+    l = _fake_desc((2,), 4)
+    assert _decode(lib, None, k, k, t, l, o) == _lib.SFB_ERR_INVALID_ARG
+    assert b"NULL" in lib.sfb_last_error()
+    cpu_q = _fake_desc((2, 8, 64), 2, device=_lib.SFB_DEVICE_CPU)
+    assert _decode(lib, cpu_q, k, k, t, l, o) == _lib.SFB_ERR_INVALID_ARG
+    assert b"no CPU path" in lib.sfb_last_error()
+    assert _decode(lib, q, k, k, t, l, o, qd=_lib.SFB_F32) == _lib.SFB_ERR_INVALID_ARG  # elem_size 2 != 4
+    bad_heads = _fake_desc((10, 16, 3, 64), 2)
+    assert _decode(lib, q, bad_heads, bad_heads, t, l, o) == _lib.SFB_ERR_INVALID_ARG
+    assert _decode(lib, q, k, _fake_desc((11, 16, 2, 64), 2), t, l, o) == _lib.SFB_ERR_INVALID_ARG
+    assert _decode(lib, q, k, k, _fake_desc((3, 4), 4), l, o) == _lib.SFB_ERR_INVALID_ARG
+    strided = _fake_desc((2, 8, 64), 2, strides=[1024, 128, 2])
+    assert _decode(lib, strided, k, k, t, l, o) == _lib.SFB_ERR_INVALID_ARG
+    # e4m3 pool without scales
+    k8 = _fake_desc((10, 16, 2, 64), 1)
+    assert _decode(lib, q, k8, k8, t, l, o, kvd=_lib.SFB_F8E4M3) == _lib.SFB_ERR_INVALID_ARG
+    # split needs a workspace: 4 blocks * 16 = 64 tokens > chunk 16
+    r = ctypes.byref
+    rc = lib.sfb_paged_attention_decode(r(q), r(k), r(k), None, None, r(t), r(l), r(o), _lib.SFB_BF16, _lib.SFB_BF16,
+                                        0.0, 16, None, 0, None)
+    assert rc == _lib.SFB_ERR_WORKSPACE
+    assert lib.sfb_status_string(rc) == b"workspace missing or too small"
+
+
+def test_workspace_size_query():
+    lib = _lib.load()
+    one = lib.sfb_paged_attention_workspace_bytes(8, 12, 64, 32, 16, 512)
+    assert one == 256  # 32 blocks * 16 = 512 tokens: a single chunk, status word only
+    two = lib.sfb_paged_attention_workspace_bytes(8, 12, 64, 33, 16, 512)
+    assert two >= 256 + 8 * 2 * 12 * (64 + 2) * 4
+    assert lib.sfb_paged_attention_workspace_bytes(8, 0, 64, 33, 16, 512) < 0
+
+
+def test_other_entry_points_validate():
+    lib = _lib.load()
+    r = ctypes.byref
+    x = _fake_desc((4, 128), 2)
+    w = _fake_desc((64,), 2)
+    assert lib.sfb_rms_norm(r(x), None, r(w), r(x), _lib.SFB_BF16, 1e-5, None) == _lib.SFB_ERR_INVALID_ARG
+    assert lib.sfb_rms_norm(r(x), None, None, r(x), 7, 1e-5, None) == _lib.SFB_ERR_INVALID_ARG
+    xs = _fake_desc((3, 16, 2, 32), 2)
+    c = _fake_desc((3, 16, 2, 32), 1)
+    s = _fake_desc((3, 3), 4)
+    assert lib.sfb_quantize_fp8(r(xs), r(c), r(s), _lib.SFB_BF16, _lib.SFB_QUANT_PER_BLOCK_HEAD, None) == _lib.SFB_ERR_INVALID_ARG
+    assert lib.sfb_quantize_fp8(r(xs), r(c), r(s), _lib.SFB_BF16, 9, None) == _lib.SFB_ERR_INVALID_ARG
+
+
+def test_python_layer_refuses_cpu_tensors():
+    import llm_compileforge_b200 as pkg
+
+    q = torch.zeros(1, 4, 32)
+    kv = torch.zeros(4, 16, 4, 32)
+    with pytest.raises(ValueError, match="CUDA"):
+        pkg.paged_attention(q, kv, kv, {"a": [0]}, {"a": 3})
+    with pytest.raises(ValueError, match="CUDA"):
+        pkg.fused_rms_norm_add(torch.zeros(2, 8), torch.zeros(2, 8), torch.ones(8))
+    with pytest.raises(ValueError, match="zero tokens"):
+        pkg.paged_attention(q, kv, kv, {"a": [0]}, {"a": 0})
+    with pytest.raises(ValueError, match="outside the pool"):
+        pkg.paged_attention(q, kv, kv, {"a": [9]}, {"a": 3})
+    with pytest.raises(ValueError, match="Unknown op"):
+        pkg.B200Backend().execute("matmul", [q, q])
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libsfb.so"))
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.load()

@@ -1,0 +1,65 @@
+"""Host-side logic: table adapters, request partitioning, workload generators,
+HAL dispatch and fallback chaining.  CPU only."""
+
+import pytest
+import torch
+
+from llm_compileforge_b200 import workloads as wl
+from llm_compileforge_b200.hal import B200Backend, OpExecutor
+from llm_compileforge_b200.tables import dense_block_tables, partition_by_request
+
+
+def test_dense_tables_follow_reference_rules():
+    tables = {"nolen": [3, 4], "toolong": [5, 1], "surplus": [0, 2, 7, 9], "one": [11]}
+    lens = {"toolong": 100, "surplus": 17, "one": 1}
+    dense, ll, rids = dense_block_tables(tables, lens, 16, n_pool_blocks=12)
+    assert rids == ["nolen", "toolong", "surplus", "one"]  # insertion order, not sorted
+    assert ll.tolist() == [32, 32, 17, 1]  # missing -> capacity; over-long -> capacity
+    assert dense.dtype == torch.int32 and dense.shape == (4, 2)
+    assert dense[2].tolist() == [0, 2]  # blocks past ceil(17/16) dropped
+    assert dense[3].tolist() == [11, 0]
+
+
+def test_partition_is_contiguous_and_balanced():
+    lengths = wl.config_lengths(wl.C5, batch=512)
+    parts = partition_by_request(lengths, 8)
+    flat = [i for p in parts for i in p]
+    assert flat == list(range(512))
+    loads = [sum(lengths[i] for i in p) for p in parts]
+    assert max(loads) <= 1.15 * (sum(lengths) / 8)
+
+
+def test_config_generators():
+    assert all(64 <= n <= 512 for n in wl.config_lengths(wl.C1))
+    l3 = wl.config_lengths(wl.C3)
+    assert len(l3) == 256 and min(l3) >= 128 and max(l3) <= 8192
+    med = sorted(l3)[128]
+    assert 1500 < med < 2800
+    w = wl.make_decode_workload(wl.C1)
+    assert w.q.shape == (8, 12, 64) and w.k_cache.shape == (512, 16, 12, 64)
+    ids = [b for t in w.block_tables.values() for b in t]
+    assert len(ids) == len(set(ids))  # non-overlapping
+    # algorithmic bytes: K+V per valid token per kv head dominate
+    n = wl.decode_algorithmic_bytes([100], 32, 8, 128, 1, 2, 2, True)
+    assert n == 2 * 100 * 8 * 128 + 2 * 7 * 8 * 4 + 4 * 7 + 4 + 32 * 128 * 4
+    assert wl.prefill_flops(32, 32, 128, 512, 2048) == 4 * 128 * 32 * 32 * (512 * 2048 + 512 * 513 // 2)
+
+
+class _Recorder(OpExecutor):
+    def __init__(self):
+        self.calls = []
+
+    def execute(self, op_name, inputs, **kwargs):
+        self.calls.append(op_name)
+        return "fallback"
+
+
+def test_backend_dispatch_and_fallback():
+    rec = _Recorder()
+    be = B200Backend(fallback=rec)
+    assert be.execute("matmul", [1, 2]) == "fallback" and rec.calls == ["matmul"]
+    assert {"paged_attention", "cache_write", "quantize", "dequantize", "rms_norm", "fused_rms_norm_add"} <= set(be.supported_ops())
+    with pytest.raises(ValueError, match="Unknown op"):
+        B200Backend().execute("softmax", [torch.zeros(2)])
+    with pytest.raises(ValueError, match="fp8"):
+        be.execute("quantize", [torch.zeros(2)], dtype="int8")
