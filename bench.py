@@ -1,0 +1,433 @@
+"""Benchmark of the paged FP8-KV decode hot path (one JSON line on stdout).
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...        # the reference's CPU algorithm on the host cores
+
+Workload: the Llama-3-70B-shaped FP8-KV decode configuration (64 query heads,
+8 kv heads, head_dim 128, block_size 16, 2048 requests, lognormal context
+lengths with median 4096 clipped to [256, 32768], e4m3 KV with per-(block,
+kv_head) float32 scales) - the whole configuration resident on EACH GPU, requests
+partitioned across GPUs (weak scaling, no data-path collective).
+
+One step = one decode iteration of the hot path: quantise-on-append of one new
+token per request into the paged FP8 pool, then paged attention of one query
+token per request over the pool (split kernel + combine).  ``value`` is decode
+tokens/s with every input already in HBM; ``e2e`` is the same step driven
+through the HAL ``OpExecutor`` with host (pinned) inputs: q, new K/V, block
+tables and lengths are copied to the device and the attention output back to
+the host inside the timed region.  The KV pool is device state, as in serving.
+
+Inputs are synthetic (seeded); the 22.7 GB code pool is far larger than L2, so
+no flush is needed between steps.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from llm_compileforge_b200 import workloads as wl  # noqa: E402
+
+METRIC = "paged_fp8_decode_tokens_per_s"
+UNIT = "tokens/s"
+NOMINAL_HBM_GBS = 8000.0
+
+
+def parse_args() -> argparse.Namespace:
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    p.add_argument("--workload", choices=["c5", "c3", "c2"], default="c5")
+    p.add_argument("--batch", type=int, default=0, help="requests per GPU (0 = the configuration's batch)")
+    p.add_argument("--chunk-tokens", type=int, default=0, help="KV split size (0 = heuristic)")
+    p.add_argument("--gather", action="store_true", help="all-gather the outputs over NCCL inside the step")
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--cpu-sample", type=int, default=48, help="requests in the CPU-baseline sample")
+    return p.parse_args()
+
+
+def shape_of(name: str) -> wl.DecodeShape:
+    return {"c5": wl.C5, "c3": wl.C3, "c2": wl.C2}[name]
+
+
+def peaks() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed
+    region runs (read-only queries)."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                for line in out.strip().splitlines():
+                    self.rows.append([c.strip() for c in line.split(",")])
+            except Exception:  # noqa: BLE001
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower() == "active" for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def pick_chunk_tokens(lengths: list[int], requested: int) -> int:
+    """Split size: enough work items to fill the GPU many times over, few
+    enough that partial results stay a small share of the KV traffic."""
+    if requested > 0:
+        return requested
+    total = sum(lengths)
+    for cand in (2048, 1024, 512, 256):
+        items = sum(-(-n // cand) for n in lengths)
+        if items >= 148 * 16 or cand == 256:
+            return cand if total >= 148 * 16 * 256 else 256
+    return 512
+
+
+class DecodeState:
+    """Device-resident serving state for one GPU: the FP8 pool, tables, tails."""
+
+    def __init__(self, shape: wl.DecodeShape, batch: int, steps_total: int, dev: torch.device, seed_offset: int):
+        from llm_compileforge_b200 import ops
+
+        self.shape, self.dev = shape, dev
+        bs, hkv, d = shape.block_size, shape.n_kv_heads, shape.head_dim
+        self.fp8 = shape.kv_fp8
+        self.lengths = wl.config_lengths(shape, batch) if seed_offset == 0 else _rank_lengths(shape, batch, seed_offset)
+        self.batch = len(self.lengths)
+        extra = -(-(steps_total + 1) // bs) + 1  # room for the tokens appended while benchmarking
+        self.n_blocks = wl.pool_blocks_for(shape, self.lengths, extra)
+        tables = wl.random_tables(self.lengths, self.n_blocks, 1005 + shape.index + seed_offset, bs, extra)
+        width = max(len(t) for t in tables.values())
+        dense = torch.zeros((self.batch, width), dtype=torch.int32)
+        for i, t in enumerate(tables.values()):
+            dense[i, : len(t)] = torch.as_tensor(t, dtype=torch.int32)
+        self.tables_host = dense.pin_memory()
+        self.tables = dense.to(dev)
+        kv_dtype = torch.uint8 if self.fp8 else shape.dtype
+        self.k_cache = torch.zeros((self.n_blocks, bs, hkv, d), dtype=kv_dtype, device=dev)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        if self.fp8:
+            self.k_scale = torch.ones((self.n_blocks, hkv), dtype=torch.float32, device=dev)
+            self.v_scale = torch.ones_like(self.k_scale)
+            self.k_tail = torch.zeros((self.batch, bs, hkv, d), dtype=shape.dtype, device=dev)
+            self.v_tail = torch.zeros_like(self.k_tail)
+        else:
+            self.k_scale = self.v_scale = self.k_tail = self.v_tail = None
+        # fill the pool through the product's own cache write, a group of requests at a time
+        gen = torch.Generator(device=dev).manual_seed(1002 + shape.index + seed_offset)
+        gain = 2.0 if self.fp8 else 1.0
+        group = 64
+        for lo in range(0, self.batch, group):
+            ls = self.lengths[lo : lo + group]
+            total = sum(ls)
+            k_new = (torch.randn((total, hkv, d), generator=gen, device=dev) * gain).to(shape.dtype)
+            v_new = (torch.randn((total, hkv, d), generator=gen, device=dev) * gain).to(shape.dtype)
+            cu = torch.zeros(len(ls) + 1, dtype=torch.int32)
+            cu[1:] = torch.tensor(ls).cumsum(0)
+            ops.cache_write(k_new, v_new, cu.to(dev), torch.zeros(len(ls), dtype=torch.int32, device=dev),
+                            self.tables[lo : lo + len(ls)], self.k_cache, self.v_cache, max_new_tokens=max(ls),
+                            k_scale=self.k_scale, v_scale=self.v_scale,
+                            k_tail=None if not self.fp8 else self.k_tail[lo : lo + len(ls)],
+                            v_tail=None if not self.fp8 else self.v_tail[lo : lo + len(ls)])
+            del k_new, v_new
+        torch.cuda.synchronize(dev)
+        self.q = torch.randn((self.batch, shape.n_heads, d), generator=gen, device=dev).to(shape.dtype)
+        self.new_k = (torch.randn((self.batch, hkv, d), generator=gen, device=dev) * gain).to(shape.dtype)
+        self.new_v = (torch.randn((self.batch, hkv, d), generator=gen, device=dev) * gain).to(shape.dtype)
+        self.cu_one = torch.arange(self.batch + 1, dtype=torch.int32, device=dev)
+        base = torch.tensor(self.lengths, dtype=torch.int32)
+        self.pos_steps_host = (base[None, :] + torch.arange(steps_total, dtype=torch.int32)[:, None]).contiguous().pin_memory()
+        self.pos_steps = self.pos_steps_host.to(dev)          # position of the token appended in step s
+        self.len_steps_host = (self.pos_steps_host + 1).pin_memory()
+        self.len_steps = self.len_steps_host.to(dev)          # attended length in step s
+
+    def algorithmic_bytes(self, step: int) -> int:
+        s = self.shape
+        lens = [n + step + 1 for n in self.lengths]
+        e = 2 if s.dtype in (torch.bfloat16, torch.float16) else 4
+        return wl.decode_algorithmic_bytes(lens, s.n_heads, s.n_kv_heads, s.head_dim, 1 if self.fp8 else e, e, e, self.fp8,
+                                           s.block_size)
+
+
+def _rank_lengths(shape: wl.DecodeShape, batch: int | None, offset: int) -> list[int]:
+    b = shape.batch if batch is None else batch
+    if shape.index == 5:
+        return wl.lognormal_lengths(b, 4096, 256, 32768, 1004 + shape.index + offset)
+    if shape.index == 3:
+        return wl.lognormal_lengths(b, 2048, 128, 8192, 1004 + shape.index + offset)
+    return wl.uniform_lengths(b, 1024, 4096, 1004 + shape.index + offset)
+
+
+def cpu_baseline(shape: wl.DecodeShape, lengths: list[int], n_sample: int, repeats: int = 1) -> dict:
+    """The reference's CPU algorithm (oracle port: dequantise the request's
+    blocks, gather, GQA-expand, SDPA per request) on the host cores, on a seeded
+    sample of the workload's requests."""
+    from oracle import reference_port as ref
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    pick = torch.randperm(len(lengths), generator=torch.Generator().manual_seed(99))[:n_sample].tolist()
+    ls = [lengths[i] for i in pick]
+    bs, hkv, d = shape.block_size, shape.n_kv_heads, shape.head_dim
+    nb = sum(wl.blocks_for(n, bs) for n in ls)
+    tables, at = {}, 0
+    for i, n in enumerate(ls):
+        tables[f"r{i}"] = list(range(at, at + wl.blocks_for(n, bs)))
+        at += wl.blocks_for(n, bs)
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn((len(ls), shape.n_heads, d), generator=g).to(shape.dtype)
+    seq = {f"r{i}": n for i, n in enumerate(ls)}
+    if shape.kv_fp8:
+        kc = torch.randint(0, 0x7E, (nb, bs, hkv, d), generator=g, dtype=torch.uint8)
+        vc = torch.randint(0, 0x7E, (nb, bs, hkv, d), generator=g, dtype=torch.uint8)
+        ks = torch.rand((nb, hkv), generator=g) * 0.02 + 0.01
+        vs = torch.rand((nb, hkv), generator=g) * 0.02 + 0.01
+
+        def run():
+            kd, vd = ref.fp8_dequantize_pool(kc, ks), ref.fp8_dequantize_pool(vc, vs)
+            return ref.paged_attention(q.float(), kd, vd, tables, seq)
+    else:
+        k = torch.randn((nb, bs, hkv, d), generator=g).to(shape.dtype)
+        v = torch.randn((nb, bs, hkv, d), generator=g).to(shape.dtype)
+
+        def run():
+            return ref.paged_attention(q, k, v, tables, seq)
+
+    run()  # warm-up
+    best = math.inf
+    for _ in range(max(1, repeats)):
+        t0 = time.perf_counter()
+        run()
+        best = min(best, time.perf_counter() - t0)
+    return {"value": len(ls) / best, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{len(ls)} seeded requests of the workload ({sum(ls)} KV tokens), best of {max(1, repeats)}, "
+                      f"{best:.3f} s per pass, torch CPU threads = {cores}"}
+
+
+def run_reference(args: argparse.Namespace, rank: int) -> None:
+    if rank != 0:
+        return
+    shape = shape_of(args.workload)
+    lengths = wl.config_lengths(shape, args.batch or None)
+    n_sample = min(args.cpu_sample, len(lengths))
+    from oracle import reference_port as ref  # noqa: F401  (the reference arm runs the oracle port)
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    # each step is one pass over the bounded sample
+    times = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        r = cpu_baseline(shape, lengths, n_sample, repeats=1)
+        if i >= args.warmup:
+            times.append(n_sample / r["value"])
+        base = r
+    ms = 1e3 * sum(times) / len(times)
+    value = n_sample / (ms / 1e3)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": workload_config(shape, len(lengths), args, 0),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": base["sample"]},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(shape: wl.DecodeShape, batch: int, args: argparse.Namespace, chunk: int) -> dict:
+    return {
+        "workload": f"{shape.name} paged decode, {batch} requests per GPU, H {shape.n_heads}/{shape.n_kv_heads}, "
+                    f"D {shape.head_dim}, block 16, {'e4m3 KV + fp32 scales' if shape.kv_fp8 else 'bf16 KV'}",
+        "requests_per_gpu": batch, "partition": "by request", "chunk_tokens": chunk,
+        "l2": "pool (GBs) >> L2, no flush needed", "step": "kv append (1 token/request) + decode + combine",
+    }
+
+
+def main() -> None:
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
+
+    import torch.distributed as dist
+
+    from llm_compileforge_b200 import B200Backend, ops
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    shape = shape_of(args.workload)
+    total_steps = args.warmup + args.steps
+    # two passes (device-resident, then end-to-end) each append `total_steps` tokens
+    st = DecodeState(shape, args.batch or shape.batch, 2 * total_steps + 2, dev, seed_offset=rank * 100)
+    chunk = pick_chunk_tokens(st.lengths, args.chunk_tokens)
+    ws_bytes = ops.decode_workspace_bytes(st.batch, shape.n_heads, shape.head_dim, st.tables.shape[1], shape.block_size, chunk)
+    workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)
+    out = torch.empty_like(st.q)
+    gathered = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device=dev) if (args.gather and world > 1) else None
+    be = B200Backend(device=dev)
+    fp8kw = dict(k_scale=st.k_scale, v_scale=st.v_scale) if st.fp8 else {}
+    tailkw = dict(k_tail=st.k_tail, v_tail=st.v_tail) if st.fp8 else {}
+
+    def step_device(s: int, ev=None) -> None:
+        ops.cache_write(st.new_k, st.new_v, st.cu_one, st.pos_steps[s], st.tables, st.k_cache, st.v_cache,
+                        max_new_tokens=1, **fp8kw, **tailkw)
+        if ev:
+            ev[0].record()
+        ops.paged_attention_decode(st.q, st.k_cache, st.v_cache, st.tables, st.len_steps[s], scale=None,
+                                   chunk_tokens=chunk, workspace=workspace, out=out, **fp8kw)
+        if ev:
+            ev[1].record()
+        if gathered is not None:
+            dist.all_gather_into_tensor(gathered, out)
+
+    def sync_all() -> None:
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    # ---- device-resident timing -------------------------------------------------
+    for s in range(args.warmup):
+        step_device(s)
+    sync_all()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        t_start.record()
+        for i in range(args.steps):
+            step_device(args.warmup + i, evs[i])
+        t_end.record()
+        sync_all()
+    elapsed_ms = t_start.elapsed_time(t_end)
+    decode_ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps  # decode + combine launches
+    status = ops.read_status(workspace)
+
+    # ---- end-to-end through the HAL executor with host buffers --------------------
+    host_q = st.q.cpu().pin_memory()
+    host_k, host_v = st.new_k.cpu().pin_memory(), st.new_v.cpu().pin_memory()
+    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    h2d = (host_q.numel() * host_q.element_size() + 2 * host_k.numel() * host_k.element_size()
+           + st.tables_host.numel() * 4 + 2 * st.batch * 4)
+    d2h = host_out.numel() * host_out.element_size()
+
+    def step_e2e(s: int) -> None:
+        q_d = host_q.to(dev, non_blocking=True)
+        k_d = host_k.to(dev, non_blocking=True)
+        v_d = host_v.to(dev, non_blocking=True)
+        tab = st.tables_host.to(dev, non_blocking=True)
+        pos = st.pos_steps_host[s].to(dev, non_blocking=True)
+        lens = st.len_steps_host[s].to(dev, non_blocking=True)
+        be.execute("cache_write", [k_d, v_d, pos], k_cache=st.k_cache, v_cache=st.v_cache, block_tables=tab,
+                   **fp8kw, **tailkw)
+        o = be.execute("paged_attention", [q_d, st.k_cache, st.v_cache, tab], seq_lens=lens, chunk_tokens=chunk,
+                       workspace=workspace, **fp8kw)
+        host_out.copy_(o, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()  # the caller needs the result before the next step
+
+    off = total_steps
+    for s in range(args.warmup):
+        step_e2e(off + s)
+    sync_all()
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for i in range(args.steps):
+        step_e2e(off + args.warmup + i)
+    e_end.record()
+    sync_all()
+    e2e_ms = e_start.elapsed_time(e_end)
+
+    if world > 1:
+        t = torch.tensor([elapsed_ms, e2e_ms, decode_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, e2e_ms, decode_ms = t.tolist()
+        tot = torch.tensor([st.batch], dtype=torch.int64, device=dev)
+        dist.all_reduce(tot)
+        total_requests = int(tot.item())
+    else:
+        total_requests = st.batch
+
+    if rank == 0:
+        ms_per_step = elapsed_ms / args.steps
+        value = total_requests / (ms_per_step / 1e3)
+        peak, peak_kind = peaks()
+        alg = st.algorithmic_bytes(args.warmup + args.steps // 2)
+        achieved = alg / (decode_ms / 1e3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "e4m3 KV, bf16 q/out, f32 accumulate" if st.fp8 else "bf16",
+            "data": "synthetic", "config": workload_config(shape, st.batch, args, chunk),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
+                         "kernel": "paged decode (+combine)", "algorithmic_bytes_per_launch": alg,
+                         "avg_launch_ms": decode_ms},
+            "e2e": {"value": total_requests / (e2e_ms / args.steps / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps * 3,
+            "clocks": clocks.summary(),
+            "device_status": status,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(shape, st.lengths, min(args.cpu_sample, st.batch), repeats=3)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
