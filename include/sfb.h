@@ -144,6 +144,35 @@ SFB_API int sfb_paged_attention_decode(const SFBTensor* q, const SFBTensor* k_ca
  * be NULL) receives the SFB_STATUS_* mask. */
 SFB_API int sfb_read_status(const void* workspace, int32_t* bits, void* stream);
 
+/* ── Decode without a caller workspace ───────────────────────────────────────
+ * No counterpart in the reference: this entry point exists only for hosts that
+ * cannot allocate device memory at the point of the call - a runtime whose KV
+ * block pool already owns all free HBM, or a dlopen-style host with no
+ * allocator binding.  Same arguments and results as sfb_paged_attention_decode,
+ * but the split-K partials and the status word live in a fixed device array
+ * inside the library (SFB_STATIC_SCRATCH_BYTES per GPU, resident from the
+ * moment the library's image is loaded on that GPU until the process exits).
+ *
+ *   - Allocates nothing: no cudaMalloc / cudaFree, no allocating library call.
+ *   - A call whose split needs more than SFB_STATIC_SCRATCH_BYTES
+ *     (sfb_paged_attention_workspace_bytes tells) fails with SFB_ERR_WORKSPACE;
+ *     raise chunk_tokens or use the workspace form.
+ *   - The first call on each device looks up the array's device address (with
+ *     that device current); make that first call outside any stream capture.
+ *   - All calls on a GPU share the one array and it keeps the previous call's
+ *     contents.  The status word is cleared by every call; everything else is
+ *     overwritten before it is read.  Two calls that can overlap on the GPU
+ *     (different streams without ordering) race on it: serialise them.
+ * sfb_read_status_static reads that array's status word like sfb_read_status. */
+#define SFB_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
+
+SFB_API int sfb_paged_attention_decode_static(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
+                                              const SFBTensor* k_scale, const SFBTensor* v_scale,
+                                              const SFBTensor* block_tables, const SFBTensor* seq_lens,
+                                              SFBTensor* out, int q_dtype, int kv_dtype, float scale,
+                                              int64_t chunk_tokens, void* stream);
+SFB_API int sfb_read_status_static(int32_t* bits, void* stream);
+
 /* ── KV cache write / FP8 quantise-on-append ───────────────────────────────
  * Replaces CacheManager.write_paged (python_runtime/engine/cache_manager.py:139-171;
  * Rust twin BlockManager::write_kv, runtime/src/cache/block.rs:348-403) for the
