@@ -135,3 +135,97 @@ def test_hal_backend_dense_and_dict_forms(cuda):
     assert torch.equal(stack_outputs(as_dict, rids), as_dense)
     want = torch.from_numpy(golden("paged_decode_c1.npz")["out"])
     assert_f32_close(as_dense.cpu(), want)
+
+
+def _random_case(seed, batch, heads, kv_heads, dim, max_len, dtype, layers=None):
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(1, max_len + 1, (batch,), generator=g).tolist()
+    lens[0] = max_len  # at least one request of full length
+    if batch > 1:
+        lens[1] = 1
+    nb = sum(-(-n // 16) for n in lens) + 3
+    tables = wl.random_tables(lens, nb, seed=seed + 1)
+    q = torch.randn((batch, heads, dim), generator=g).to(dtype)
+    shape = (nb, 16, kv_heads, dim) if layers is None else (nb, layers, 16, kv_heads, dim)
+    k = torch.randn(shape, generator=g).to(dtype)
+    v = torch.randn(shape, generator=g).to(dtype)
+    return q, k, v, tables, {r: n for r, n in zip(tables, lens)}
+
+
+@pytest.mark.parametrize("dtype,dim", [(torch.bfloat16, 64), (torch.bfloat16, 128), (torch.float16, 64), (torch.float16, 128)])
+@pytest.mark.parametrize("heads,kv_heads", [(8, 8), (32, 4), (16, 2), (8, 1), (32, 16), (6, 2), (5, 1)])
+def test_tensor_core_path_shapes(cuda, dtype, dim, heads, kv_heads):
+    """Shapes the TMA + tensor-core kernel covers (128- and 256-byte rows, 1..8 query
+    heads per kv head, every head-group layout), single pass and split."""
+    q, k, v, tables, lens = _random_case(100 + heads + dim, 5, heads, kv_heads, dim, 200, dtype)
+    want = ref.paged_attention_f64(q, k, v, tables, lens)
+    rids = list(tables)
+    for chunk in (0, 48):
+        out = pkg.paged_attention(q.to(cuda), k.to(cuda), v.to(cuda), tables, lens, chunk_tokens=chunk)
+        assert_half_close(stack_outputs(out, rids).cpu(), stack_outputs(want, rids), what=f"{dtype} D{dim} H{heads}/{kv_heads} chunk {chunk}")
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim", [(32, 8, 128), (64, 8, 128), (8, 1, 128), (16, 4, 256), (12, 2, 128)])
+@pytest.mark.parametrize("qdtype", [torch.bfloat16, torch.float16])
+def test_tensor_core_path_fp8(cuda, heads, kv_heads, dim, qdtype):
+    q, k, v, tables, lens = _random_case(300 + heads + dim, 6, heads, kv_heads, dim, 300, torch.bfloat16)
+    k, v = k * 2, v * 2
+    k[3] *= 50.0  # blocks with very different scales exercise the scale-in-exponent path
+    v[5] *= 0.001
+    v[7] *= 300.0
+    kc, ks = ref.fp8_quantize_pool_fast(k)
+    vc, vs = ref.fp8_quantize_pool_fast(v)
+    kd, vd = ref.fp8_dequantize_pool(kc, ks), ref.fp8_dequantize_pool(vc, vs)
+    q = q.to(qdtype)
+    want = ref.paged_attention_f64(q, kd, vd, tables, lens)
+    want32 = ref.paged_attention(q.float(), kd, vd, tables, lens)  # the reference's own arithmetic
+    rids = list(tables)
+    for chunk in (0, 64):
+        out = pkg.paged_attention(q.to(cuda), kc.to(cuda), vc.to(cuda), tables, lens, k_scale=ks.to(cuda), v_scale=vs.to(cuda),
+                                  chunk_tokens=chunk)
+        got = stack_outputs(out, rids).cpu()
+        # 2e-2 absolute for O(1) rows; a row dominated by the 300x block is O(1000), where the
+        # 16-bit output grid and the 16-bit probability operand are coarser in absolute terms:
+        # allow 2^-8 of the row's largest magnitude on top
+        w64 = stack_outputs(want, rids)
+        tol = 2e-2 + 2.0 ** -8 * w64.abs().amax(dim=-1, keepdim=True)
+        assert ((got.double() - w64).abs() <= tol).all()
+        assert ((got.double() - stack_outputs(want32, rids).double()).abs() <= tol).all()
+        from helpers import cos_deficit
+        assert cos_deficit(got, stack_outputs(want, rids)) <= 1e-4
+
+
+def test_tensor_core_path_strided_slab_and_bad_block(cuda):
+    q, k, v, tables, lens = _random_case(7, 4, 16, 4, 64, 150, torch.bfloat16, layers=2)
+    dk, dv = k.to(cuda), v.to(cuda)
+    rids = list(tables)
+    for layer in range(2):
+        want = ref.paged_attention_f64(q, k[:, layer], v[:, layer], tables, lens)
+        out = pkg.paged_attention(q.to(cuda), dk[:, layer], dv[:, layer], tables, lens)
+        assert_half_close(stack_outputs(out, rids).cpu(), stack_outputs(want, rids), what=f"slab layer {layer}")
+    # out-of-pool block id: skipped and flagged, the kernel keeps running
+    dense, ll, _ = dense_block_tables(tables, lens, 16)
+    dense = dense.clone()
+    dense[0, 1] = 10_000
+    ws = torch.zeros(ops.decode_workspace_bytes(4, 16, 64, dense.shape[1], 16, 32), dtype=torch.uint8, device=cuda)
+    out = ops.paged_attention_decode(q.to(cuda), dk[:, 0], dv[:, 0], dense.to(cuda), ll.to(cuda), chunk_tokens=32, workspace=ws)
+    assert ops.read_status(ws) == 1
+    assert torch.isfinite(out.float()).all()
+    want = ref.paged_attention_f64(q, k[:, 0], v[:, 0], tables, lens)
+    assert_half_close(out[1:].cpu(), stack_outputs(want, rids)[1:], what="rows without the bad block")
+
+
+def test_stale_slots_past_length_are_ignored(cuda):
+    """Slots after a request's last token may hold anything (NaN bit patterns
+    included); they must not leak into the result."""
+    q, k, v, tables, lens = _random_case(9, 3, 8, 2, 64, 90, torch.bfloat16)
+    want = ref.paged_attention_f64(q, k, v, tables, lens)
+    k2, v2 = k.clone(), v.clone()
+    for r, n in lens.items():
+        last = tables[r][(n - 1) // 16]
+        if n % 16:
+            k2[last, n % 16 :] = float("nan")
+            v2[last, n % 16 :] = float("nan")
+    out = pkg.paged_attention(q.to(cuda), k2.to(cuda), v2.to(cuda), tables, lens)
+    rids = list(tables)
+    assert_half_close(stack_outputs(out, rids).cpu(), stack_outputs(want, rids), what="stale slots")
