@@ -200,6 +200,34 @@ SFB_API int sfb_cache_write(const SFBTensor* k_new, const SFBTensor* v_new, cons
                     SFBTensor* v_cache, SFBTensor* k_scale, SFBTensor* v_scale, SFBTensor* k_tail,
                     SFBTensor* v_tail, int src_dtype, int kv_dtype, int64_t max_new_tokens, void* stream);
 
+/* ── Chunked prefill over the paged pool ────────────────────────────────────
+ * Replaces kernels/flash_attention.py:179-202 `flash_attention_fwd` (CPU path
+ * :28-46, dense causal SDPA) for the serving case the reference only sketches:
+ * a chunk of new tokens attending causally to prefix + chunk, with K/V read
+ * through the block table (kernels/paged_attention.py:36-48) so that a radix
+ * prefix shared by several requests is the same physical blocks in every table
+ * (runtime/src/cache/block.rs:214-232).  The chunk's own K/V must already be in
+ * the pool (sfb_cache_write first).
+ *
+ *   q, out       [T, H, D]   dtype; chunks packed request after request
+ *   cu_q         [R+1] int32 request r owns rows cu_q[r] .. cu_q[r+1]-1
+ *   ctx_lens     [R] int32   cached tokens of request r including this chunk;
+ *                            query i of the chunk sits at ctx_len - n_q + i and
+ *                            sees positions 0 .. its own (causal != 0); with
+ *                            causal == 0 every query sees all ctx_len tokens
+ *   block_tables [R, max_blocks] int32
+ *   k_cache, v_cache [NB, bs, Hkv, D] dtype (same as q)
+ *
+ * BF16 / F16 with D = 128 and bs = 16 run on the tcgen05 kernel; every other
+ * shape takes the decode kernels with one row per query token.  `workspace`
+ * (sfb_prefill_workspace_bytes) holds the status word and, for that second
+ * route, 8 bytes per query token.  max_q_tokens >= the longest chunk. */
+SFB_API int64_t sfb_prefill_workspace_bytes(int64_t total_q_tokens);
+SFB_API int sfb_prefill_paged(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
+                              const SFBTensor* block_tables, const SFBTensor* cu_q, const SFBTensor* ctx_lens,
+                              SFBTensor* out, int dtype, float scale, int causal, int64_t max_q_tokens,
+                              void* workspace, int64_t workspace_bytes, void* stream);
+
 /* ── FP8 quantise / dequantise ──────────────────────────────────────────────
  * Replaces FP8KVCacheQuantizer.quantize_block / dequantize_block
  * (compiler/quantize/fp8_kv_cache.py:66-105); HAL op names `quantize` /

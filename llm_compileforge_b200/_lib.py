@@ -118,7 +118,9 @@ def _optional(lib: ctypes.CDLL) -> None:
     """Prototypes of entry points added after ABI version 1's first set."""
     if hasattr(lib, "sfb_prefill_paged"):
         lib.sfb_prefill_paged.restype = c_int
-        lib.sfb_prefill_paged.argtypes = [_T] * 7 + [c_int, c_float, c_int64, c_void_p]
+        lib.sfb_prefill_paged.argtypes = [_T] * 7 + [c_int, c_float, c_int, c_int64, c_void_p, c_int64, c_void_p]
+        lib.sfb_prefill_workspace_bytes.restype = c_int64
+        lib.sfb_prefill_workspace_bytes.argtypes = [c_int64]
 
 
 def dtype_code(dtype: torch.dtype) -> int:

@@ -166,6 +166,83 @@ int sfb_paged_attention_decode(const SFBTensor* q, const SFBTensor* k_cache, con
     return launch_decode_combine(a, st);
 }
 
+int64_t sfb_prefill_workspace_bytes(int64_t total_q_tokens) {
+    if (total_q_tokens < 0) return SFB_ERR_INVALID_ARG;
+    return kWorkspaceHeader + ceil_div(total_q_tokens * 8, 256) * 256;
+}
+
+int sfb_prefill_paged(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache, const SFBTensor* block_tables,
+                      const SFBTensor* cu_q, const SFBTensor* ctx_lens, SFBTensor* out, int dtype, float scale,
+                      int causal, int64_t max_q_tokens, void* workspace, int64_t workspace_bytes, void* stream) {
+    const int e = dtype_size(dtype);
+    if (!e || dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "prefill: dtype %d", dtype);
+    View vq, vk, vv, vt, vc, vl, vo;
+    int rc;
+    if ((rc = make_view(q, "q", 3, 3, e, &vq))) return rc;
+    if ((rc = make_view(out, "out", 3, 3, e, &vo))) return rc;
+    if ((rc = make_view(k_cache, "k_cache", 4, 4, e, &vk))) return rc;
+    if ((rc = make_view(v_cache, "v_cache", 4, 4, e, &vv))) return rc;
+    if ((rc = make_view(block_tables, "block_tables", 2, 2, 4, &vt))) return rc;
+    if ((rc = make_view(cu_q, "cu_q", 1, 1, 4, &vc))) return rc;
+    if ((rc = make_view(ctx_lens, "ctx_lens", 1, 1, 4, &vl))) return rc;
+    const int64_t T = vq.size[1], H = vq.size[2], D = vq.size[3], R = vl.size[3];
+    const int64_t NB = vk.size[0], bs = vk.size[1], Hkv = vk.size[2];
+    if (vc.size[3] != R + 1 || vt.size[2] != R) return fail(SFB_ERR_INVALID_ARG, "prefill: cu_q needs R+1 and block_tables R rows (R = %lld)", (long long)R);
+    if (vk.size[3] != D || vv.size[3] != D) return fail(SFB_ERR_INVALID_ARG, "prefill: head_dim of q and pools differ");
+    for (int i = 0; i < 4; ++i)
+        if (vk.size[i] != vv.size[i]) return fail(SFB_ERR_INVALID_ARG, "prefill: k_cache and v_cache shapes differ");
+    if (vo.size[1] != T || vo.size[2] != H || vo.size[3] != D) return fail(SFB_ERR_INVALID_ARG, "prefill: out shape differs from q");
+    if (Hkv <= 0 || H % Hkv) return fail(SFB_ERR_INVALID_ARG, "prefill: query heads not a multiple of kv heads");
+    if ((D * e) % 16 || !aligned16(vk, 0) || !aligned16(vv, 0)) return fail(SFB_ERR_UNSUPPORTED, "prefill: pools must be 16-byte aligned");
+    if (T == 0 || R == 0 || max_q_tokens <= 0) return SFB_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (workspace && workspace_bytes < kWorkspaceHeader) workspace = nullptr;
+    if (workspace) SFB_CUDA_CHECK(cudaMemsetAsync(workspace, 0, 4, st));
+    const float sc = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
+
+    PrefillLaunch p{};
+    p.q = vq.base; p.k = vk.base; p.v = vv.base; p.out = vo.base;
+    p.cu_q = reinterpret_cast<const int32_t*>(vc.base);
+    p.ctx_lens = reinterpret_cast<const int32_t*>(vl.base);
+    p.tables = reinterpret_cast<const int32_t*>(vt.base);
+    p.table_stride = vt.stride[2]; p.max_blocks = (int)vt.size[3]; p.block_size = (int)bs; p.head_dim = (int)D;
+    p.n_requests = (int)R; p.n_heads = (int)H; p.n_kv_heads = (int)Hkv; p.n_pool_blocks = NB;
+    p.total_q = T; p.max_q_tokens = max_q_tokens;
+    p.q_stride[0] = vq.stride[1]; p.q_stride[1] = vq.stride[2];
+    p.out_stride[0] = vo.stride[1]; p.out_stride[1] = vo.stride[2];
+    for (int i = 0; i < 3; ++i) { p.k_stride[i] = vk.stride[i]; p.v_stride[i] = vv.stride[i]; }
+    p.scale = sc; p.dtype = dtype; p.causal = causal != 0; p.status = static_cast<int*>(workspace);
+    const bool q_tma_ok = reinterpret_cast<uintptr_t>(vq.base) % 16 == 0 && (vq.stride[1] * e) % 16 == 0 && (vq.stride[2] * e) % 16 == 0;
+    rc = q_tma_ok ? launch_prefill_tcgen05(p, st) : SFB_ERR_UNSUPPORTED;
+    if (rc != SFB_ERR_UNSUPPORTED) return rc;
+
+    // every other shape: one decode row per query token, single pass over its whole context
+    const int64_t need = sfb_prefill_workspace_bytes(T);
+    if (!workspace || workspace_bytes < need)
+        return fail(SFB_ERR_WORKSPACE, "prefill: workspace of %lld B needed for this shape, %lld given", (long long)need,
+                    (long long)(workspace ? workspace_bytes : 0));
+    int32_t* rows = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + kWorkspaceHeader);
+    int32_t* lens = rows + T;
+    if ((rc = launch_prefill_expand(p.cu_q, p.ctx_lens, (int)R, T, p.max_blocks, (int)bs, causal != 0, rows, lens, st))) return rc;
+    DecodeArgs a{};
+    a.q = vq.base; a.k = vk.base; a.v = vv.base; a.out = vo.base;
+    a.tables = p.tables; a.table_rows = rows; a.seq_lens = lens;
+    a.q_dtype = dtype; a.kv_dtype = dtype;
+    a.batch = (int)T; a.n_heads = (int)H; a.n_kv_heads = (int)Hkv; a.head_dim = (int)D;
+    a.block_size = (int)bs; a.max_blocks = p.max_blocks; a.n_pool_blocks = NB;
+    a.q_stride[0] = vq.stride[1]; a.q_stride[1] = vq.stride[2];
+    a.out_stride[0] = vo.stride[1]; a.out_stride[1] = vo.stride[2];
+    for (int i = 0; i < 3; ++i) { a.k_stride[i] = vk.stride[i]; a.v_stride[i] = vv.stride[i]; }
+    a.table_stride = vt.stride[2];
+    a.scale = sc;
+    a.split = decode_split(T, H, D, p.max_blocks, bs, (int64_t)p.max_blocks * bs);  // one chunk: no partials
+    a.workspace = static_cast<char*>(workspace);
+    if (T > 65535) return fail(SFB_ERR_UNSUPPORTED, "prefill: %lld query tokens exceed the generic route's limit 65535", (long long)T);
+    rc = launch_decode_tma(a, st);
+    if (rc == SFB_ERR_UNSUPPORTED) rc = launch_decode_generic(a, st);
+    return rc;
+}
+
 int sfb_read_status(const void* workspace, int32_t* bits, void* stream) {
     if (!workspace) return fail(SFB_ERR_INVALID_ARG, "read_status: workspace is NULL");
     int32_t host = 0;

@@ -38,7 +38,30 @@ __global__ void decode_combine_kernel(DecodeArgs a) {
     }
 }
 
+// Packed prefill tokens -> one decode row each: token i of request r sits at position
+// ctx_len - n_q + i and attends to position + 1 tokens through request r's table row.
+__global__ void prefill_expand_kernel(const int32_t* cu_q, const int32_t* ctx_lens, int n_requests, int max_tokens_cap, int causal,
+                                      int32_t* rows_out, int32_t* lens_out) {
+    const int req = blockIdx.y;
+    const int begin = cu_q[req], n_q = cu_q[req + 1] - begin;
+    int ctx = ctx_lens[req];
+    if (ctx > max_tokens_cap) ctx = max_tokens_cap;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_q; i += gridDim.x * blockDim.x) {
+        rows_out[begin + i] = req;
+        lens_out[begin + i] = causal ? ctx - n_q + i + 1 : ctx;  // <= 0 (inconsistent request) is flagged by the decode kernel
+    }
+}
+
 }  // namespace
+
+int launch_prefill_expand(const int32_t* cu_q, const int32_t* ctx_lens, int n_requests, int64_t total_q, int max_blocks,
+                          int block_size, int causal, int32_t* rows_out, int32_t* lens_out, cudaStream_t stream) {
+    (void)total_q;
+    dim3 grid(8, (unsigned)n_requests);
+    prefill_expand_kernel<<<grid, 256, 0, stream>>>(cu_q, ctx_lens, n_requests, max_blocks * block_size, causal, rows_out, lens_out);
+    SFB_CUDA_CHECK(cudaGetLastError());
+    return SFB_OK;
+}
 
 int launch_decode_generic(const DecodeArgs& a, cudaStream_t stream) {
     const int group = a.n_heads / a.n_kv_heads;

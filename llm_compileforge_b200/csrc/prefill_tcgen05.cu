@@ -1,0 +1,520 @@
+// Chunked-prefill attention over the paged KV pool on the 5th-generation tensor
+// cores (tcgen05 MMA, accumulators in tensor memory, operands fed by TMA).
+//
+// Semantics restated from kernels/flash_attention.py:35-46 of the reference
+// (dense causal softmax(Q K^T scale) V): the queries of a request's chunk sit at
+// positions ctx_len - n_q .. ctx_len - 1 and see every cached token up to their
+// own position; K/V come from the request's block table exactly like
+// kernels/paged_attention.py:36-48, so a radix-shared prefix is simply the same
+// physical blocks at the head of several tables.  GQA: query head h reads kv
+// head h / (H / Hkv).
+//
+// One thread block = 128 query tokens of one (request, query head):
+//   warp 4    TMA producer: Q tile once, then per 128-token KV tile sixteen
+//             [16 tokens x 128 B] boxes for K and sixteen for V, two stages each
+//   warp 5    issues tcgen05.mma: S = Q K^T (128x128x128, both operands K-major
+//             in 128B-swizzled shared memory) into one of two S buffers in
+//             tensor memory, then O += P V with P read from tensor memory and V
+//             as an MN-major shared-memory operand
+//   warps 0-3 one thread per query row: tcgen05.ld the S row, running max /
+//             sum in log2 units, P written back to tensor memory as bf16/fp16,
+//             O rescaled in tensor memory only when the max grew by more than
+//             2^8 (the stale max stays exact in fp32), final O / l written out
+// Tensor memory: S0, S1 (128 columns each), O (128), P0, P1 (64 each) = 512.
+// Bound: tensor pipe (4*D*Sq*Skv flops per head against ~1.4 PFLOP/s dense).
+
+#include <cuda.h>
+
+#include <mutex>
+
+#include "sfb_common.cuh"
+
+namespace sfb {
+namespace {
+
+constexpr int kTileQ = 128;
+constexpr int kTileKV = 128;
+constexpr int kHeadDim = 128;
+constexpr int kSubBytes = kTileKV * 128;     // one [128 rows][128 B] swizzled sub-tile
+constexpr int kTileBytes = 2 * kSubBytes;    // D = 128 16-bit values = two sub-tiles
+constexpr int kThreads = 192;
+constexpr uint32_t kSpin = 1u << 24;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f;    // log2 units
+
+struct PrefillArgs {
+    const void* q;
+    void* out;
+    const int32_t* cu_q;      // [R+1] packed query offsets
+    const int32_t* ctx_lens;  // [R]   tokens cached after this chunk was written
+    const int32_t* tables;
+    int64_t table_stride;
+    int max_blocks;
+    int n_requests, n_heads, n_kv_heads;
+    int64_t n_pool_blocks;
+    int64_t out_stride[2];  // token, head (elements)
+    float scale;
+    int bf16;               // 1 = bfloat16, 0 = float16
+    int causal;             // 0: every query sees all ctx_len tokens
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpin; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst), "l"(map), "r"(0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(dst), "l"(map), "r"(0), "r"(0), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
+        : "memory");
+}
+
+// ---- tensor memory and tcgen05 ------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem desc] . B[smem desc]
+__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] . B[smem desc]
+__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+        ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+        "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+        "%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+          "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+          "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    uint32_t r;
+    if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading and
+// stride byte offsets in 16-byte units, version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fff);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor for kind::f16: fp32 accumulate, 16-bit A/B, M x N tile.
+__host__ __device__ constexpr uint32_t instr_desc(bool bf16, bool b_mn_major, int m, int n) {
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// barrier slots
+enum {
+    B_Q_FULL = 0,
+    B_K_FULL = 1,    // +stage
+    B_K_EMPTY = 3,   // +stage
+    B_V_FULL = 5,    // +stage
+    B_V_EMPTY = 7,   // +stage
+    B_S_FULL = 9,    // +buffer
+    B_S_EMPTY = 11,  // +buffer
+    B_P_FULL = 13,   // +buffer
+    B_PV_DONE = 15,  // +buffer
+    B_COUNT = 17
+};
+constexpr int kSmemBytes = 5 * kTileBytes + B_COUNT * 8 + 16 + 1024;
+
+// tensor-memory columns
+constexpr uint32_t kColS = 0;    // S0 at 0, S1 at 128
+constexpr uint32_t kColO = 256;  // O
+constexpr uint32_t kColP = 384;  // P0 at 384, P1 at 448 (16-bit pairs)
+
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                       const __grid_constant__ CUtensorMap vmap, const PrefillArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const int req = blockIdx.z, head = blockIdx.y;
+    const int q_begin = a.cu_q[req], n_q = a.cu_q[req + 1] - q_begin;
+    // heaviest tiles (latest queries) first
+    const int q_tiles = (n_q + kTileQ - 1) / kTileQ;
+    const int qt = q_tiles - 1 - (int)blockIdx.x;
+    if (qt < 0) return;
+    int ctx = a.ctx_lens[req];
+    if (ctx > a.max_blocks * 16) ctx = a.max_blocks * 16;
+    if (ctx < n_q || n_q <= 0) {  // inconsistent request: flag it, write nothing
+        if (a.status && threadIdx.x == 0) atomicOr(a.status, SFB_STATUS_EMPTY_REQUEST);
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q0 = qt * kTileQ;
+    const int rows = min(kTileQ, n_q - q0);
+    const int pos0 = ctx - n_q + q0;                 // position of the tile's first query
+    const int n_tiles = (a.causal ? pos0 + rows - 1 : ctx - 1) / kTileKV + 1;
+    const int used_blocks = (ctx + 15) >> 4;
+    const int group = a.n_heads / a.n_kv_heads;
+    const int kvh = head / group;
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t q_s = base, k_s = base + kTileBytes, v_s = base + 3 * kTileBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + 5 * kTileBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(B_Q_FULL), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar(B_K_FULL + s), 1);
+            mbar_init(bar(B_K_EMPTY + s), 1);
+            mbar_init(bar(B_V_FULL + s), 1);
+            mbar_init(bar(B_V_EMPTY + s), 1);
+            mbar_init(bar(B_S_FULL + s), 1);
+            mbar_init(bar(B_S_EMPTY + s), 4);
+            mbar_init(bar(B_P_FULL + s), 4);
+            mbar_init(bar(B_PV_DONE + s), 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 5) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    bool timed_out = false;
+
+    if (warp == 4) {
+        // ============================ TMA producer ============================
+        if (lane == 0) {
+            mbar_expect_tx(bar(B_Q_FULL), kTileBytes);
+            tma_load_4d(q_s, &qmap, bar(B_Q_FULL), q_begin + q0, 0, head);
+            tma_load_4d(q_s + kSubBytes, &qmap, bar(B_Q_FULL), q_begin + q0, 1, head);
+        }
+        const int blk = (lane & 15) >> 1, sub = lane & 1;
+        const int32_t* table = a.tables + (int64_t)req * a.table_stride;
+        auto lookup = [&](int tile) -> int {
+            const int e = tile * 8 + blk;
+            if (tile >= n_tiles || e >= used_blocks) return (int)a.n_pool_blocks;  // out of range -> zero fill
+            const int64_t p = table[e];
+            if (p < 0 || p >= a.n_pool_blocks) {
+                if (a.status) atomicOr(a.status, SFB_STATUS_BAD_BLOCK_ID);
+                return (int)a.n_pool_blocks;
+            }
+            return (int)p;
+        };
+        int phys = lookup(0);
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j & 1;
+            const uint32_t par = ((j >> 1) & 1) ^ 1;
+            const int next_phys = lookup(j + 1);  // in flight while this tile's copies are issued
+            const uint32_t dst_off = sub * kSubBytes + blk * 2048;
+            if (!mbar_wait(bar(B_K_EMPTY + s), par)) { timed_out = true; break; }
+            if (lane == 0) mbar_expect_tx(bar(B_K_FULL + s), kTileBytes);
+            __syncwarp();
+            if (lane < 16) tma_load_5d(k_s + s * kTileBytes + dst_off, &kmap, bar(B_K_FULL + s), sub, kvh, phys);
+            if (!mbar_wait(bar(B_V_EMPTY + s), par)) { timed_out = true; break; }
+            if (lane == 16) mbar_expect_tx(bar(B_V_FULL + s), kTileBytes);
+            __syncwarp();
+            if (lane >= 16) tma_load_5d(v_s + s * kTileBytes + dst_off, &vmap, bar(B_V_FULL + s), sub, kvh, phys);
+            phys = next_phys;
+        }
+    } else if (warp == 5) {
+        // ============================ MMA issuer ==============================
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = instr_desc(BF16, false, kTileQ, kTileKV);
+            constexpr uint32_t idesc_pv = instr_desc(BF16, true, kTileQ, kHeadDim);
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j & 1;
+                if (!mbar_wait(bar(B_K_FULL + s), (j >> 1) & 1)) return false;
+                if (j >= 2 && !mbar_wait(bar(B_S_EMPTY + s), ((j - 2) >> 1) & 1)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {  // 16 head-dim values per instruction
+                    const uint32_t off = (ks >> 2) * kSubBytes + (ks & 3) * 32;
+                    mma_ss(tmem + kColS + s * 128, smem_desc(q_s + off, 16, 1024), smem_desc(k_s + s * kTileBytes + off, 16, 1024),
+                           idesc_qk, ks > 0);
+                }
+                tc_commit(bar(B_S_FULL + s));
+                tc_commit(bar(B_K_EMPTY + s));
+                return true;
+            };
+            auto issue_pv = [&](int j) -> bool {
+                const int s = j & 1;
+                if (!mbar_wait(bar(B_V_FULL + s), (j >> 1) & 1)) return false;
+                if (!mbar_wait(bar(B_P_FULL + s), (j >> 1) & 1)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)  // 16 KV tokens per instruction
+                    mma_ts(tmem + kColO, tmem + kColP + s * 64 + ks * 8,
+                           smem_desc(v_s + s * kTileBytes + ks * 2048, kSubBytes, 1024), idesc_pv, (j > 0 || ks > 0));
+                tc_commit(bar(B_PV_DONE + s));
+                tc_commit(bar(B_V_EMPTY + s));
+                return true;
+            };
+            bool ok = mbar_wait(bar(B_Q_FULL), 0);
+            ok = ok && issue_qk(0);
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+                ok = ok && issue_pv(j);
+            }
+            timed_out = !ok;
+        }
+    } else {
+        // ======================= softmax / correction / epilogue ==============
+        const int row = threadIdx.x;  // 0..127 = tensor-memory lane
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        const bool row_valid = row < rows;
+        const int pos = (row_valid && a.causal) ? pos0 + row : ctx - 1;  // padding rows attend to everything; never written
+        const float sl2 = a.scale * kLog2e;
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int b = j & 1;
+            if (!mbar_wait(bar(B_S_FULL + b), (j >> 1) & 1)) { ok = false; break; }
+            tc_fence_after();
+            const int kv0 = j * kTileKV;
+            const bool full = kv0 + kTileKV - 1 <= pos;  // no masking needed for this row
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ++ch) {
+                float v[32];
+                tmem_ld32(lane_base + kColS + b * 128 + ch * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (full || kv0 + ch * 32 + i <= pos) mx = fmaxf(mx, v[i]);
+            }
+            const float m_new = fmaxf(m_used, mx * sl2);
+            if (j == 0) {
+                m_used = m_new;
+            } else {
+                const bool need = m_new > m_used + kRescaleThreshold;
+                if (__any_sync(0xffffffffu, need)) {
+                    // O is only touched between PV products: wait for the previous one
+                    if (!mbar_wait(bar(B_PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    const float f = need ? fast_exp2(m_used - m_new) : 1.f;
+                    l *= f;
+                    if (need) m_used = m_new;
+#pragma unroll 1
+                    for (int ch = 0; ch < 4; ++ch) {
+                        float o[32];
+                        tmem_ld32(lane_base + kColO + ch * 32, o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] *= f;
+                        tmem_st32(lane_base + kColO + ch * 32, o);
+                    }
+                    tmem_wait_st();
+                }
+            }
+            // P[b] was last read by the PV product of tile j-2
+            if (j >= 2 && !mbar_wait(bar(B_PV_DONE + b), ((j - 2) >> 1) & 1)) { ok = false; break; }
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ++ch) {
+                float v[32];
+                tmem_ld32(lane_base + kColS + b * 128 + ch * 32, v);
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int c = kv0 + ch * 32 + 2 * i;
+                    float p0 = fast_exp2(fmaf(v[2 * i], sl2, -m_used));
+                    float p1 = fast_exp2(fmaf(v[2 * i + 1], sl2, -m_used));
+                    if (!full) {
+                        if (c > pos) p0 = 0.f;
+                        if (c + 1 > pos) p1 = 0.f;
+                    }
+                    l += p0 + p1;
+                    pk[i] = pack2<BF16>(p0, p1);
+                }
+                tmem_st16(lane_base + kColP + b * 64 + ch * 16, pk);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar(B_P_FULL + b));
+                mbar_arrive(bar(B_S_EMPTY + b));
+            }
+        }
+        // ---- epilogue: O / l
+        if (ok) ok = mbar_wait(bar(B_PV_DONE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1);
+        if (ok) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(q_begin + q0 + row) * a.out_stride[0] +
+                            (int64_t)head * a.out_stride[1];
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ++ch) {
+                float o[32];
+                tmem_ld32(lane_base + kColO + ch * 32, o);
+                if (row_valid) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 w;
+                        w.x = pack2<BF16>(o[8 * i] * inv, o[8 * i + 1] * inv);
+                        w.y = pack2<BF16>(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
+                        w.z = pack2<BF16>(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
+                        w.w = pack2<BF16>(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
+                        *reinterpret_cast<uint4*>(dst + ch * 32 + i * 8) = w;
+                    }
+                }
+            }
+        }
+        timed_out = !ok;
+    }
+    if (timed_out && a.status && lane == 0) atomicOr(a.status, SFB_STATUS_WAIT_TIMEOUT);
+    // ---- teardown: every warp arrives here; tensor memory is released before exit
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static std::once_flag once;
+    static EncodeTiledFn fn = nullptr;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+bool encode(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint32_t es[5] = {1, 1, 1, 1, 1};
+    for (int i = 0; i < rank - 1; ++i)
+        if (strides[i] % 16 || strides[i] >= (1ull << 40)) return false;
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void*>(base), dims, strides, box, es,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+// Returns SFB_ERR_UNSUPPORTED when the shape is outside this kernel (the caller then takes the generic route).
+int launch_prefill_tcgen05(const PrefillLaunch& p, cudaStream_t stream) {
+    if (p.head_dim != kHeadDim || p.block_size != 16 || (p.dtype != SFB_BF16 && p.dtype != SFB_F16)) return SFB_ERR_UNSUPPORTED;
+    if (p.n_heads % p.n_kv_heads || p.n_requests > 65535 || p.n_heads > 65535) return SFB_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(p.out) % 16 || p.out_stride[0] % 8 || p.out_stride[1] % 8) return SFB_ERR_UNSUPPORTED;
+    CUtensorMap qmap, kmap, vmap;
+    {
+        cuuint64_t dims[4] = {128, (cuuint64_t)p.total_q, 2, (cuuint64_t)p.n_heads};
+        cuuint64_t strides[3] = {(cuuint64_t)p.q_stride[0] * 2, 128, (cuuint64_t)p.q_stride[1] * 2};
+        cuuint32_t box[4] = {128, (cuuint32_t)kTileQ, 1, 1};
+        if (!encode(&qmap, p.q, 4, dims, strides, box)) return SFB_ERR_UNSUPPORTED;
+    }
+    for (int which = 0; which < 2; ++which) {
+        const int64_t* st = which ? p.v_stride : p.k_stride;
+        cuuint64_t dims[5] = {128, 16, 2, (cuuint64_t)p.n_kv_heads, (cuuint64_t)p.n_pool_blocks};
+        cuuint64_t strides[4] = {(cuuint64_t)st[1] * 2, 128, (cuuint64_t)st[2] * 2, (cuuint64_t)st[0] * 2};
+        cuuint32_t box[5] = {128, 16, 1, 1, 1};
+        if (!encode(which ? &vmap : &kmap, which ? p.v : p.k, 5, dims, strides, box)) return SFB_ERR_UNSUPPORTED;
+    }
+    PrefillArgs a{};
+    a.q = p.q; a.out = p.out; a.cu_q = p.cu_q; a.ctx_lens = p.ctx_lens; a.tables = p.tables;
+    a.table_stride = p.table_stride; a.max_blocks = p.max_blocks; a.n_requests = p.n_requests;
+    a.n_heads = p.n_heads; a.n_kv_heads = p.n_kv_heads; a.n_pool_blocks = p.n_pool_blocks;
+    a.out_stride[0] = p.out_stride[0]; a.out_stride[1] = p.out_stride[1];
+    a.scale = p.scale; a.bf16 = p.dtype == SFB_BF16; a.causal = p.causal; a.status = p.status;
+    dim3 grid((unsigned)ceil_div(p.max_q_tokens, kTileQ), (unsigned)p.n_heads, (unsigned)p.n_requests);
+    static bool attr_set[2] = {false, false};
+    if (a.bf16) {
+        if (!attr_set[1]) { SFB_CUDA_CHECK(cudaFuncSetAttribute(prefill_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)); attr_set[1] = true; }
+        prefill_tcgen05_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(qmap, kmap, vmap, a);
+    } else {
+        if (!attr_set[0]) { SFB_CUDA_CHECK(cudaFuncSetAttribute(prefill_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)); attr_set[0] = true; }
+        prefill_tcgen05_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(qmap, kmap, vmap, a);
+    }
+    SFB_CUDA_CHECK(cudaGetLastError());
+    return SFB_OK;
+}
+
+}  // namespace sfb

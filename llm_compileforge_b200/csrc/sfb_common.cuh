@@ -151,6 +151,7 @@ struct DecodeArgs {
     const float* k_scale;
     const float* v_scale;
     const int32_t* tables;
+    const int32_t* table_rows;  // optional: query row r uses table row table_rows[r] (prefill tokens share a row)
     const int32_t* seq_lens;
     void* out;
     int q_dtype, kv_dtype;
@@ -206,6 +207,32 @@ int launch_cache_write(const AppendArgs& a, cudaStream_t stream);
 int launch_quantize(const View& x, const View& codes, const View& scales, int x_dtype, int granularity, cudaStream_t stream);
 int launch_dequantize(const View& codes, const View& scales, const View& out, int out_dtype, int granularity,
                       cudaStream_t stream);
+
+struct PrefillLaunch {
+    const void* q;
+    const void* k;
+    const void* v;
+    void* out;
+    const int32_t* cu_q;
+    const int32_t* ctx_lens;
+    const int32_t* tables;
+    int64_t table_stride;
+    int max_blocks, block_size, head_dim;
+    int n_requests, n_heads, n_kv_heads;
+    int64_t n_pool_blocks, total_q, max_q_tokens;
+    int64_t q_stride[2];    // token, head (elements)
+    int64_t out_stride[2];
+    int64_t k_stride[3];    // block, token, head
+    int64_t v_stride[3];
+    float scale;
+    int dtype;
+    int causal;
+    int* status;
+};
+int launch_prefill_tcgen05(const PrefillLaunch& p, cudaStream_t stream);
+// token r of the packed query batch -> (table row, attended length) for the decode-kernel route
+int launch_prefill_expand(const int32_t* cu_q, const int32_t* ctx_lens, int n_requests, int64_t total_q, int max_blocks,
+                          int block_size, int causal, int32_t* rows_out, int32_t* lens_out, cudaStream_t stream);
 
 struct NormArgs {
     const void* x;

@@ -64,6 +64,8 @@ class B200Backend(OpExecutor):
             "dequantize": self._op_dequantize,
             "rms_norm": self._op_rms_norm,
             "fused_rms_norm_add": self._op_fused_rms_norm_add,
+            "flash_attention": self._op_flash_attention,
+            "chunked_prefill": self._op_chunked_prefill,
         }
 
     def supported_ops(self) -> list[str]:
@@ -131,6 +133,20 @@ class B200Backend(OpExecutor):
 
     def _op_fused_rms_norm_add(self, inputs: list[Any], **kw: Any) -> torch.Tensor:
         return ops.rms_norm(inputs[0], inputs[2], eps=kw.get("eps", 1e-6), residual=inputs[1])
+
+
+    def _op_flash_attention(self, inputs: list[Any], **kw: Any) -> torch.Tensor:
+        """Dense attention ``[q, k, v]`` each ``[B,H,S,D]`` with the keywords of
+        kernels.flash_attention_fwd (``scale``, ``causal`` default True)."""
+        return kernels_api.flash_attention_fwd(inputs[0], inputs[1], inputs[2], scale=kw.get("scale"),
+                                               causal=kw.get("causal", kw.get("is_causal", True)))
+
+    def _op_chunked_prefill(self, inputs: list[Any], **kw: Any) -> torch.Tensor:
+        """inputs ``[query [T,H,D], key_cache, value_cache, block_table [R,max_blocks]]``
+        with keywords ``cu_q [R+1]``, ``ctx_lens [R]`` (int32, device) and ``max_q_tokens``."""
+        q, k_cache, v_cache, table = inputs[:4]
+        return ops.prefill_paged(q, k_cache, v_cache, table, kw["cu_q"], kw["ctx_lens"], max_q_tokens=int(kw["max_q_tokens"]),
+                                 scale=kw.get("scale"), causal=kw.get("causal", True), workspace=kw.get("workspace"))
 
 
 def register(name: str = "b200") -> None:

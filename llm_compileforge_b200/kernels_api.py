@@ -54,6 +54,75 @@ def paged_attention(
     return {rid: out[i] for i, rid in enumerate(rids)}
 
 
+def flash_attention_fwd(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float | None = None, causal: bool = True
+) -> torch.Tensor:
+    """FlashAttention forward (kernels/flash_attention.py:179-202): ``q, k, v``
+    ``[batch, heads, seq, head_dim]`` -> same shape; ``causal`` defaults to True,
+    ``scale`` to ``1/sqrt(head_dim)``.
+
+    The dense K/V are viewed as a paged pool with identity block tables (one copy
+    to token-major layout, zero padding to whole 16-token blocks) and run through
+    the chunked-prefill kernel; K/V may have fewer heads than Q (GQA).  As in the
+    reference's CPU path, ``causal=True`` needs equal query and key lengths."""
+    if q.dim() != 4 or k.shape != v.shape or k.shape[0] != q.shape[0] or k.shape[-1] != q.shape[-1]:
+        raise ValueError("flash_attention_fwd expects q [B,H,S,D] and k, v [B,Hkv,Skv,D]")
+    b, h, sq, d = q.shape
+    hkv, skv = k.shape[1], k.shape[2]
+    if causal and sq != skv:
+        raise ValueError("causal flash_attention_fwd needs equal query and key lengths")
+    bs = 16
+    nblk = -(-skv // bs)
+    dev = q.device
+
+    def pool(x: torch.Tensor) -> torch.Tensor:
+        t = x.permute(0, 2, 1, 3)  # [B, S, Hkv, D]
+        if nblk * bs != skv:
+            t = torch.nn.functional.pad(t, (0, 0, 0, 0, 0, nblk * bs - skv))
+        return t.contiguous().view(b * nblk, bs, hkv, d)
+
+    tables = torch.arange(b * nblk, dtype=torch.int32, device=dev).view(b, nblk)
+    cu_q = torch.arange(b + 1, dtype=torch.int32, device=dev) * sq
+    ctx = torch.full((b,), skv, dtype=torch.int32, device=dev)
+    q_tok = q.permute(0, 2, 1, 3).contiguous().view(b * sq, h, d)
+    out = ops.prefill_paged(q_tok, pool(k), pool(v), tables, cu_q, ctx, max_q_tokens=sq, scale=scale, causal=causal)
+    return out.view(b, sq, h, d).permute(0, 2, 1, 3).contiguous()
+
+
+def chunked_prefill(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_tables: Mapping[str, Sequence[int]],
+    ctx_lens: Mapping[str, int],
+    n_tokens: Mapping[str, int],
+    block_size: int = 16,
+    scale: float | None = None,
+) -> dict[str, torch.Tensor]:
+    """Causal attention of each request's newest ``n_tokens[rid]`` tokens over all
+    of its ``ctx_lens[rid]`` cached tokens (prefix + chunk), K/V through the block
+    tables.  ``q [T,H,D]`` packs the chunks in dict order (the scheduler's
+    ``ScheduledRequest.n_tokens`` / ``block_table``, runtime/src/engine/types.rs:85-94).
+    Returns ``{rid: [n_tokens, H, D]}``."""
+    if k_cache.shape[1] != block_size:
+        raise ValueError(f"k_cache block dimension {k_cache.shape[1]} != block_size {block_size}")
+    rids = list(block_tables)
+    lens = {r: ctx_lens[r] for r in rids}
+    dense, ll, _ = dense_block_tables(block_tables, lens, block_size, n_pool_blocks=k_cache.shape[0])
+    counts = [int(n_tokens[r]) for r in rids]
+    for r, n in zip(rids, counts):
+        if n <= 0 or n > min(int(ctx_lens[r]), len(block_tables[r]) * block_size):
+            raise ValueError(f"request {r!r}: chunk of {n} tokens does not fit its context")
+    cu = torch.zeros(len(rids) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(counts, dtype=torch.int32).cumsum(0)
+    if int(cu[-1]) != q.shape[0]:
+        raise ValueError(f"q has {q.shape[0]} rows, the chunks add up to {int(cu[-1])}")
+    dev = q.device
+    out = ops.prefill_paged(q, k_cache, v_cache, dense.to(dev, non_blocking=True), cu.to(dev), ll.to(dev, non_blocking=True),
+                            max_q_tokens=max(counts), scale=scale, causal=True)
+    return {r: out[int(cu[i]) : int(cu[i + 1])] for i, r in enumerate(rids)}
+
+
 def fused_rms_norm_add(
     input_tensor: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6
 ) -> torch.Tensor:

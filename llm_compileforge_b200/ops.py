@@ -185,3 +185,39 @@ def rms_norm(
     check(lib.sfb_rms_norm(desc(x2, "x"), desc(r2, "residual"), desc(w, "weight"), desc(o2, "out"),
                            dtype_code(x.dtype), float(eps), current_stream(x.device)))
     return o2.reshape(x.shape) if out is None else out
+
+
+def prefill_workspace_bytes(total_q_tokens: int) -> int:
+    return int(_lib.load().sfb_prefill_workspace_bytes(int(total_q_tokens)))
+
+
+def prefill_paged(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    cu_q: torch.Tensor,
+    ctx_lens: torch.Tensor,
+    *,
+    max_q_tokens: int,
+    scale: float | None = None,
+    causal: bool = True,
+    workspace: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Attention of packed query chunks ``q [T,H,D]`` over prefix + chunk read from
+    the paged pool.  Request ``r`` owns rows ``cu_q[r]:cu_q[r+1]``; its chunk ends
+    at cached position ``ctx_lens[r] - 1`` (the chunk's K/V are already in the pool)."""
+    lib = _lib.load()
+    if out is None:
+        out = torch.empty_like(q)
+    need = prefill_workspace_bytes(q.shape[0])
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    check(lib.sfb_prefill_paged(
+        desc(q, "q"), desc(k_cache, "k_cache"), desc(v_cache, "v_cache"), desc(block_tables, "block_tables"),
+        desc(cu_q, "cu_q"), desc(ctx_lens, "ctx_lens"), desc(out, "out"), dtype_code(q.dtype),
+        float(scale) if scale is not None else 0.0, 1 if causal else 0, int(max_q_tokens), workspace.data_ptr(),
+        workspace.numel() * workspace.element_size(), current_stream(q.device),
+    ))
+    return out
