@@ -1,0 +1,114 @@
+"""Collective plumbing for the multi-GPU partitions of the decode path.
+
+Attention needs no exchange step: requests are independent, and within a
+request the kv-head groups are independent.  The only collective is the
+all-gather that brings per-GPU outputs to every device when the caller wants
+them in one place.  ``TorchDistCommunicator`` implements the reference's
+5-member ``Communicator`` interface (python_runtime/hal/communicator.py:17-72:
+``all_reduce``, ``all_gather`` along the last dimension, ``broadcast``, ``rank``,
+``world_size``) over ``torch.distributed`` - NCCL on NVLink/NVSwitch for GPU
+tensors, Gloo for CPU tensors (the multi-rank tests).
+"""
+
+from __future__ import annotations
+
+from collections.abc import Sequence
+
+import torch
+import torch.distributed as dist
+
+try:
+    from python_runtime.hal.communicator import Communicator  # type: ignore
+except Exception:  # noqa: BLE001
+    from abc import ABC, abstractmethod
+
+    class Communicator(ABC):  # type: ignore[no-redef]
+        """Same contract as python_runtime/hal/communicator.py:17-72."""
+
+        @abstractmethod
+        def all_reduce(self, tensor: torch.Tensor, op: str = "sum") -> torch.Tensor: ...
+
+        @abstractmethod
+        def all_gather(self, tensor: torch.Tensor) -> torch.Tensor: ...
+
+        @abstractmethod
+        def broadcast(self, tensor: torch.Tensor, src: int) -> torch.Tensor: ...
+
+        @property
+        @abstractmethod
+        def rank(self) -> int: ...
+
+        @property
+        @abstractmethod
+        def world_size(self) -> int: ...
+
+
+_OPS = {"sum": dist.ReduceOp.SUM, "min": dist.ReduceOp.MIN, "max": dist.ReduceOp.MAX, "avg": dist.ReduceOp.SUM}
+
+
+class TorchDistCommunicator(Communicator):
+    """``Communicator`` over an initialised ``torch.distributed`` process group."""
+
+    def __init__(self, group: dist.ProcessGroup | None = None) -> None:
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+        self._group = group
+
+    @property
+    def rank(self) -> int:
+        return dist.get_rank(self._group)
+
+    @property
+    def world_size(self) -> int:
+        return dist.get_world_size(self._group)
+
+    def all_reduce(self, tensor: torch.Tensor, op: str = "sum") -> torch.Tensor:
+        if op not in _OPS:
+            raise ValueError(f"unknown reduction {op!r}")
+        out = tensor.clone()
+        dist.all_reduce(out, op=_OPS[op], group=self._group)
+        if op == "avg":
+            out = out / self.world_size
+        return out
+
+    def all_gather(self, tensor: torch.Tensor) -> torch.Tensor:
+        """Concatenation of every rank's tensor along the last dimension."""
+        return torch.cat(self._gather_parts(tensor.contiguous()), dim=-1)
+
+    def _gather_parts(self, t: torch.Tensor) -> list[torch.Tensor]:
+        parts = [torch.empty_like(t) for _ in range(self.world_size)]
+        dist.all_gather(parts, t, group=self._group)
+        return parts
+
+    def broadcast(self, tensor: torch.Tensor, src: int) -> torch.Tensor:
+        out = tensor.clone()
+        dist.broadcast(out, src=src, group=self._group)
+        return out
+
+    # ── decode-path helpers ──────────────────────────────────────────────────
+    def gather_requests(self, out_local: torch.Tensor, counts: Sequence[int]) -> torch.Tensor:
+        """Partition by request: rank ``g`` holds ``out_local [counts[g], H, D]`` for a
+        contiguous request range; returns ``[sum(counts), H, D]`` in request order on
+        every rank (rows are padded to the largest count for the collective)."""
+        width = max(counts)
+        padded = out_local.new_zeros((width,) + tuple(out_local.shape[1:]))
+        padded[: out_local.shape[0]] = out_local
+        parts = self._gather_parts(padded)
+        return torch.cat([parts[g][: counts[g]] for g in range(self.world_size)], dim=0)
+
+    def gather_heads(self, out_local: torch.Tensor) -> torch.Tensor:
+        """Partition by kv head: rank ``g`` holds ``out_local [B, H/G, D]`` for its
+        query-head slice; returns ``[B, H, D]`` (heads of rank 0 first)."""
+        b, hg, d = out_local.shape
+        flat = self.all_gather(out_local.reshape(b, hg * d))
+        return flat.view(b, self.world_size * hg, d)
+
+
+def kv_head_shard(t: torch.Tensor, rank: int, world_size: int, dim: int) -> torch.Tensor:
+    """View of rank ``rank``'s slice of a head axis (``k_cache[:, :, g]`` style
+    partition for the 8-GPU configuration: one kv head, or H/Hkv query heads, per GPU)."""
+    n = t.shape[dim]
+    if n % world_size:
+        raise ValueError(f"axis of {n} heads does not divide over {world_size} ranks")
+    per = n // world_size
+    return t.narrow(dim, rank * per, per)

@@ -1,0 +1,181 @@
+"""Per-kernel measurements for the hot path's other kernels (one JSON line each).
+
+    python -m llm_compileforge_b200.kernel_bench [--only prefill,append,norm,decode_c2,decode_c3] [--iters 20]
+
+``bench.py`` at the repository root reports the headline decode metric; this
+module times the remaining kernels on their configurations with CUDA events
+(at least 3 warm-ups; inputs larger than L2 or an L2 flush between iterations)
+and prints achieved bandwidth / FLOP rate against the measured peaks.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import ops
+from . import workloads as wl
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"],
+                "kind": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "kind": "fallback"}
+
+
+class L2Flush:
+    def __init__(self, dev, enabled=True):
+        self.buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if enabled else None
+
+    def __call__(self):
+        if self.buf is not None:
+            self.buf.zero_()
+
+
+def time_ms(fn, iters: int, warmup: int = 3, flush=None) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush:
+            flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    return total / iters
+
+
+def bench_prefill(dev, iters):
+    pw = wl.make_prefill_workload()  # config 4: 32 requests, 2048 shared prefix + 512 chunk, H 32/8, D 128, bf16
+    q, k, v = pw.q.to(dev), pw.k_cache.to(dev), pw.v_cache.to(dev)
+    rids = list(pw.block_tables)
+    width = max(len(t) for t in pw.block_tables.values())
+    tables = torch.zeros((len(rids), width), dtype=torch.int32)
+    for i, r in enumerate(rids):
+        tables[i, : len(pw.block_tables[r])] = torch.tensor(pw.block_tables[r], dtype=torch.int32)
+    tables = tables.to(dev)
+    cu = (torch.arange(len(rids) + 1, dtype=torch.int32) * pw.chunk_len).to(dev)
+    ctx = torch.full((len(rids),), pw.prefix_len + pw.chunk_len, dtype=torch.int32, device=dev)
+    ws = torch.zeros(ops.prefill_workspace_bytes(q.shape[0]), dtype=torch.uint8, device=dev)
+    out = torch.empty_like(q)
+    fn = lambda: ops.prefill_paged(q, k, v, tables, cu, ctx, max_q_tokens=pw.chunk_len, scale=pw.scale, workspace=ws, out=out)
+    ms = time_ms(fn, iters, flush=L2Flush(dev))
+    flops = wl.prefill_flops(len(rids), pw.n_heads, pw.head_dim, pw.chunk_len, pw.prefix_len)
+    p = _peaks()
+    tf = flops / (ms / 1e3) / 1e12
+    return {"kernel": "prefill_tcgen05", "workload": "config 4: 32 requests, 2048-token shared prefix + 512-token chunk, H 32/8, D 128, bf16",
+            "ms": ms, "flops": flops, "achieved_tflops": tf, "peak_tflops": p["bf16_tflops_sustained"],
+            "frac": tf / p["bf16_tflops_sustained"], "frac_of_burst": tf / p["bf16_tflops"], "peak_kind": p["kind"],
+            "status": ops.read_status(ws)}
+
+
+def bench_append(dev, iters):
+    shape = wl.C3
+    lengths = wl.config_lengths(shape)
+    nb = wl.pool_blocks_for(shape, lengths)
+    tables = wl.random_tables(lengths, nb, 1005 + shape.index)
+    hkv, d, bs = shape.n_kv_heads, shape.head_dim, shape.block_size
+    b, total = len(lengths), sum(lengths)
+    width = max(len(t) for t in tables.values())
+    dense = torch.zeros((b, width), dtype=torch.int32)
+    for i, t in enumerate(tables.values()):
+        dense[i, : len(t)] = torch.tensor(t, dtype=torch.int32)
+    dense = dense.to(dev)
+    gen = torch.Generator(device=dev).manual_seed(5)
+    k_new = (torch.randn((total, hkv, d), generator=gen, device=dev) * 2).to(torch.bfloat16)
+    v_new = (torch.randn((total, hkv, d), generator=gen, device=dev) * 2).to(torch.bfloat16)
+    kc = torch.zeros((nb, bs, hkv, d), dtype=torch.uint8, device=dev)
+    vc = torch.zeros_like(kc)
+    ks = torch.ones((nb, hkv), dtype=torch.float32, device=dev)
+    vs = torch.ones_like(ks)
+    kt = torch.zeros((b, bs, hkv, d), dtype=torch.bfloat16, device=dev)
+    vt = torch.zeros_like(kt)
+    cu = torch.zeros(b + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(lengths).cumsum(0)
+    cu = cu.to(dev)
+    start = torch.zeros(b, dtype=torch.int32, device=dev)
+    fn = lambda: ops.cache_write(k_new, v_new, cu, start, dense, kc, vc, max_new_tokens=max(lengths), k_scale=ks, v_scale=vs,
+                                 k_tail=kt, v_tail=vt)
+    ms = time_ms(fn, iters)  # 2.1 GB of source + 1 GB of codes per pass: far larger than L2
+    byts = wl.append_algorithmic_bytes(total, hkv, d)
+    p = _peaks()
+    gbs = byts / (ms / 1e3) / 1e9
+    return {"kernel": "cache_write_kernel (FP8 quantise-on-append)", "workload": f"config 3: {b} requests, {total} tokens appended, Hkv 8, D 128, bf16 -> e4m3",
+            "ms": ms, "bytes": byts, "achieved_gbs": gbs, "peak_gbs": p["hbm_gbs"], "frac": gbs / p["hbm_gbs"],
+            "frac_of_nominal_8TBs": gbs / 8000.0, "peak_kind": p["kind"]}
+
+
+def bench_norm(dev, iters, rows):
+    x, w, eps = wl.make_rms_norm_inputs(rows=rows)
+    x, w = x.to(dev), w.to(dev)
+    out = torch.empty_like(x)
+    fn = lambda: ops.rms_norm(x, w, eps, out=out)
+    ms = time_ms(fn, iters, flush=L2Flush(dev))
+    byts = wl.rms_norm_algorithmic_bytes(rows, x.shape[1], 2)
+    p = _peaks()
+    gbs = byts / (ms / 1e3) / 1e9
+    return {"kernel": "rms_norm_vec_kernel", "workload": f"[{rows}, 4096] bf16, eps 1e-5, L2 flushed between iterations", "ms": ms,
+            "bytes": byts, "achieved_gbs": gbs, "peak_gbs": p["hbm_gbs"], "frac": gbs / p["hbm_gbs"],
+            "frac_of_nominal_8TBs": gbs / 8000.0, "peak_kind": p["kind"]}
+
+
+def bench_decode(dev, iters, shape):
+    import bench as root_bench  # the repository-level benchmark owns the serving-state builder
+
+    st = root_bench.DecodeState(shape, shape.batch, 4, dev, seed_offset=0)
+    chunk = root_bench.pick_chunk_tokens(st.lengths, 0)
+    ws = torch.zeros(ops.decode_workspace_bytes(st.batch, shape.n_heads, shape.head_dim, st.tables.shape[1], 16, chunk),
+                     dtype=torch.uint8, device=dev)
+    out = torch.empty_like(st.q)
+    kw = dict(k_scale=st.k_scale, v_scale=st.v_scale) if st.fp8 else {}
+    fn = lambda: ops.paged_attention_decode(st.q, st.k_cache, st.v_cache, st.tables, st.len_steps[0], chunk_tokens=chunk,
+                                            workspace=ws, out=out, **kw)
+    pool_bytes = 2 * st.k_cache.numel() * st.k_cache.element_size()
+    ms = time_ms(fn, iters, flush=L2Flush(dev, enabled=pool_bytes < (1 << 30)))
+    byts = st.algorithmic_bytes(0)
+    p = _peaks()
+    gbs = byts / (ms / 1e3) / 1e9
+    return {"kernel": "paged decode (+combine)", "workload": f"{shape.name}, {st.batch} requests, chunk {chunk}", "ms": ms, "bytes": byts,
+            "achieved_gbs": gbs, "peak_gbs": p["hbm_gbs"], "frac": gbs / p["hbm_gbs"], "frac_of_nominal_8TBs": gbs / 8000.0,
+            "tokens_per_s": st.batch / (ms / 1e3), "peak_kind": p["kind"]}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="prefill,append,norm,decode_c2,decode_c3")
+    ap.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("kernel_bench needs a CUDA device")
+    dev = torch.device("cuda:0")
+    which = args.only.split(",")
+    import sys
+    sys.path.insert(0, ROOT)
+    if "prefill" in which:
+        print(json.dumps(bench_prefill(dev, args.iters)), flush=True)
+    if "append" in which:
+        print(json.dumps(bench_append(dev, args.iters)), flush=True)
+    if "norm" in which:
+        print(json.dumps(bench_norm(dev, args.iters, 256)), flush=True)
+        print(json.dumps(bench_norm(dev, args.iters, 16384)), flush=True)
+    if "decode_c2" in which:
+        print(json.dumps(bench_decode(dev, args.iters, wl.C2)), flush=True)
+    if "decode_c3" in which:
+        print(json.dumps(bench_decode(dev, args.iters, wl.C3)), flush=True)
+
+
+if __name__ == "__main__":
+    main()
