@@ -75,28 +75,70 @@ def peaks() -> tuple[float, str]:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed
-    region runs (read-only queries)."""
-
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and throttle reasons while the timed region runs
+    (read-only NVML queries every few milliseconds; nvidia-smi as a fallback)."""
 
     def __init__(self, index: int):
         self.index = index
-        self.rows: list[list[str]] = []
+        self.sm: list[int] = []
+        self.sm_max = None
+        self.reasons: set[str] = set()
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
+        self._nvml = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index(index))
+            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+        except Exception:  # noqa: BLE001
+            self._nvml = None
+
+    @staticmethod
+    def _physical_index(index: int) -> int:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            parts = [p for p in vis.split(",") if p.strip()]
+            if index < len(parts) and parts[index].strip().isdigit():
+                return int(parts[index])
+        return index
+
+    def _sample_nvml(self) -> None:
+        n = self._nvml
+        self.sm.append(int(n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM)))
+        bits = int(n.nvmlDeviceGetCurrentClocksEventReasons(self._handle)) if hasattr(n, "nvmlDeviceGetCurrentClocksEventReasons") \
+            else int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle))
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+        for bit, name in names.items():
+            if bits & bit:
+                self.reasons.add(name)
+
+    def _sample_smi(self) -> None:
+        fields = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                  "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={fields}", "--format=csv,noheader,nounits"],
+                             capture_output=True, text=True, timeout=5).stdout
+        for line in out.strip().splitlines():
+            r = [c.strip() for c in line.split(",")]
+            if r and r[0].isdigit():
+                self.sm.append(int(r[0]))
+                self.sm_max = int(r[1]) if r[1].isdigit() else self.sm_max
+                for i, name in enumerate(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]):
+                    if len(r) > 2 + i and r[2 + i].lower() == "active":
+                        self.reasons.add(name)
 
     def _run(self) -> None:
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
-                for line in out.strip().splitlines():
-                    self.rows.append([c.strip() for c in line.split(",")])
+                if self._nvml:
+                    self._sample_nvml()
+                else:
+                    self._sample_smi()
             except Exception:  # noqa: BLE001
                 pass
-            self._stop.wait(0.1)
+            self._stop.wait(0.005 if self._nvml else 0.1)
 
     def __enter__(self):
         self._thread.start()
@@ -107,25 +149,15 @@ class ClockSampler:
         self._thread.join(timeout=6)
 
     def summary(self) -> dict:
-        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
-        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower() == "active" for r in self.rows)]
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+        sm = sorted(self.sm)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons),
+                "samples": len(sm)}
 
 
 def pick_chunk_tokens(lengths: list[int], requested: int) -> int:
-    """Split size: enough work items to fill the GPU many times over, few
-    enough that partial results stay a small share of the KV traffic."""
-    if requested > 0:
-        return requested
-    total = sum(lengths)
-    for cand in (2048, 1024, 512, 256):
-        items = sum(-(-n // cand) for n in lengths)
-        if items >= 148 * 16 or cand == 256:
-            return cand if total >= 148 * 16 * 256 else 256
-    return 512
+    from llm_compileforge_b200.tables import pick_chunk_tokens as heuristic
+
+    return requested if requested > 0 else heuristic(lengths)
 
 
 class DecodeState:

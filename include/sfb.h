@@ -257,6 +257,19 @@ SFB_API int sfb_dequantize_fp8(const SFBTensor* codes, const SFBTensor* scales, 
 SFB_API int sfb_rms_norm(const SFBTensor* x, const SFBTensor* residual, const SFBTensor* weight, SFBTensor* out,
                  int dtype, float eps, void* stream);
 
+/* ── `_mlir_ciface_*` convention ─────────────────────────────────────────────
+ * The reference's runtime calls compiled kernels as
+ *   void _mlir_ciface_<name>(void* sret, const memref* in0, ...)
+ * (runtime/src/hal/cpu/executable.rs:23-29,159-200): the callee allocates each
+ * output, writes its memref descriptor into `sret`, and the caller frees
+ * `allocated` with the library's `serveforge_free`
+ * (runtime/src/hal/cpu/device.rs:94-109).  This shim has the signature and
+ * epsilon (1e-5) of the reference's golden kernel tests/data/golden/rms_norm.c:35-75,
+ * with device pointers; it synchronises before returning.  On failure
+ * `allocated` is NULL (the convention has no error channel). */
+SFB_API void _mlir_ciface_sfb_rms_norm_f32(void* sret, const SFBMemRef2* x, const SFBMemRef1* w);
+SFB_API void serveforge_free(void* ptr);
+
 #ifdef __cplusplus
 }
 #endif

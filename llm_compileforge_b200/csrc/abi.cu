@@ -155,14 +155,15 @@ int sfb_paged_attention_decode(const SFBTensor* q, const SFBTensor* k_cache, con
     }
     a.workspace = static_cast<char*>(workspace);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (a.workspace) SFB_CUDA_CHECK(cudaMemsetAsync(a.workspace, 0, 4, st));
+    if (a.workspace)  // status word, and the arrival counters when the split is active
+        SFB_CUDA_CHECK(cudaMemsetAsync(a.workspace, 0, a.split.n_chunks > 1 ? a.split.ml_offset : 4, st));
     if (max_blocks == 0) {
         // every request is empty: zero rows, flag it
         return fail(SFB_ERR_INVALID_ARG, "decode: block_tables has zero columns");
     }
-    rc = launch_decode_tma(a, st);  // returns SFB_ERR_UNSUPPORTED (without error text change) when not applicable
-    if (rc == SFB_ERR_UNSUPPORTED) rc = launch_decode_generic(a, st);
-    if (rc) return rc;
+    rc = launch_decode_tma(a, st);  // merges its own partials; SFB_ERR_UNSUPPORTED when the shape is not covered
+    if (rc != SFB_ERR_UNSUPPORTED) return rc;
+    if ((rc = launch_decode_generic(a, st))) return rc;
     return launch_decode_combine(a, st);
 }
 

@@ -443,57 +443,138 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             }
         }
     }
-    if (!consumer || slot != 0) return;
-
-    // ---- write the final rows, or this chunk's partials for the combine kernel
-#pragma unroll
-    for (int o = 4; o <= 16; o <<= 1) {
-        st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], o);
-        st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], o);
-    }
+    // ---- write the final rows (single-chunk request), or this chunk's partials
+    const int used_chunks = (len + (int)a.split.chunk_tokens - 1) / (int)a.split.chunk_tokens;
     float* part_ml = reinterpret_cast<float*>(a.workspace + a.split.ml_offset);
     float* part_o = reinterpret_cast<float*>(a.workspace + a.split.o_offset);
+    if (consumer && slot == 0) {
 #pragma unroll
-    for (int col = 0; col < 2; ++col) {
-        const int qh_in_group = 2 * t + col;
-        if (qh_in_group >= group) continue;
-        const int head = kvh * group + qh_in_group;
-        const float l = st.l[col];
-        if (n_chunks == 1) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            QT* dst = out + req * a.out_stride[0] + (int64_t)head * a.out_stride[1];
+        for (int o = 4; o <= 16; o <<= 1) {
+            st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], o);
+            st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], o);
+        }
 #pragma unroll
-            for (int sub = 0; sub < NSUB; ++sub) {
-                const int d0 = sub * C::EPR + rowk * C::EPC;
+        for (int col = 0; col < 2; ++col) {
+            const int qh_in_group = 2 * t + col;
+            if (qh_in_group >= group) continue;
+            const int head = kvh * group + qh_in_group;
+            const float l = st.l[col];
+            if (used_chunks == 1) {
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                QT* dst = out + req * a.out_stride[0] + (int64_t)head * a.out_stride[1];
 #pragma unroll
-                for (int q4 = 0; q4 < C::EPC / 8; ++q4) {  // 8 outputs = 16 bytes per store
-                    uint32_t w[4];
+                for (int sub = 0; sub < NSUB; ++sub) {
+                    const int d0 = sub * C::EPR + rowk * C::EPC;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const int mt = sub * (C::EPC / 2) + q4 * 4 + k;
-                        w[k] = pack2<QBF16>(st.o[mt][col] * inv, st.o[mt][2 + col] * inv);
+                    for (int q4 = 0; q4 < C::EPC / 8; ++q4) {  // 8 outputs = 16 bytes per store
+                        uint32_t w[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int mt = sub * (C::EPC / 2) + q4 * 4 + k;
+                            w[k] = pack2<QBF16>(st.o[mt][col] * inv, st.o[mt][2 + col] * inv);
+                        }
+                        *reinterpret_cast<uint4*>(dst + d0 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    *reinterpret_cast<uint4*>(dst + d0 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
-            }
-        } else {
-            const int64_t pslot = ((int64_t)req * n_chunks + chunk) * a.n_heads + head;
-            if (g == 0) { part_ml[pslot * 2] = st.m[col]; part_ml[pslot * 2 + 1] = l; }
-            float* dst = part_o + pslot * C::D;
+            } else {
+                const int64_t pslot = ((int64_t)req * n_chunks + chunk) * a.n_heads + head;
+                if (g == 0) { part_ml[pslot * 2] = st.m[col]; part_ml[pslot * 2 + 1] = l; }
+                float* dst = part_o + pslot * C::D;
 #pragma unroll
-            for (int sub = 0; sub < NSUB; ++sub) {
-                const int d0 = sub * C::EPR + rowk * C::EPC;
+                for (int sub = 0; sub < NSUB; ++sub) {
+                    const int d0 = sub * C::EPR + rowk * C::EPC;
 #pragma unroll
-                for (int q4 = 0; q4 < C::EPC / 4; ++q4) {  // 4 floats per store
-                    const int mt = sub * (C::EPC / 2) + q4 * 2;
-                    *reinterpret_cast<float4*>(dst + d0 + q4 * 4) =
-                        make_float4(st.o[mt][col], st.o[mt][2 + col], st.o[mt + 1][col], st.o[mt + 1][2 + col]);
+                    for (int q4 = 0; q4 < C::EPC / 4; ++q4) {  // 4 floats per store
+                        const int mt = sub * (C::EPC / 2) + q4 * 2;
+                        *reinterpret_cast<float4*>(dst + d0 + q4 * 4) =
+                            make_float4(st.o[mt][col], st.o[mt][2 + col], st.o[mt + 1][col], st.o[mt + 1][2 + col]);
+                    }
                 }
             }
         }
     }
-}
+    if (used_chunks == 1) return;
 
+    // ---- the thread block that finishes a request's last chunk merges all of its partials
+    // (no second launch; the partials it reads are still in L2)
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* done = reinterpret_cast<int*>(a.workspace + a.split.cnt_offset) + (int64_t)req * gridDim.y + hg;
+        is_last = atomicAdd(done, 1) == used_chunks - 1;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const int heads_here = HB * group;
+    const int64_t slot_base = ((int64_t)req * n_chunks) * a.n_heads + hg * heads_here;
+    // (a) per (head, chunk) weights exp2(m_c - m) / sum_c l_c exp2(m_c - m) into the drained ring
+    float* w_s = reinterpret_cast<float*>(ring_ptr);  // [heads_here][used_chunks]
+    const bool fits = (int64_t)heads_here * used_chunks * 4 <= (int64_t)STAGES * C::STAGE_BYTES;
+    if (fits) {
+        for (int hl = threadIdx.x; hl < heads_here; hl += C::THREADS) {
+            float m = -INFINITY;
+            for (int c = 0; c < used_chunks; ++c) m = fmaxf(m, __ldcg(part_ml + (slot_base + hl + (int64_t)c * a.n_heads) * 2));
+            float l = 0.f;
+            for (int c = 0; c < used_chunks; ++c) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (slot_base + hl + (int64_t)c * a.n_heads) * 2));
+                const float f = ml.x == -INFINITY ? 0.f : fast_exp2(ml.x - m);
+                w_s[hl * used_chunks + c] = f;
+                l = fmaf(ml.y, f, l);
+            }
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            for (int c = 0; c < used_chunks; ++c) w_s[hl * used_chunks + c] *= inv;
+        }
+        __syncthreads();
+        // (b) out[h][d] = sum_c w[h][c] * part_o[c][h][d]; several independent 16-byte loads in flight per thread
+        constexpr int VPR = C::D / 4;  // float4 per row
+        constexpr int ITEMS = (HB * 8 * VPR + C::THREADS - 1) / C::THREADS;
+        const int n_items = heads_here * VPR;
+        float4 acc[ITEMS];
+#pragma unroll
+        for (int k = 0; k < ITEMS; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c = 0; c < used_chunks; ++c) {
+#pragma unroll
+            for (int k = 0; k < ITEMS; ++k) {
+                const int i = threadIdx.x + k * C::THREADS;
+                if (i < n_items) {
+                    const int hl = i / VPR, v4 = i - hl * VPR;
+                    const float w = w_s[hl * used_chunks + c];
+                    const float4 x = __ldcg(reinterpret_cast<const float4*>(part_o + (slot_base + hl + (int64_t)c * a.n_heads) * C::D) + v4);
+                    acc[k].x = fmaf(x.x, w, acc[k].x); acc[k].y = fmaf(x.y, w, acc[k].y);
+                    acc[k].z = fmaf(x.z, w, acc[k].z); acc[k].w = fmaf(x.w, w, acc[k].w);
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < ITEMS; ++k) {
+            const int i = threadIdx.x + k * C::THREADS;
+            if (i < n_items) {
+                const int hl = i / VPR, v4 = i - hl * VPR;
+                QT* dst = out + req * a.out_stride[0] + (int64_t)(hg * heads_here + hl) * a.out_stride[1] + v4 * 4;
+                *reinterpret_cast<uint2*>(dst) = make_uint2(pack2<QBF16>(acc[k].x, acc[k].y), pack2<QBF16>(acc[k].z, acc[k].w));
+            }
+        }
+        return;
+    }
+    // very long splits: plain loop (one output element per thread at a time)
+    for (int i = threadIdx.x; i < heads_here * C::D; i += C::THREADS) {
+        const int hl = i / C::D, d = i - hl * C::D;
+        float m = -INFINITY;
+        for (int c = 0; c < used_chunks; ++c) m = fmaxf(m, __ldcg(part_ml + (slot_base + hl + (int64_t)c * a.n_heads) * 2));
+        float l = 0.f, o = 0.f;
+        for (int c = 0; c < used_chunks; ++c) {
+            const int64_t ps = slot_base + hl + (int64_t)c * a.n_heads;
+            const float mc = __ldcg(part_ml + ps * 2);
+            if (mc == -INFINITY) continue;
+            const float f = fast_exp2(mc - m);
+            l = fmaf(__ldcg(part_ml + ps * 2 + 1), f, l);
+            o = fmaf(__ldcg(part_o + ps * C::D + d), f, o);
+        }
+        out[req * a.out_stride[0] + (int64_t)(hg * heads_here + hl) * a.out_stride[1] + d] = from_float<QT>(l > 0.f ? o / l : 0.f);
+    }
+}
 
 // ---------------------------------------------------------------------------
 // Host side: tensor maps and dispatch

@@ -10,9 +10,12 @@
 // One warp owns one (block, kv_head) slice: it pulls the slice's rows with
 // 128-bit loads (rows that precede this call's tokens come from the request's
 // unquantised tail copy, rows after them are zero), keeps them in registers,
-// reduces |x| with shuffles, then writes codes, scale and - while the block is
-// still open - the refreshed tail copy.  Single pass over the source; bound:
+// reduces |x| with shuffles (packed 16-bit max), divides through a correctly
+// rounded reciprocal + one FMA correction, then writes codes, scale and - while
+// the block is still open - the refreshed tail copy.  Single pass over the source; bound:
 // HBM bandwidth.
+
+#include <type_traits>
 
 #include "sfb_common.cuh"
 
@@ -57,28 +60,121 @@ struct Src<__half> {
     }
 };
 
-// scale rule of fp8_kv_cache.py:81-86 (NaN in the slice makes the scale NaN,
-// as torch's max / clamp do)
-__device__ __forceinline__ float scale_from_amax(float amax, bool has_nan) {
-    if (has_nan) return __int_as_float(0x7fc00000);
+// Running |x| maximum over 16-byte chunks, NaN-propagating like torch's abs().max().
+// 16-bit sources stay packed (one AND and one packed max per two values).
+template <typename ST>
+struct AbsMax;
+template <>
+struct AbsMax<float> {
+    float m = 0.f;
+    __device__ void add(const uint4& r) {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) asm("max.NaN.f32 %0, %0, %1;" : "+f"(m) : "f"(fabsf(__uint_as_float(w[i]))));
+    }
+    __device__ float value() const { return m; }
+};
+template <>
+struct AbsMax<__nv_bfloat16> {
+    uint32_t m = 0u;
+    __device__ void add(const uint4& r) {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) asm("max.NaN.bf16x2 %0, %0, %1;" : "+r"(m) : "r"(w[i] & 0x7fff7fffu));
+    }
+    __device__ float value() const {
+        float r = __uint_as_float(m << 16);
+        asm("max.NaN.f32 %0, %0, %1;" : "+f"(r) : "f"(__uint_as_float(m & 0xffff0000u)));
+        return r;
+    }
+};
+template <>
+struct AbsMax<__half> {
+    uint32_t m = 0u;
+    __device__ void add(const uint4& r) {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) asm("max.NaN.f16x2 %0, %0, %1;" : "+r"(m) : "r"(w[i] & 0x7fff7fffu));
+    }
+    __device__ float value() const {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&m));
+        float r = f.x;
+        asm("max.NaN.f32 %0, %0, %1;" : "+f"(r) : "f"(f.y));
+        return r;
+    }
+};
+
+__device__ __forceinline__ float warp_max_nan(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, v, o);
+        asm("max.NaN.f32 %0, %0, %1;" : "+f"(v) : "f"(other));
+    }
+    return v;
+}
+
+// scale rule of fp8_kv_cache.py:81-86 (a NaN in the slice makes amax, hence the scale, NaN)
+__device__ __forceinline__ float scale_from_amax(float amax) {
+    if (amax != amax) return amax;
     if (amax == 0.f) return 1.0f;
     return fmaxf(__fdiv_rn(amax, 448.0f), 1e-12f);
 }
 
+// x / scale for every element of a slice.  The reference divides (fp8_kv_cache.py:89), so the
+// quotient must be the correctly rounded one.  With r = RN(1/scale): q = RN(x r),
+// q' = RN(q + RN(x - q scale) r) is that quotient (the residual is exact in an FMA; this is the
+// fast path of IEEE float division) as long as no intermediate leaves the normal range, which
+// holds for scales in [2^-60, 2^60]: there |q| <= 448 (1 + 2^-23), and an x small enough for the
+// residual to underflow gives a quotient far below the smallest e4m3 step.  Other scales, NaN
+// included, take the division instruction.
+struct Divider {
+    float scale, rcp;
+    bool fast;
+    __device__ static Divider make(float s) {
+        Divider d;
+        d.scale = s;
+        d.rcp = __frcp_rn(s);
+        d.fast = s >= 0x1p-60f && s <= 0x1p60f;
+        return d;
+    }
+    __device__ __forceinline__ float quick(float x) const {
+        const float q = __fmul_rn(x, rcp);
+        const float y = __fmaf_rn(__fmaf_rn(-q, scale, x), rcp, q);
+        return copysignf(y, x);  // scale > 0: the quotient has x's sign, also when it is zero (-0.0 encodes as 0x80)
+    }
+};
+
 // N source values -> N codes packed little-endian into 32-bit words
 template <int N>
-__device__ __forceinline__ void encode(const float* x, float scale, uint32_t* words) {
+__device__ __forceinline__ void encode_quick(const float* x, const Divider& div, uint32_t* words) {
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) {
+        uint16_t lo = float2_to_e4m3x2(div.quick(x[4 * i]), div.quick(x[4 * i + 1]));
+        uint16_t hi = float2_to_e4m3x2(div.quick(x[4 * i + 2]), div.quick(x[4 * i + 3]));
+        words[i] = (uint32_t)lo | ((uint32_t)hi << 16);
+    }
+}
+// the rare out-of-range scale: IEEE division instruction, kept out of line and register-to-register
+template <typename ST>
+__device__ __noinline__ uint2 encode_exact_chunk(uint4 raw, float scale) {
+    constexpr int N = Src<ST>::N;
+    float x[N];
+    Src<ST>::unpack(raw, x);
+    uint32_t words[2] = {0u, 0u};
 #pragma unroll
     for (int i = 0; i < N / 4; ++i) {
         uint16_t lo = float2_to_e4m3x2(__fdiv_rn(x[4 * i], scale), __fdiv_rn(x[4 * i + 1], scale));
         uint16_t hi = float2_to_e4m3x2(__fdiv_rn(x[4 * i + 2], scale), __fdiv_rn(x[4 * i + 3], scale));
         words[i] = (uint32_t)lo | ((uint32_t)hi << 16);
     }
+    return make_uint2(words[0], words[1]);
 }
 
 // CPL = 16-byte source chunks each lane keeps; a slice has bs * D / N chunks.
-template <typename ST, int CPL, bool FP8>
-__global__ void __launch_bounds__(kThreads) cache_write_kernel(AppendArgs a, int blk_offset) {
+// Grid: x strides over the blocks a request touches, y = request, z = K / V.
+template <typename ST, int CPL, bool FP8, bool EVEN, bool FIRST>
+__global__ void __launch_bounds__(kThreads) cache_write_kernel(AppendArgs a) {
+    constexpr bool first_pass = FIRST;
     constexpr int N = Src<ST>::N;
     const int req = blockIdx.y, which = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -86,11 +182,12 @@ __global__ void __launch_bounds__(kThreads) cache_write_kernel(AppendArgs a, int
     const int n_new = a.cu_tokens[req + 1] - a.cu_tokens[req];
     if (n_new <= 0) return;
     const int start = a.start_pos[req], end = start + n_new;
-    const int blk = start / bs + blk_offset + blockIdx.x;
-    if (blk > (end - 1) / bs || blk >= a.max_blocks) return;
-    const int64_t phys = a.tables[(int64_t)req * a.table_stride + blk];
-    if (phys < 0 || phys >= a.n_pool_blocks) return;
-    const int lo = blk * bs;
+    const int first_blk = start / bs;
+    const int last_blk = min((end - 1) / bs, a.max_blocks - 1);
+    // pass 0 handles each request's first touched block (the one that reads the tail copy),
+    // pass 1 all later ones (the last of which rewrites the tail copy)
+    int blk = first_pass ? first_blk : first_blk + 1 + (int)blockIdx.x;
+    const int blk_step = first_pass ? (1 << 30) : (int)gridDim.x;
 
     const ST* src = reinterpret_cast<const ST*>(which ? a.v_new : a.k_new) + (int64_t)a.cu_tokens[req] * (which ? a.vnew_stride[0] : a.new_stride[0]);
     const int64_t src_tok = which ? a.vnew_stride[0] : a.new_stride[0];
@@ -99,67 +196,100 @@ __global__ void __launch_bounds__(kThreads) cache_write_kernel(AppendArgs a, int
     const int cpr = dim / N;            // chunks per row
     const int n_chunks = bs * cpr;
 
+    // This lane's chunk j of a slice sits at row (token slot) row_of(j), column col_of(j).  When the chunks
+    // of a row divide a warp evenly (every usual head_dim) the column is the same for all j.
+    constexpr bool even = EVEN;  // (32 % cpr) == 0, checked by the launcher
+    const int r0 = even ? lane / cpr : 0, rpp = even ? 32 / cpr : 0, c0 = even ? (lane % cpr) * N : 0;
+    auto row_of = [&](int j) -> int {
+        const int i = lane + 32 * j;
+        if (i >= n_chunks) return 1 << 20;
+        return even ? r0 + j * rpp : i / cpr;
+    };
+    auto col_of = [&](int j) -> int { return even ? c0 : ((lane + 32 * j) % cpr) * N; };
+
     if constexpr (!FP8) {
-        ST* pool = reinterpret_cast<ST*>(which ? a.v_cache : a.k_cache) + phys * ps[0];
-        for (int h = warp; h < a.n_kv_heads; h += kWarps)
-            for (int i = lane; i < n_chunks; i += 32) {
-                int t = i / cpr, c = i - t * cpr, p = lo + t;
-                if (p >= start && p < end) {
-                    uint4 v = *reinterpret_cast<const uint4*>(src + (int64_t)(p - start) * src_tok + h * src_head + c * N);
-                    *reinterpret_cast<uint4*>(pool + t * ps[1] + h * ps[2] + c * N) = v;
+        for (; blk <= last_blk; blk += blk_step) {
+            const int64_t phys = a.tables[(int64_t)req * a.table_stride + blk];
+            if (phys < 0 || phys >= a.n_pool_blocks) continue;
+            const int lo = blk * bs;
+            ST* pool = reinterpret_cast<ST*>(which ? a.v_cache : a.k_cache) + phys * ps[0];
+            for (int h = warp; h < a.n_kv_heads; h += kWarps)
+                for (int i = lane; i < n_chunks; i += 32) {
+                    int t = i / cpr, c = i - t * cpr, p = lo + t;
+                    if (p >= start && p < end) {
+                        uint4 v = ldg_stream(src + (int64_t)(p - start) * src_tok + h * src_head + c * N);
+                        *reinterpret_cast<uint4*>(pool + t * ps[1] + h * ps[2] + c * N) = v;
+                    }
                 }
-            }
-        return;
+        }
     } else {
-        uint8_t* pool = reinterpret_cast<uint8_t*>(which ? a.v_cache : a.k_cache) + phys * ps[0];
+        uint8_t* pool_base = reinterpret_cast<uint8_t*>(which ? a.v_cache : a.k_cache);
         float* scales = which ? a.v_scale : a.k_scale;
         const int64_t* ss = which ? a.vs_stride : a.ks_stride;
-        ST* tail = reinterpret_cast<ST*>(which ? a.v_tail : a.k_tail);
         const int64_t* ts = which ? a.vt_stride : a.kt_stride;
-        tail += (int64_t)req * ts[0];
-        const bool still_open = end < lo + bs;  // this block keeps free slots after the call
+        ST* tail = reinterpret_cast<ST*>(which ? a.v_tail : a.k_tail) + (int64_t)req * ts[0];
+        if (warp >= a.n_kv_heads) return;
 
-        for (int h = warp; h < a.n_kv_heads; h += kWarps) {
-            uint4 raw[CPL];
-            float amax = 0.f;
-            bool has_nan = false;
+        // The warp walks its (block, head) slices with the next slice's rows already in flight
+        // while the current one is reduced and encoded.
+        auto fetch = [&](int fb, int fh, uint4 (&raw)[CPL]) {
+            const int lo = fb * bs;
 #pragma unroll
             for (int j = 0; j < CPL; ++j) {
-                const int i = lane + 32 * j;
                 raw[j] = make_uint4(0, 0, 0, 0);
-                if (i < n_chunks) {
-                    int t = i / cpr, c = i - t * cpr, p = lo + t;
-                    if (p < start) raw[j] = *reinterpret_cast<const uint4*>(tail + t * ts[1] + h * ts[2] + c * N);
-                    else if (p < end) raw[j] = ldg_stream(src + (int64_t)(p - start) * src_tok + h * src_head + c * N);
-                    float x[N];
-                    Src<ST>::unpack(raw[j], x);
+                const int p = lo + row_of(j);  // lanes past the slice get a row beyond `end`
+                if (FIRST && p < start) raw[j] = *reinterpret_cast<const uint4*>(tail + row_of(j) * ts[1] + fh * ts[2] + col_of(j));
+                else if (p < end) raw[j] = ldg_stream(src + (int64_t)(p - start) * src_tok + fh * src_head + col_of(j));
+            }
+        };
+        int h = warp;
+        uint4 raw[CPL], nxt[CPL];
+        if (blk <= last_blk) fetch(blk, h, raw);
+        while (blk <= last_blk) {
+            int nb = blk, nh = h + kWarps;
+            if (nh >= a.n_kv_heads) { nh = warp; nb = blk + blk_step; }
+            const bool more = nb <= last_blk;
+            if (more) fetch(nb, nh, nxt);
+
+            const int64_t phys = a.tables[(int64_t)req * a.table_stride + blk];
+            if (phys >= 0 && phys < a.n_pool_blocks) {
+                const int lo = blk * bs;
+                const bool still_open = end < lo + bs;  // this block keeps free slots after the call
+                uint8_t* pool = pool_base + phys * ps[0];
+                AbsMax<ST> am;
 #pragma unroll
-                    for (int e = 0; e < N; ++e) {
-                        float v = fabsf(x[e]);
-                        amax = fmaxf(amax, v);
-                        has_nan |= (v != v);
+                for (int j = 0; j < CPL; ++j) am.add(raw[j]);
+                const float scale = scale_from_amax(warp_max_nan(am.value()));
+                if (lane == 0) scales[phys * ss[0] + h * ss[1]] = scale;
+                const Divider div = Divider::make(scale);
+                // lane-constant parts of the destination addresses (row_of(j) = r0 + j*rpp when EVEN)
+                uint8_t* const dst_h = pool + h * ps[2];
+                ST* const tail_h = tail + h * ts[2];
+#pragma unroll
+                for (int j = 0; j < CPL; ++j) {
+                    if (row_of(j) < bs) {
+                        uint2 words;
+                        if (div.fast) {
+                            float x[N];
+                            Src<ST>::unpack(raw[j], x);
+                            uint32_t w[N / 4];
+                            encode_quick<N>(x, div, w);
+                            words = make_uint2(w[0], N == 8 ? w[N / 4 - 1] : 0u);
+                        } else {
+                            words = encode_exact_chunk<ST>(raw[j], scale);
+                        }
+                        uint8_t* dst = dst_h + row_of(j) * ps[1] + col_of(j);
+                        if constexpr (N == 8) *reinterpret_cast<uint2*>(dst) = words;
+                        else *reinterpret_cast<uint32_t*>(dst) = words.x;
+                        if (still_open) *reinterpret_cast<uint4*>(tail_h + row_of(j) * ts[1] + col_of(j)) = raw[j];
                     }
                 }
             }
-            amax = warp_max(amax);
-            has_nan = __any_sync(0xffffffffu, has_nan);
-            const float scale = scale_from_amax(amax, has_nan);
-            if (lane == 0) scales[phys * ss[0] + h * ss[1]] = scale;
+            if (!more) break;
 #pragma unroll
-            for (int j = 0; j < CPL; ++j) {
-                const int i = lane + 32 * j;
-                if (i < n_chunks) {
-                    int t = i / cpr, c = i - t * cpr;
-                    float x[N];
-                    Src<ST>::unpack(raw[j], x);
-                    uint32_t words[N / 4];
-                    encode<N>(x, scale, words);
-                    uint8_t* dst = pool + t * ps[1] + h * ps[2] + c * N;
-                    if constexpr (N == 8) *reinterpret_cast<uint2*>(dst) = make_uint2(words[0], words[1]);
-                    else *reinterpret_cast<uint32_t*>(dst) = words[0];
-                    if (still_open) *reinterpret_cast<uint4*>(tail + t * ts[1] + h * ts[2] + c * N) = raw[j];
-                }
-            }
+            for (int j = 0; j < CPL; ++j) raw[j] = nxt[j];
+            blk = nb;
+            h = nh;
         }
     }
 }
@@ -177,13 +307,28 @@ int launch_t(const AppendArgs& a, cudaStream_t stream) {
     // the last one rewrites it; stream order keeps the read before the write when
     // an append spans several blocks.
     for (int pass = 0; pass < 2; ++pass) {
-        const int count = pass == 0 ? 1 : touched - 1;
+        // pass 0: one thread block per request for its first touched block; pass 1: up to 32 thread
+        // blocks per request stride over its remaining blocks (few idle blocks for short requests)
+        const int count = pass == 0 ? 1 : (touched - 1 < 32 ? touched - 1 : 32);
         if (count <= 0) continue;
         dim3 grid((unsigned)count, (unsigned)a.batch, 2);
-        if (!FP8 || cpl <= 4) cache_write_kernel<ST, 4, FP8><<<grid, kThreads, 0, stream>>>(a, pass);
-        else if (cpl <= 8) cache_write_kernel<ST, 8, FP8><<<grid, kThreads, 0, stream>>>(a, pass);
-        else if (cpl <= 16) cache_write_kernel<ST, 16, FP8><<<grid, kThreads, 0, stream>>>(a, pass);
-        else cache_write_kernel<ST, 32, FP8><<<grid, kThreads, 0, stream>>>(a, pass);
+        const bool even = 32 % (a.head_dim / N) == 0;
+        auto go = [&](auto cpl_c, auto even_c, auto first_c) {
+            cache_write_kernel<ST, decltype(cpl_c)::value, FP8, decltype(even_c)::value, decltype(first_c)::value>
+                <<<grid, kThreads, 0, stream>>>(a);
+        };
+        auto by_pass = [&](auto cpl_c, auto even_c) {
+            if (pass == 0) go(cpl_c, even_c, std::true_type{});
+            else go(cpl_c, even_c, std::false_type{});
+        };
+        auto by_even = [&](auto cpl_c) {
+            if (even) by_pass(cpl_c, std::true_type{});
+            else by_pass(cpl_c, std::false_type{});
+        };
+        if (!FP8 || cpl <= 4) by_even(std::integral_constant<int, 4>{});
+        else if (cpl <= 8) by_even(std::integral_constant<int, 8>{});
+        else if (cpl <= 16) by_even(std::integral_constant<int, 16>{});
+        else by_even(std::integral_constant<int, 32>{});
         SFB_CUDA_CHECK(cudaGetLastError());
     }
     return SFB_OK;

@@ -56,6 +56,7 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 // ---------------------------------------------------------------------------
 // Workspace layout of the decode path (shared by the kernels and the size query):
 //   [0, 256)                     status word + padding
+//   done    [B][Hkv]             int32 arrival counters (chunks finished per request and kv-head group)
 //   part_ml [B][n_chunks][H][2]  float32 (running max in log2 units, denominator)
 //   part_o  [B][n_chunks][H][D]  float32 (unnormalised numerator)
 // ---------------------------------------------------------------------------
@@ -65,6 +66,7 @@ constexpr int64_t kDefaultChunkTokens = 512;
 struct DecodeSplit {
     int64_t chunk_tokens;
     int64_t n_chunks;
+    int64_t cnt_offset;
     int64_t ml_offset;
     int64_t o_offset;
     int64_t total_bytes;
@@ -78,7 +80,8 @@ inline DecodeSplit decode_split(int64_t batch, int64_t n_heads, int64_t head_dim
     s.chunk_tokens = chunk_tokens;
     s.n_chunks = ceil_div(max_blocks * block_size, chunk_tokens);
     if (s.n_chunks < 1) s.n_chunks = 1;
-    s.ml_offset = kWorkspaceHeader;
+    s.cnt_offset = kWorkspaceHeader;
+    s.ml_offset = s.cnt_offset + ceil_div(batch * n_heads * 4, 256) * 256;  // n_heads >= kv-head groups
     int64_t ml_bytes = batch * s.n_chunks * n_heads * 2 * 4;
     s.o_offset = s.ml_offset + ceil_div(ml_bytes, 256) * 256;
     s.total_bytes = s.o_offset + batch * s.n_chunks * n_heads * head_dim * 4;

@@ -58,6 +58,21 @@ def time_ms(fn, iters: int, warmup: int = 3, flush=None) -> float:
     return total / iters
 
 
+def time_ms_graph(fn, iters: int, warmup: int = 3, flush=None) -> float:
+    """Device time of one call replayed from a CUDA graph (no host launch latency
+    between the call's memset and kernels)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            fn()
+    torch.cuda.synchronize()
+    return time_ms(graph.replay, iters, warmup=2, flush=flush)
+
+
 def bench_prefill(dev, iters):
     pw = wl.make_prefill_workload()  # config 4: 32 requests, 2048 shared prefix + 512 chunk, H 32/8, D 128, bf16
     q, k, v = pw.q.to(dev), pw.k_cache.to(dev), pw.v_cache.to(dev)
@@ -132,11 +147,11 @@ def bench_norm(dev, iters, rows):
             "frac_of_nominal_8TBs": gbs / 8000.0, "peak_kind": p["kind"]}
 
 
-def bench_decode(dev, iters, shape):
+def bench_decode(dev, iters, shape, chunk_tokens=0):
     import bench as root_bench  # the repository-level benchmark owns the serving-state builder
 
     st = root_bench.DecodeState(shape, shape.batch, 4, dev, seed_offset=0)
-    chunk = root_bench.pick_chunk_tokens(st.lengths, 0)
+    chunk = root_bench.pick_chunk_tokens(st.lengths, chunk_tokens)
     ws = torch.zeros(ops.decode_workspace_bytes(st.batch, shape.n_heads, shape.head_dim, st.tables.shape[1], 16, chunk),
                      dtype=torch.uint8, device=dev)
     out = torch.empty_like(st.q)
@@ -144,19 +159,22 @@ def bench_decode(dev, iters, shape):
     fn = lambda: ops.paged_attention_decode(st.q, st.k_cache, st.v_cache, st.tables, st.len_steps[0], chunk_tokens=chunk,
                                             workspace=ws, out=out, **kw)
     pool_bytes = 2 * st.k_cache.numel() * st.k_cache.element_size()
-    ms = time_ms(fn, iters, flush=L2Flush(dev, enabled=pool_bytes < (1 << 30)))
+    flush = L2Flush(dev, enabled=pool_bytes < (1 << 30))
+    ms_eager = time_ms(fn, iters, flush=flush)
+    ms = time_ms_graph(fn, iters, flush=flush)
     byts = st.algorithmic_bytes(0)
     p = _peaks()
     gbs = byts / (ms / 1e3) / 1e9
     return {"kernel": "paged decode (+combine)", "workload": f"{shape.name}, {st.batch} requests, chunk {chunk}", "ms": ms, "bytes": byts,
             "achieved_gbs": gbs, "peak_gbs": p["hbm_gbs"], "frac": gbs / p["hbm_gbs"], "frac_of_nominal_8TBs": gbs / 8000.0,
-            "tokens_per_s": st.batch / (ms / 1e3), "peak_kind": p["kind"]}
+            "tokens_per_s": st.batch / (ms / 1e3), "peak_kind": p["kind"], "timing": "CUDA graph replay", "ms_eager_launch": ms_eager}
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="prefill,append,norm,decode_c2,decode_c3")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--chunk-tokens", type=int, default=0)
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("kernel_bench needs a CUDA device")
@@ -172,9 +190,9 @@ def main() -> None:
         print(json.dumps(bench_norm(dev, args.iters, 256)), flush=True)
         print(json.dumps(bench_norm(dev, args.iters, 16384)), flush=True)
     if "decode_c2" in which:
-        print(json.dumps(bench_decode(dev, args.iters, wl.C2)), flush=True)
+        print(json.dumps(bench_decode(dev, args.iters, wl.C2, args.chunk_tokens)), flush=True)
     if "decode_c3" in which:
-        print(json.dumps(bench_decode(dev, args.iters, wl.C3)), flush=True)
+        print(json.dumps(bench_decode(dev, args.iters, wl.C3, args.chunk_tokens)), flush=True)
 
 
 if __name__ == "__main__":

@@ -18,7 +18,7 @@ from collections.abc import Mapping, Sequence
 import torch
 
 from . import ops
-from .tables import dense_block_tables
+from .tables import dense_block_tables, pick_chunk_tokens
 
 
 def paged_attention(
@@ -47,6 +47,8 @@ def paged_attention(
     if len(rids) > q.shape[0]:
         raise IndexError(f"{len(rids)} block tables for {q.shape[0]} query rows")
     dev = q.device
+    if chunk_tokens <= 0:
+        chunk_tokens = pick_chunk_tokens(lens.tolist())
     out = ops.paged_attention_decode(
         q[: len(rids)], k_cache, v_cache, dense.to(dev, non_blocking=True), lens.to(dev, non_blocking=True),
         k_scale=k_scale, v_scale=v_scale, scale=scale, chunk_tokens=chunk_tokens,

@@ -66,3 +66,17 @@ def partition_by_request(lengths: Sequence[int], world_size: int) -> list[list[i
         parts[g].append(i)
         acc += n
     return parts
+
+
+def pick_chunk_tokens(lengths: Sequence[int], n_sm: int = 148) -> int:
+    """KV split size for the decode kernel: the largest of 2048/1024/512/256 that still
+    gives every SM slot (two thread blocks per SM) a handful of work items, so the last
+    wave stays short while split partials remain a small share of the KV traffic."""
+    slots = 2 * n_sm
+    for cand in (2048, 1024, 512):
+        if sum(-(-int(n) // cand) for n in lengths) >= 6 * slots:
+            return cand
+    for cand in (1024, 512):
+        if sum(-(-int(n) // cand) for n in lengths) >= 2 * slots:
+            return cand
+    return 256

@@ -201,3 +201,36 @@ def test_fp8_config3_sampled(cuda):
         want = ref.paged_attention(q[r : r + 1].float().cpu(), ref.fp8_dequantize_pool(wkc, wks),
                                    ref.fp8_dequantize_pool(wvc, wvs), {"x": local}, {"x": n})
         assert_half_close(out[r].cpu(), want["x"], what=f"config 3 request {r}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_append_division_is_exact_over_many_scales(cuda, dtype):
+    """The append kernel divides through a reciprocal plus one FMA correction; the codes
+    must equal torch's true division on a few million values spread over many block
+    scales (tiny, huge, powers of two, all-ones mantissas)."""
+    gen = torch.Generator().manual_seed(123)
+    nb, hkv, d, bs = 1500, 2, 128, 16
+    x = torch.randn((nb, bs, hkv, d), generator=gen)
+    gain = torch.exp2(torch.randint(-24 if dtype != torch.float16 else -10, 24 if dtype != torch.float16 else 10, (nb, 1, hkv, 1), generator=gen).float())
+    gain = gain * (1 + torch.rand((nb, 1, hkv, 1), generator=gen))
+    x = (x * gain).to(dtype)
+    x[5, :, 0] = 0
+    x[6, :, 1, :] = torch.tensor(448.0).to(dtype)                       # scale exactly 1
+    x[7, 0, 0, 0] = torch.tensor(float.fromhex("0x1.fffffep+3")).to(dtype)  # all-ones mantissa amax (fp32 source)
+    tables = {"r": list(range(nb))}
+    dense, _, _ = dense_block_tables(tables, {}, bs)
+    kc = torch.zeros((nb, bs, hkv, d), dtype=torch.uint8, device=cuda)
+    vc = torch.zeros_like(kc)
+    ks = torch.ones((nb, hkv), dtype=torch.float32, device=cuda)
+    vs = torch.ones_like(ks)
+    kt = torch.zeros((1, bs, hkv, d), dtype=dtype, device=cuda)
+    vt = torch.zeros_like(kt)
+    new = x.reshape(nb * bs, hkv, d).to(cuda)
+    cu = torch.tensor([0, nb * bs], dtype=torch.int32, device=cuda)
+    ops.cache_write(new, new.flip(0).contiguous(), cu, torch.zeros(1, dtype=torch.int32, device=cuda), dense.to(cuda), kc, vc,
+                    max_new_tokens=nb * bs, k_scale=ks, v_scale=vs, k_tail=kt, v_tail=vt)
+    want_c, want_s = ref.fp8_quantize_pool_fast(x)
+    assert torch.equal(ks.cpu(), want_s)
+    assert torch.equal(kc.cpu(), want_c)
+    want_c, want_s = ref.fp8_quantize_pool_fast(x.reshape(nb * bs, hkv, d).flip(0).reshape(nb, bs, hkv, d))
+    assert torch.equal(vc.cpu(), want_c) and torch.equal(vs.cpu(), want_s)
