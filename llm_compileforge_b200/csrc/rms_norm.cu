@@ -12,13 +12,15 @@
 // than the register budget, or not 16-byte tileable, take a two-pass scalar path.
 // Bound: HBM bandwidth.
 
+#include <type_traits>
+
 #include "sfb_common.cuh"
 
 namespace sfb {
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kMaxChunks = 4;  // 16-byte chunks per thread held in registers
+constexpr int kThreads = 128;   // small blocks: many rows resident per SM keeps more loads in flight
+constexpr int kMaxChunks = 16;  // 16-byte chunks per thread held in registers (template-selected)
 
 template <typename T>
 struct Pack;  // 16 bytes of T
@@ -83,7 +85,7 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return t;
 }
 
-template <typename T, bool RES>
+template <typename T, bool RES, int CH>
 __global__ void __launch_bounds__(kThreads) rms_norm_vec_kernel(NormArgs a) {
     constexpr int N = Pack<T>::N;
     __shared__ float scratch[kThreads / 32];
@@ -93,10 +95,10 @@ __global__ void __launch_bounds__(kThreads) rms_norm_vec_kernel(NormArgs a) {
     T* out = reinterpret_cast<T*>(a.out) + row * a.out_stride;
     const T* w = reinterpret_cast<const T*>(a.weight);
     const int n_chunks = (int)(a.hidden / N);
-    float vals[kMaxChunks][N];
+    float vals[CH][N];
     float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < kMaxChunks; ++j) {
+    for (int j = 0; j < CH; ++j) {
         const int c = threadIdx.x + j * kThreads;
         if (c < n_chunks) {
             uint4 raw = ldg_stream(x + (int64_t)c * N);
@@ -115,7 +117,7 @@ __global__ void __launch_bounds__(kThreads) rms_norm_vec_kernel(NormArgs a) {
     ss = block_sum(ss, scratch);
     const float inv = __frcp_rn(__fsqrt_rn(__fdiv_rn(ss, (float)a.hidden) + a.eps));  // torch: 1 / sqrt(mean + eps)
 #pragma unroll
-    for (int j = 0; j < kMaxChunks; ++j) {
+    for (int j = 0; j < CH; ++j) {
         const int c = threadIdx.x + j * kThreads;
         if (c < n_chunks) {
             float o[N];
@@ -170,8 +172,17 @@ int launch_t(const NormArgs& a, cudaStream_t stream) {
     if (a.rows > 0x7fffffffLL) return fail(SFB_ERR_UNSUPPORTED, "rms_norm: too many rows");
     dim3 grid((unsigned)a.rows);
     if (vec) {
-        if (a.residual) rms_norm_vec_kernel<T, true><<<grid, kThreads, 0, stream>>>(a);
-        else rms_norm_vec_kernel<T, false><<<grid, kThreads, 0, stream>>>(a);
+        const int ch = (int)ceil_div(a.hidden / N, kThreads);
+        auto go = [&](auto ch_c) {
+            constexpr int CH = decltype(ch_c)::value;
+            if (a.residual) rms_norm_vec_kernel<T, true, CH><<<grid, kThreads, 0, stream>>>(a);
+            else rms_norm_vec_kernel<T, false, CH><<<grid, kThreads, 0, stream>>>(a);
+        };
+        if (ch <= 1) go(std::integral_constant<int, 1>{});
+        else if (ch <= 2) go(std::integral_constant<int, 2>{});
+        else if (ch <= 4) go(std::integral_constant<int, 4>{});
+        else if (ch <= 8) go(std::integral_constant<int, 8>{});
+        else go(std::integral_constant<int, 16>{});
     } else {
         if (a.residual) rms_norm_scalar_kernel<T, true><<<grid, kThreads, 0, stream>>>(a);
         else rms_norm_scalar_kernel<T, false><<<grid, kThreads, 0, stream>>>(a);

@@ -129,9 +129,9 @@ def test_hal_backend_dense_and_dict_forms(cuda):
     w = wl.make_decode_workload(wl.C1)
     be = pkg.B200Backend()
     q, k, v = w.q.to(cuda), w.k_cache.to(cuda), w.v_cache.to(cuda)
-    as_dict = be.execute("paged_attention", [q, k, v, w.block_tables], seq_lens=w.seq_lens, scale=w.scale)
+    as_dict = be.execute("paged_attention", [q, k, v, w.block_tables], seq_lens=w.seq_lens, scale=w.scale, chunk_tokens=128)
     dense, lens, rids = dense_block_tables(w.block_tables, w.seq_lens, 16)
-    as_dense = be.execute("paged_attention", [q, k, v, dense.to(cuda)], seq_lens=lens.to(cuda), scale=w.scale)
+    as_dense = be.execute("paged_attention", [q, k, v, dense.to(cuda)], seq_lens=lens.to(cuda), scale=w.scale, chunk_tokens=128)
     assert torch.equal(stack_outputs(as_dict, rids), as_dense)
     want = torch.from_numpy(golden("paged_decode_c1.npz")["out"])
     assert_f32_close(as_dense.cpu(), want)
