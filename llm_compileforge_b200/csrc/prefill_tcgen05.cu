@@ -9,18 +9,20 @@
 // physical blocks at the head of several tables.  GQA: query head h reads kv
 // head h / (H / Hkv).
 //
-// One thread block = 128 query tokens of one (request, query head):
-//   warp 4    TMA producer: Q tile once, then per 128-token KV tile sixteen
+// One thread block = 256 query tokens (two 128-row tiles) of one (request, query head):
+//   warp 8    TMA producer: both Q tiles once, then per 128-token KV tile sixteen
 //             [16 tokens x 128 B] boxes for K and sixteen for V, two stages each
-//   warp 5    issues tcgen05.mma: S = Q K^T (128x128x128, both operands K-major
-//             in 128B-swizzled shared memory) into one of two S buffers in
-//             tensor memory, then O += P V with P read from tensor memory and V
-//             as an MN-major shared-memory operand
-//   warps 0-3 one thread per query row: tcgen05.ld the S row, running max /
-//             sum in log2 units, P written back to tensor memory as bf16/fp16,
-//             O rescaled in tensor memory only when the max grew by more than
-//             2^8 (the stale max stays exact in fp32), final O / l written out
-// Tensor memory: S0, S1 (128 columns each), O (128), P0, P1 (64 each) = 512.
+//   warp 9    issues tcgen05.mma: S_t = Q_t K^T (128x128x128, both operands K-major
+//             in 128B-swizzled shared memory) and O_t += P_t V with P_t read from
+//             tensor memory and V as an MN-major shared-memory operand, alternating
+//             between the two query tiles so that one tile's MMAs run while the
+//             other tile's rows are in the softmax warps
+//   warps 0-7 two softmax warpgroups, one thread per query row: tcgen05.ld the S
+//             row, running max / sum in log2 units, P written as bf16/fp16 over the
+//             first half of S's own tensor-memory columns, O rescaled in tensor
+//             memory only when the max grew by more than 2^8 (the stale max stays
+//             exact in fp32), final O / l written out
+// Tensor memory: per query tile S|P (128 columns) and O (128) = 512 columns in all.
 // Bound: tensor pipe (4*D*Sq*Skv flops per head against ~1.4 PFLOP/s dense).
 
 #include <cuda.h>
@@ -37,7 +39,7 @@ constexpr int kTileKV = 128;
 constexpr int kHeadDim = 128;
 constexpr int kSubBytes = kTileKV * 128;     // one [128 rows][128 B] swizzled sub-tile
 constexpr int kTileBytes = 2 * kSubBytes;    // D = 128 16-bit values = two sub-tiles
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // 2 softmax warpgroups, TMA warp, MMA warp
 constexpr uint32_t kSpin = 1u << 24;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;    // log2 units
@@ -191,18 +193,17 @@ enum {
     B_K_EMPTY = 3,   // +stage
     B_V_FULL = 5,    // +stage
     B_V_EMPTY = 7,   // +stage
-    B_S_FULL = 9,    // +buffer
-    B_S_EMPTY = 11,  // +buffer
-    B_P_FULL = 13,   // +buffer
-    B_PV_DONE = 15,  // +buffer
-    B_COUNT = 17
+    B_S_FULL = 9,    // +query tile
+    B_P_FULL = 11,   // +query tile
+    B_PV_DONE = 13,  // +query tile
+    B_COUNT = 15
 };
-constexpr int kSmemBytes = 5 * kTileBytes + B_COUNT * 8 + 16 + 1024;
+constexpr int kSmemBytes = 6 * kTileBytes + B_COUNT * 8 + 16 + 1024;  // 2 Q tiles, 2 K stages, 2 V stages
 
-// tensor-memory columns
-constexpr uint32_t kColS = 0;    // S0 at 0, S1 at 128
-constexpr uint32_t kColO = 256;  // O
-constexpr uint32_t kColP = 384;  // P0 at 384, P1 at 448 (16-bit pairs)
+// Tensor-memory columns of query tile t: S (fp32, 128 columns) at t*256, with P (16-bit pairs,
+// 64 columns) written over its first half once the row has been read; O (fp32) at t*256 + 128.
+constexpr uint32_t kColTile = 256;
+constexpr uint32_t kColO = 128;
 
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -211,10 +212,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     extern __shared__ uint8_t smem_raw[];
     const int req = blockIdx.z, head = blockIdx.y;
     const int q_begin = a.cu_q[req], n_q = a.cu_q[req + 1] - q_begin;
-    // heaviest tiles (latest queries) first
-    const int q_tiles = (n_q + kTileQ - 1) / kTileQ;
-    const int qt = q_tiles - 1 - (int)blockIdx.x;
-    if (qt < 0) return;
+    // heaviest blocks (latest queries) first
+    const int q_blocks = (n_q + 2 * kTileQ - 1) / (2 * kTileQ);
+    const int qb = q_blocks - 1 - (int)blockIdx.x;
+    if (qb < 0) return;
     int ctx = a.ctx_lens[req];
     if (ctx > a.max_blocks * 16) ctx = a.max_blocks * 16;
     if (ctx < n_q || n_q <= 0) {  // inconsistent request: flag it, write nothing
@@ -222,18 +223,23 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         return;
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int q0 = qt * kTileQ;
-    const int rows = min(kTileQ, n_q - q0);
-    const int pos0 = ctx - n_q + q0;                 // position of the tile's first query
-    const int n_tiles = (a.causal ? pos0 + rows - 1 : ctx - 1) / kTileKV + 1;
+    const int q0 = qb * 2 * kTileQ;                       // first query row of the block
+    int rows_t[2], tiles_t[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        rows_t[t] = max(0, min(kTileQ, n_q - q0 - t * kTileQ));
+        const int last_pos = a.causal ? ctx - n_q + q0 + t * kTileQ + rows_t[t] - 1 : ctx - 1;
+        tiles_t[t] = rows_t[t] > 0 ? last_pos / kTileKV + 1 : 0;
+    }
+    const int n_tiles = max(tiles_t[0], tiles_t[1]);
     const int used_blocks = (ctx + 15) >> 4;
     const int group = a.n_heads / a.n_kv_heads;
     const int kvh = head / group;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t q_s = base, k_s = base + kTileBytes, v_s = base + 3 * kTileBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + 5 * kTileBytes);
+    const uint32_t q_s = base, k_s = base + 2 * kTileBytes, v_s = base + 4 * kTileBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + 6 * kTileBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -246,26 +252,28 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             mbar_init(bar(B_V_FULL + s), 1);
             mbar_init(bar(B_V_EMPTY + s), 1);
             mbar_init(bar(B_S_FULL + s), 1);
-            mbar_init(bar(B_S_EMPTY + s), 4);
             mbar_init(bar(B_P_FULL + s), 4);
             mbar_init(bar(B_PV_DONE + s), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 5) tmem_alloc(smem_u32(tmem_slot), 512);
+    if (warp == 9) tmem_alloc(smem_u32(tmem_slot), 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     bool timed_out = false;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ============================ TMA producer ============================
         if (lane == 0) {
-            mbar_expect_tx(bar(B_Q_FULL), kTileBytes);
-            tma_load_4d(q_s, &qmap, bar(B_Q_FULL), q_begin + q0, 0, head);
-            tma_load_4d(q_s + kSubBytes, &qmap, bar(B_Q_FULL), q_begin + q0, 1, head);
+            mbar_expect_tx(bar(B_Q_FULL), 2 * kTileBytes);
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {  // rows past the packed batch read as zeros
+                tma_load_4d(q_s + t * kTileBytes, &qmap, bar(B_Q_FULL), q_begin + q0 + t * kTileQ, 0, head);
+                tma_load_4d(q_s + t * kTileBytes + kSubBytes, &qmap, bar(B_Q_FULL), q_begin + q0 + t * kTileQ, 1, head);
+            }
         }
         const int blk = (lane & 15) >> 1, sub = lane & 1;
         const int32_t* table = a.tables + (int64_t)req * a.table_stride;
@@ -295,59 +303,71 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             if (lane >= 16) tma_load_5d(v_s + s * kTileBytes + dst_off, &vmap, bar(B_V_FULL + s), sub, kvh, phys);
             phys = next_phys;
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ============================ MMA issuer ==============================
+        // Issue order PV0(j), QK0(j+1), PV1(j), QK1(j+1): while one query tile's rows are in the
+        // softmax warps, the tensor pipe works on the other tile.
         if (lane == 0) {
             constexpr uint32_t idesc_qk = instr_desc(BF16, false, kTileQ, kTileKV);
             constexpr uint32_t idesc_pv = instr_desc(BF16, true, kTileQ, kHeadDim);
-            auto issue_qk = [&](int j) -> bool {
+            auto issue_qk = [&](int t, int j) {  // K stage j&1 is known to be full
                 const int s = j & 1;
-                if (!mbar_wait(bar(B_K_FULL + s), (j >> 1) & 1)) return false;
-                if (j >= 2 && !mbar_wait(bar(B_S_EMPTY + s), ((j - 2) >> 1) & 1)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {  // 16 head-dim values per instruction
                     const uint32_t off = (ks >> 2) * kSubBytes + (ks & 3) * 32;
-                    mma_ss(tmem + kColS + s * 128, smem_desc(q_s + off, 16, 1024), smem_desc(k_s + s * kTileBytes + off, 16, 1024),
-                           idesc_qk, ks > 0);
+                    mma_ss(tmem + t * kColTile, smem_desc(q_s + t * kTileBytes + off, 16, 1024),
+                           smem_desc(k_s + s * kTileBytes + off, 16, 1024), idesc_qk, ks > 0);
                 }
-                tc_commit(bar(B_S_FULL + s));
-                tc_commit(bar(B_K_EMPTY + s));
-                return true;
+                tc_commit(bar(B_S_FULL + t));
             };
-            auto issue_pv = [&](int j) -> bool {
+            auto issue_pv = [&](int t, int j) -> bool {  // V stage j&1 is known to be full
                 const int s = j & 1;
-                if (!mbar_wait(bar(B_V_FULL + s), (j >> 1) & 1)) return false;
-                if (!mbar_wait(bar(B_P_FULL + s), (j >> 1) & 1)) return false;
+                if (!mbar_wait(bar(B_P_FULL + t), j & 1)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)  // 16 KV tokens per instruction
-                    mma_ts(tmem + kColO, tmem + kColP + s * 64 + ks * 8,
+                    mma_ts(tmem + t * kColTile + kColO, tmem + t * kColTile + ks * 8,
                            smem_desc(v_s + s * kTileBytes + ks * 2048, kSubBytes, 1024), idesc_pv, (j > 0 || ks > 0));
-                tc_commit(bar(B_PV_DONE + s));
-                tc_commit(bar(B_V_EMPTY + s));
+                tc_commit(bar(B_PV_DONE + t));
                 return true;
             };
-            bool ok = mbar_wait(bar(B_Q_FULL), 0);
-            ok = ok && issue_qk(0);
+            bool ok = mbar_wait(bar(B_Q_FULL), 0) && mbar_wait(bar(B_K_FULL), 0);
+            if (ok) {
+                if (tiles_t[0] > 0) issue_qk(0, 0);
+                if (tiles_t[1] > 0) issue_qk(1, 0);
+                tc_commit(bar(B_K_EMPTY));
+            }
             for (int j = 0; ok && j < n_tiles; ++j) {
-                if (j + 1 < n_tiles) ok = issue_qk(j + 1);
-                ok = ok && issue_pv(j);
+                const int s = j & 1;
+                const bool more = j + 1 < n_tiles;
+                ok = mbar_wait(bar(B_V_FULL + s), (j >> 1) & 1);
+                if (ok && more) ok = mbar_wait(bar(B_K_FULL + (s ^ 1)), ((j + 1) >> 1) & 1);
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (ok && j < tiles_t[t]) ok = issue_pv(t, j);
+                    if (ok && j + 1 < tiles_t[t]) issue_qk(t, j + 1);
+                }
+                if (ok) {
+                    tc_commit(bar(B_V_EMPTY + s));
+                    if (more) tc_commit(bar(B_K_EMPTY + (s ^ 1)));
+                }
             }
             timed_out = !ok;
         }
     } else {
         // ======================= softmax / correction / epilogue ==============
-        const int row = threadIdx.x;  // 0..127 = tensor-memory lane
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        const int t = warp >> 2;                 // query tile of this warpgroup
+        const int row = threadIdx.x & 127;       // tensor-memory lane
+        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + t * kColTile;
+        const int rows = rows_t[t], my_tiles = tiles_t[t];
         const bool row_valid = row < rows;
-        const int pos = (row_valid && a.causal) ? pos0 + row : ctx - 1;  // padding rows attend to everything; never written
+        const int pos = (row_valid && a.causal) ? ctx - n_q + q0 + t * kTileQ + row : ctx - 1;  // padding rows see everything
         const float sl2 = a.scale * kLog2e;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < n_tiles && ok; ++j) {
-            const int b = j & 1;
-            if (!mbar_wait(bar(B_S_FULL + b), (j >> 1) & 1)) { ok = false; break; }
+        for (int j = 0; j < my_tiles && ok; ++j) {
+            if (!mbar_wait(bar(B_S_FULL + t), j & 1)) { ok = false; break; }
             tc_fence_after();
             const int kv0 = j * kTileKV;
             const bool full = kv0 + kTileKV - 1 <= pos;  // no masking needed for this row
@@ -355,7 +375,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
 #pragma unroll 1
             for (int ch = 0; ch < 4; ++ch) {
                 float v[32];
-                tmem_ld32(lane_base + kColS + b * 128 + ch * 32, v);
+                tmem_ld32(lane_base + ch * 32, v);
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
                     if (full || kv0 + ch * 32 + i <= pos) mx = fmaxf(mx, v[i]);
@@ -367,7 +387,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                 const bool need = m_new > m_used + kRescaleThreshold;
                 if (__any_sync(0xffffffffu, need)) {
                     // O is only touched between PV products: wait for the previous one
-                    if (!mbar_wait(bar(B_PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1)) { ok = false; break; }
+                    if (!mbar_wait(bar(B_PV_DONE + t), (j - 1) & 1)) { ok = false; break; }
                     tc_fence_after();
                     const float f = need ? fast_exp2(m_used - m_new) : 1.f;
                     l *= f;
@@ -383,12 +403,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     tmem_wait_st();
                 }
             }
-            // P[b] was last read by the PV product of tile j-2
-            if (j >= 2 && !mbar_wait(bar(B_PV_DONE + b), ((j - 2) >> 1) & 1)) { ok = false; break; }
+            // P chunk ch (16 columns) lands on S columns that chunk <= ch has already read
 #pragma unroll 1
             for (int ch = 0; ch < 4; ++ch) {
                 float v[32];
-                tmem_ld32(lane_base + kColS + b * 128 + ch * 32, v);
+                tmem_ld32(lane_base + ch * 32, v);
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -402,22 +421,19 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     l += p0 + p1;
                     pk[i] = pack2<BF16>(p0, p1);
                 }
-                tmem_st16(lane_base + kColP + b * 64 + ch * 16, pk);
+                tmem_st16(lane_base + ch * 16, pk);
             }
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bar(B_P_FULL + b));
-                mbar_arrive(bar(B_S_EMPTY + b));
-            }
+            if (lane == 0) mbar_arrive(bar(B_P_FULL + t));
         }
         // ---- epilogue: O / l
-        if (ok) ok = mbar_wait(bar(B_PV_DONE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1);
-        if (ok) {
+        if (ok && my_tiles > 0) ok = mbar_wait(bar(B_PV_DONE + t), (my_tiles - 1) & 1);
+        if (ok && my_tiles > 0) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(q_begin + q0 + row) * a.out_stride[0] +
+            uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(q_begin + q0 + t * kTileQ + row) * a.out_stride[0] +
                             (int64_t)head * a.out_stride[1];
 #pragma unroll 1
             for (int ch = 0; ch < 4; ++ch) {
@@ -442,12 +458,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     // ---- teardown: every warp arrives here; tensor memory is released before exit
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }
 }
-
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -504,7 +519,7 @@ int launch_prefill_tcgen05(const PrefillLaunch& p, cudaStream_t stream) {
     a.n_heads = p.n_heads; a.n_kv_heads = p.n_kv_heads; a.n_pool_blocks = p.n_pool_blocks;
     a.out_stride[0] = p.out_stride[0]; a.out_stride[1] = p.out_stride[1];
     a.scale = p.scale; a.bf16 = p.dtype == SFB_BF16; a.causal = p.causal; a.status = p.status;
-    dim3 grid((unsigned)ceil_div(p.max_q_tokens, kTileQ), (unsigned)p.n_heads, (unsigned)p.n_requests);
+    dim3 grid((unsigned)ceil_div(p.max_q_tokens, 2 * kTileQ), (unsigned)p.n_heads, (unsigned)p.n_requests);
     static bool attr_set[2] = {false, false};
     if (a.bf16) {
         if (!attr_set[1]) { SFB_CUDA_CHECK(cudaFuncSetAttribute(prefill_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)); attr_set[1] = true; }
