@@ -45,6 +45,10 @@ from llm_compileforge_b200 import workloads as wl  # noqa: E402
 METRIC = "paged_fp8_decode_tokens_per_s"
 UNIT = "tokens/s"
 NOMINAL_HBM_GBS = 8000.0
+# dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes of the decode kernel, from the ncu capture of a
+# 128-request case of the same shape (profiles/decode_tma_fp8_c5.md: 1.259 GB + 0.077 GB for 1.253 GB algorithmic);
+# the full launch is beyond the capture size rule, and its traffic grows with the KV tokens read.
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.066
 
 
 def parse_args() -> argparse.Namespace:
@@ -57,6 +61,9 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--batch", type=int, default=0, help="requests per GPU (0 = the configuration's batch)")
     p.add_argument("--chunk-tokens", type=int, default=0, help="KV split size (0 = heuristic)")
     p.add_argument("--gather", action="store_true", help="all-gather the outputs over NCCL inside the step")
+    p.add_argument("--partition", choices=["request", "head"], default="request",
+                   help="request: every GPU serves its own requests (weak scaling, default); head: the configuration's "
+                        "requests on every GPU with 1/N of the kv heads each (strong scaling, the 8-GPU layout of config 5)")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--cpu-sample", type=int, default=48, help="requests in the CPU-baseline sample")
     return p.parse_args()
@@ -317,7 +324,8 @@ def workload_config(shape: wl.DecodeShape, batch: int, args: argparse.Namespace,
     return {
         "workload": f"{shape.name} paged decode, {batch} requests per GPU, H {shape.n_heads}/{shape.n_kv_heads}, "
                     f"D {shape.head_dim}, block 16, {'e4m3 KV + fp32 scales' if shape.kv_fp8 else 'bf16 KV'}",
-        "requests_per_gpu": batch, "partition": "by request", "chunk_tokens": chunk,
+        "requests_per_gpu": batch, "partition": "by kv head" if getattr(args, "partition", "request") == "head" and args.gpus > 1 else "by request",
+        "chunk_tokens": chunk,
         "l2": "pool (GBs) >> L2, no flush needed", "step": "kv append (1 token/request) + decode + combine",
     }
 
@@ -342,14 +350,22 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     shape = shape_of(args.workload)
+    by_head = args.partition == "head" and world > 1
+    if by_head:
+        if shape.n_kv_heads % world:
+            raise SystemExit(f"{shape.n_kv_heads} kv heads do not divide over {world} GPUs")
+        import dataclasses
+
+        shape = dataclasses.replace(shape, n_heads=shape.n_heads // world, n_kv_heads=shape.n_kv_heads // world)
     total_steps = args.warmup + args.steps
     # two passes (device-resident, then end-to-end) each append `total_steps` tokens
-    st = DecodeState(shape, args.batch or shape.batch, 2 * total_steps + 2, dev, seed_offset=rank * 100)
+    st = DecodeState(shape, args.batch or shape.batch, 2 * total_steps + 2, dev, seed_offset=0 if by_head else rank * 100)
     chunk = pick_chunk_tokens(st.lengths, args.chunk_tokens)
     ws_bytes = ops.decode_workspace_bytes(st.batch, shape.n_heads, shape.head_dim, st.tables.shape[1], shape.block_size, chunk)
     workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)
     out = torch.empty_like(st.q)
     gathered = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device=dev) if (args.gather and world > 1) else None
+    # (head partition: rank g's slab is heads [g*H/N, (g+1)*H/N) of every request; `gathered[g]` is that slab)
     be = B200Backend(device=dev)
     fp8kw = dict(k_scale=st.k_scale, v_scale=st.v_scale) if st.fp8 else {}
     tailkw = dict(k_tail=st.k_tail, v_tail=st.v_tail) if st.fp8 else {}
@@ -428,7 +444,7 @@ def main() -> None:
         elapsed_ms, e2e_ms, decode_ms = t.tolist()
         tot = torch.tensor([st.batch], dtype=torch.int64, device=dev)
         dist.all_reduce(tot)
-        total_requests = int(tot.item())
+        total_requests = st.batch if by_head else int(tot.item())
     else:
         total_requests = st.batch
 
@@ -440,16 +456,16 @@ def main() -> None:
         achieved = alg / (decode_ms / 1e3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if by_head else "weak", "vs_baseline": None,
             "dtype": "e4m3 KV, bf16 q/out, f32 accumulate" if st.fp8 else "bf16",
             "data": "synthetic", "config": workload_config(shape, st.batch, args, chunk),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
+                         "traffic": alg * TRAFFIC_PER_ALGORITHMIC_BYTE, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
                          "kernel": "paged decode (+combine)", "algorithmic_bytes_per_launch": alg,
                          "avg_launch_ms": decode_ms},
             "e2e": {"value": total_requests / (e2e_ms / args.steps / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * 3,
+            "gpu_launches": args.steps * 2,  # per step: cache_write_kernel + decode_tma_kernel (split merge is in-kernel)
             "clocks": clocks.summary(),
             "device_status": status,
         }
