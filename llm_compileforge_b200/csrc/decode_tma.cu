@@ -37,7 +37,7 @@ namespace {
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kTileBytes = 2048;      // one [16 tokens][128 B] sub-tile
 constexpr int kMaxChunkBlocks = 256;  // block-table entries cached per thread block
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 21;  // bounded waits: a stuck pipeline gives up (status bit) within about a second
 
 enum KvKind { KV_E4M3 = 0, KV_BF16 = 1, KV_F16 = 2 };
 

@@ -40,7 +40,7 @@ constexpr int kHeadDim = 128;
 constexpr int kSubBytes = kTileKV * 128;     // one [128 rows][128 B] swizzled sub-tile
 constexpr int kTileBytes = 2 * kSubBytes;    // D = 128 16-bit values = two sub-tiles
 constexpr int kThreads = 320;  // 2 softmax warpgroups, TMA warp, MMA warp
-constexpr uint32_t kSpin = 1u << 24;
+constexpr uint32_t kSpin = 1u << 21;  // bounded waits: a stuck pipeline gives up (status bit) within about a second
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;    // log2 units
 
@@ -159,6 +159,11 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 __device__ __forceinline__ float fast_exp2(float x) {
     float r;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
     return r;
 }
 template <bool BF16>
@@ -370,15 +375,26 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             if (!mbar_wait(bar(B_S_FULL + t), j & 1)) { ok = false; break; }
             tc_fence_after();
             const int kv0 = j * kTileKV;
-            const bool full = kv0 + kTileKV - 1 <= pos;  // no masking needed for this row
+            // tcgen05.ld / st are warp-collective: the masked / unmasked choice must be uniform across the warp
+            const bool full = __all_sync(0xffffffffu, kv0 + kTileKV - 1 <= pos);  // no row of this warp needs masking
             float mx = -INFINITY;
+            if (full) {
 #pragma unroll 1
-            for (int ch = 0; ch < 4; ++ch) {
-                float v[32];
-                tmem_ld32(lane_base + ch * 32, v);
+                for (int ch = 0; ch < 4; ++ch) {
+                    float v[32];
+                    tmem_ld32(lane_base + ch * 32, v);
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (full || kv0 + ch * 32 + i <= pos) mx = fmaxf(mx, v[i]);
+                    for (int i = 0; i < 32; i += 2) mx = max3(mx, v[i], v[i + 1]);
+                }
+            } else {
+#pragma unroll 1
+                for (int ch = 0; ch < 4; ++ch) {
+                    float v[32];
+                    tmem_ld32(lane_base + ch * 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (kv0 + ch * 32 + i <= pos) mx = fmaxf(mx, v[i]);
+                }
             }
             const float m_new = fmaxf(m_used, mx * sl2);
             if (j == 0) {
@@ -404,25 +420,43 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                 }
             }
             // P chunk ch (16 columns) lands on S columns that chunk <= ch has already read
+            const float neg_m = -m_used;
+            float l0 = 0.f, l1 = 0.f;
+            if (full) {
 #pragma unroll 1
-            for (int ch = 0; ch < 4; ++ch) {
-                float v[32];
-                tmem_ld32(lane_base + ch * 32, v);
-                uint32_t pk[16];
+                for (int ch = 0; ch < 4; ++ch) {
+                    float v[32];
+                    tmem_ld32(lane_base + ch * 32, v);
+                    uint32_t pk[16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int c = kv0 + ch * 32 + 2 * i;
-                    float p0 = fast_exp2(fmaf(v[2 * i], sl2, -m_used));
-                    float p1 = fast_exp2(fmaf(v[2 * i + 1], sl2, -m_used));
-                    if (!full) {
-                        if (c > pos) p0 = 0.f;
-                        if (c + 1 > pos) p1 = 0.f;
+                    for (int i = 0; i < 16; ++i) {
+                        const float p0 = fast_exp2(fmaf(v[2 * i], sl2, neg_m));
+                        const float p1 = fast_exp2(fmaf(v[2 * i + 1], sl2, neg_m));
+                        l0 += p0;
+                        l1 += p1;
+                        pk[i] = pack2<BF16>(p0, p1);
                     }
-                    l += p0 + p1;
-                    pk[i] = pack2<BF16>(p0, p1);
+                    tmem_st16(lane_base + ch * 16, pk);
                 }
-                tmem_st16(lane_base + ch * 16, pk);
+            } else {
+#pragma unroll 1
+                for (int ch = 0; ch < 4; ++ch) {
+                    float v[32];
+                    tmem_ld32(lane_base + ch * 32, v);
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int c = kv0 + ch * 32 + 2 * i;
+                        const float p0 = c <= pos ? fast_exp2(fmaf(v[2 * i], sl2, neg_m)) : 0.f;
+                        const float p1 = c + 1 <= pos ? fast_exp2(fmaf(v[2 * i + 1], sl2, neg_m)) : 0.f;
+                        l0 += p0;
+                        l1 += p1;
+                        pk[i] = pack2<BF16>(p0, p1);
+                    }
+                    tmem_st16(lane_base + ch * 16, pk);
+                }
             }
+            l += l0 + l1;
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
