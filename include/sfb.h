@@ -228,6 +228,28 @@ SFB_API int sfb_prefill_paged(const SFBTensor* q, const SFBTensor* k_cache, cons
                               SFBTensor* out, int dtype, float scale, int causal, int64_t max_q_tokens,
                               void* workspace, int64_t workspace_bytes, void* stream);
 
+/* ── Decode with a shared (radix) prefix ────────────────────────────────────
+ * Same result as sfb_paged_attention_decode for requests whose first
+ * `shared_prefix_blocks` table entries are the same physical blocks in EVERY
+ * row - what RadixCache.match_prefix + BlockManager::assign_cached_blocks /
+ * share_prefix produce for a common system prompt
+ * (python_runtime/engine/cache/radix_cache.py:68-103,
+ * runtime/src/cache/block.rs:214-232,273-306) - but the prefix is read once
+ * for the whole batch instead of once per request: the batch's queries attend
+ * to it as one dense [B*H/Hkv x prefix] contraction per kv head on the tcgen05
+ * kernel, each request's remaining tokens go through the split decode kernel,
+ * and the thread block finishing a request merges both partial results.
+ * The caller guarantees the rows really share those blocks (only row 0's are
+ * read) and that every seq_len exceeds the prefix.  BF16 / F16, head_dim 128,
+ * block_size 16.  Workspace from sfb_shared_prefix_workspace_bytes. */
+SFB_API int64_t sfb_shared_prefix_workspace_bytes(int64_t batch, int64_t n_heads, int64_t head_dim, int64_t max_blocks,
+                                                  int64_t block_size, int64_t chunk_tokens, int64_t shared_prefix_blocks);
+SFB_API int sfb_paged_attention_decode_shared_prefix(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
+                                                     const SFBTensor* block_tables, const SFBTensor* seq_lens,
+                                                     SFBTensor* out, int dtype, float scale, int64_t shared_prefix_blocks,
+                                                     int64_t chunk_tokens, void* workspace, int64_t workspace_bytes,
+                                                     void* stream);
+
 /* ── FP8 quantise / dequantise ──────────────────────────────────────────────
  * Replaces FP8KVCacheQuantizer.quantize_block / dequantize_block
  * (compiler/quantize/fp8_kv_cache.py:66-105); HAL op names `quantize` /

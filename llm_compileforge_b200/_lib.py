@@ -110,6 +110,7 @@ def load() -> ctypes.CDLL:
     lib.sfb_rms_norm.restype = c_int
     lib.sfb_rms_norm.argtypes = [_T, _T, _T, _T, c_int, c_float, c_void_p]
     _optional(lib)
+    _shared_prefix_protos(lib)
     _lib = lib
     return lib
 
@@ -121,6 +122,13 @@ def _optional(lib: ctypes.CDLL) -> None:
         lib.sfb_prefill_paged.argtypes = [_T] * 7 + [c_int, c_float, c_int, c_int64, c_void_p, c_int64, c_void_p]
         lib.sfb_prefill_workspace_bytes.restype = c_int64
         lib.sfb_prefill_workspace_bytes.argtypes = [c_int64]
+
+
+def _shared_prefix_protos(lib: ctypes.CDLL) -> None:
+    lib.sfb_shared_prefix_workspace_bytes.restype = c_int64
+    lib.sfb_shared_prefix_workspace_bytes.argtypes = [c_int64] * 7
+    lib.sfb_paged_attention_decode_shared_prefix.restype = c_int
+    lib.sfb_paged_attention_decode_shared_prefix.argtypes = [_T] * 6 + [c_int, c_float, c_int64, c_int64, c_void_p, c_int64, c_void_p]
 
 
 def dtype_code(dtype: torch.dtype) -> int:

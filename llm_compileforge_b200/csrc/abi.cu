@@ -244,6 +244,90 @@ int sfb_prefill_paged(const SFBTensor* q, const SFBTensor* k_cache, const SFBTen
     return rc;
 }
 
+int64_t sfb_shared_prefix_workspace_bytes(int64_t batch, int64_t n_heads, int64_t head_dim, int64_t max_blocks, int64_t block_size,
+                                          int64_t chunk_tokens, int64_t shared_prefix_blocks) {
+    if (batch < 0 || n_heads <= 0 || head_dim <= 0 || block_size <= 0 || shared_prefix_blocks < 0 || max_blocks < shared_prefix_blocks)
+        return SFB_ERR_INVALID_ARG;
+    return decode_split(batch, n_heads, head_dim, max_blocks - shared_prefix_blocks, block_size, chunk_tokens, 1).total_bytes;
+}
+
+int sfb_paged_attention_decode_shared_prefix(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
+                                             const SFBTensor* block_tables, const SFBTensor* seq_lens, SFBTensor* out, int dtype,
+                                             float scale, int64_t shared_prefix_blocks, int64_t chunk_tokens, void* workspace,
+                                             int64_t workspace_bytes, void* stream) {
+    const int e = dtype_size(dtype);
+    if (dtype != SFB_BF16 && dtype != SFB_F16)
+        return fail(SFB_ERR_UNSUPPORTED, "shared-prefix decode: bf16 / fp16 pools only (the prefix runs on the tcgen05 kernel)");
+    View vq, vk, vv, vt, vl, vo;
+    int rc;
+    if ((rc = make_view(q, "q", 3, 3, e, &vq))) return rc;
+    if ((rc = make_view(out, "out", 3, 3, e, &vo))) return rc;
+    if ((rc = make_view(k_cache, "k_cache", 4, 4, e, &vk))) return rc;
+    if ((rc = make_view(v_cache, "v_cache", 4, 4, e, &vv))) return rc;
+    if ((rc = make_view(block_tables, "block_tables", 2, 2, 4, &vt))) return rc;
+    if ((rc = make_view(seq_lens, "seq_lens", 1, 1, 4, &vl))) return rc;
+    const int64_t B = vq.size[1], H = vq.size[2], D = vq.size[3];
+    const int64_t NB = vk.size[0], bs = vk.size[1], Hkv = vk.size[2], max_blocks = vt.size[3];
+    if (vk.size[3] != D || vv.size[3] != D) return fail(SFB_ERR_INVALID_ARG, "shared-prefix decode: head_dim of q and pools differ");
+    for (int i = 0; i < 4; ++i)
+        if (vk.size[i] != vv.size[i]) return fail(SFB_ERR_INVALID_ARG, "shared-prefix decode: k_cache and v_cache shapes differ");
+    if (vo.size[1] != B || vo.size[2] != H || vo.size[3] != D) return fail(SFB_ERR_INVALID_ARG, "shared-prefix decode: out shape differs from q");
+    if (Hkv <= 0 || H % Hkv) return fail(SFB_ERR_INVALID_ARG, "shared-prefix decode: query heads not a multiple of kv heads");
+    if (vt.size[2] != B || vl.size[3] != B) return fail(SFB_ERR_INVALID_ARG, "shared-prefix decode: block_tables/seq_lens rows != batch");
+    if (shared_prefix_blocks <= 0 || shared_prefix_blocks >= max_blocks)
+        return fail(SFB_ERR_INVALID_ARG, "shared-prefix decode: shared_prefix_blocks must be in [1, max_blocks)");
+    if (bs != 16 || D != 128) return fail(SFB_ERR_UNSUPPORTED, "shared-prefix decode: block_size 16 and head_dim 128 only");
+    if (!aligned16(vk, 0) || !aligned16(vv, 0)) return fail(SFB_ERR_UNSUPPORTED, "shared-prefix decode: pools must be 16-byte aligned");
+    if (B == 0) return SFB_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const float sc = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
+
+    DecodeArgs a{};
+    a.q = vq.base; a.k = vk.base; a.v = vv.base; a.out = vo.base;
+    a.tables = reinterpret_cast<const int32_t*>(vt.base);
+    a.seq_lens = reinterpret_cast<const int32_t*>(vl.base);
+    a.q_dtype = a.kv_dtype = dtype;
+    a.batch = (int)B; a.n_heads = (int)H; a.n_kv_heads = (int)Hkv; a.head_dim = (int)D;
+    a.block_size = (int)bs; a.max_blocks = (int)max_blocks; a.n_pool_blocks = NB;
+    a.q_stride[0] = vq.stride[1]; a.q_stride[1] = vq.stride[2];
+    a.out_stride[0] = vo.stride[1]; a.out_stride[1] = vo.stride[2];
+    for (int i = 0; i < 3; ++i) { a.k_stride[i] = vk.stride[i]; a.v_stride[i] = vv.stride[i]; }
+    a.table_stride = vt.stride[2];
+    a.scale = sc;
+    a.prefix_tokens = (int)(shared_prefix_blocks * bs);
+    a.split = decode_split(B, H, D, max_blocks - shared_prefix_blocks, bs, chunk_tokens, 1);
+    if (!workspace || workspace_bytes < a.split.total_bytes)
+        return fail(SFB_ERR_WORKSPACE, "shared-prefix decode: workspace of %lld B needed, %lld given", (long long)a.split.total_bytes,
+                    (long long)(workspace ? workspace_bytes : 0));
+    a.workspace = static_cast<char*>(workspace);
+    SFB_CUDA_CHECK(cudaMemsetAsync(a.workspace, 0, a.split.ml_offset, st));
+
+    // (1) the shared prefix once for all requests: rows = requests, keys = the prefix blocks of table row 0
+    PrefillLaunch p{};
+    p.q = vq.base; p.k = vk.base; p.v = vv.base; p.out = nullptr;
+    p.cu_q = nullptr; p.ctx_lens = nullptr;
+    p.tables = a.tables; p.table_stride = vt.stride[2]; p.max_blocks = (int)max_blocks; p.block_size = (int)bs; p.head_dim = (int)D;
+    p.n_requests = 1; p.n_heads = (int)H; p.n_kv_heads = (int)Hkv; p.n_pool_blocks = NB;
+    p.total_q = B; p.max_q_tokens = B;
+    p.q_stride[0] = vq.stride[1]; p.q_stride[1] = vq.stride[2];
+    for (int i = 0; i < 3; ++i) { p.k_stride[i] = vk.stride[i]; p.v_stride[i] = vv.stride[i]; }
+    p.scale = sc; p.dtype = dtype; p.causal = 0; p.status = reinterpret_cast<int*>(workspace);
+    p.fixed_nq = (int)B; p.fixed_ctx = a.prefix_tokens;
+    p.part_o = reinterpret_cast<float*>(a.workspace + a.split.o_offset);
+    p.part_ml = reinterpret_cast<float*>(a.workspace + a.split.ml_offset);
+    p.part_seq_lens = a.seq_lens; p.part_n_chunks = (int)a.split.n_chunks; p.part_chunk_tokens = (int)a.split.chunk_tokens;
+    p.part_max_tokens = (int)(max_blocks * bs);
+    if (reinterpret_cast<uintptr_t>(vq.base) % 16 || (vq.stride[1] * e) % 16 || (vq.stride[2] * e) % 16)
+        return fail(SFB_ERR_UNSUPPORTED, "shared-prefix decode: q must be 16-byte aligned");
+    rc = launch_prefill_tcgen05(p, st);
+    if (rc == SFB_ERR_UNSUPPORTED) return fail(SFB_ERR_UNSUPPORTED, "shared-prefix decode: shape not covered by the tcgen05 kernel");
+    if (rc) return rc;
+    // (2) every request's own tokens, merged in-kernel with the prefix partial
+    rc = launch_decode_tma(a, st);
+    if (rc == SFB_ERR_UNSUPPORTED) return fail(SFB_ERR_UNSUPPORTED, "shared-prefix decode: shape not covered by the TMA decode kernel");
+    return rc;
+}
+
 int sfb_read_status(const void* workspace, int32_t* bits, void* stream) {
     if (!workspace) return fail(SFB_ERR_INVALID_ARG, "read_status: workspace is NULL");
     int32_t host = 0;

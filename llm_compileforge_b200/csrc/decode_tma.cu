@@ -178,6 +178,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 
     int len = a.seq_lens[req];
     if (len > a.max_blocks * 16) len = a.max_blocks * 16;
+    len -= a.prefix_tokens;  // shared-prefix mode: this launch covers the tokens after the prefix
     if (len <= 0) {
         if (chunk == 0) {
             if (status && threadIdx.x == 0 && hg == 0) atomicOr(status, SFB_STATUS_EMPTY_REQUEST);
@@ -210,7 +211,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    const int32_t* table = a.tables + (int64_t)(a.table_rows ? a.table_rows[req] : req) * a.table_stride + blk_begin;
+    const int32_t* table = a.tables + (int64_t)(a.table_rows ? a.table_rows[req] : req) * a.table_stride + (a.prefix_tokens >> 4) + blk_begin;
     for (int i = threadIdx.x; i < nblk; i += C::THREADS) table_s[i] = table[i];
     __syncthreads();
 
@@ -445,6 +446,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     }
     // ---- write the final rows (single-chunk request), or this chunk's partials
     const int used_chunks = (len + (int)a.split.chunk_tokens - 1) / (int)a.split.chunk_tokens;
+    const int merge_chunks = used_chunks + (a.prefix_tokens > 0 ? 1 : 0);  // + the shared-prefix partial
     float* part_ml = reinterpret_cast<float*>(a.workspace + a.split.ml_offset);
     float* part_o = reinterpret_cast<float*>(a.workspace + a.split.o_offset);
     if (consumer && slot == 0) {
@@ -459,7 +461,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             if (qh_in_group >= group) continue;
             const int head = kvh * group + qh_in_group;
             const float l = st.l[col];
-            if (used_chunks == 1) {
+            if (merge_chunks == 1) {
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 QT* dst = out + req * a.out_stride[0] + (int64_t)head * a.out_stride[1];
 #pragma unroll
@@ -493,7 +495,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             }
         }
     }
-    if (used_chunks == 1) return;
+    if (merge_chunks == 1) return;
 
     // ---- the thread block that finishes a request's last chunk merges all of its partials
     // (no second launch; the partials it reads are still in L2)
@@ -510,21 +512,21 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     const int heads_here = HB * group;
     const int64_t slot_base = ((int64_t)req * n_chunks) * a.n_heads + hg * heads_here;
     // (a) per (head, chunk) weights exp2(m_c - m) / sum_c l_c exp2(m_c - m) into the drained ring
-    float* w_s = reinterpret_cast<float*>(ring_ptr);  // [heads_here][used_chunks]
-    const bool fits = (int64_t)heads_here * used_chunks * 4 <= (int64_t)STAGES * C::STAGE_BYTES;
+    float* w_s = reinterpret_cast<float*>(ring_ptr);  // [heads_here][merge_chunks]
+    const bool fits = (int64_t)heads_here * merge_chunks * 4 <= (int64_t)STAGES * C::STAGE_BYTES;
     if (fits) {
         for (int hl = threadIdx.x; hl < heads_here; hl += C::THREADS) {
             float m = -INFINITY;
-            for (int c = 0; c < used_chunks; ++c) m = fmaxf(m, __ldcg(part_ml + (slot_base + hl + (int64_t)c * a.n_heads) * 2));
+            for (int c = 0; c < merge_chunks; ++c) m = fmaxf(m, __ldcg(part_ml + (slot_base + hl + (int64_t)c * a.n_heads) * 2));
             float l = 0.f;
-            for (int c = 0; c < used_chunks; ++c) {
+            for (int c = 0; c < merge_chunks; ++c) {
                 const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (slot_base + hl + (int64_t)c * a.n_heads) * 2));
                 const float f = ml.x == -INFINITY ? 0.f : fast_exp2(ml.x - m);
-                w_s[hl * used_chunks + c] = f;
+                w_s[hl * merge_chunks + c] = f;
                 l = fmaf(ml.y, f, l);
             }
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            for (int c = 0; c < used_chunks; ++c) w_s[hl * used_chunks + c] *= inv;
+            for (int c = 0; c < merge_chunks; ++c) w_s[hl * merge_chunks + c] *= inv;
         }
         __syncthreads();
         // (b) out[h][d] = sum_c w[h][c] * part_o[c][h][d]; several independent 16-byte loads in flight per thread
@@ -534,13 +536,13 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         float4 acc[ITEMS];
 #pragma unroll
         for (int k = 0; k < ITEMS; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int c = 0; c < used_chunks; ++c) {
+        for (int c = 0; c < merge_chunks; ++c) {
 #pragma unroll
             for (int k = 0; k < ITEMS; ++k) {
                 const int i = threadIdx.x + k * C::THREADS;
                 if (i < n_items) {
                     const int hl = i / VPR, v4 = i - hl * VPR;
-                    const float w = w_s[hl * used_chunks + c];
+                    const float w = w_s[hl * merge_chunks + c];
                     const float4 x = __ldcg(reinterpret_cast<const float4*>(part_o + (slot_base + hl + (int64_t)c * a.n_heads) * C::D) + v4);
                     acc[k].x = fmaf(x.x, w, acc[k].x); acc[k].y = fmaf(x.y, w, acc[k].y);
                     acc[k].z = fmaf(x.z, w, acc[k].z); acc[k].w = fmaf(x.w, w, acc[k].w);
@@ -562,9 +564,9 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     for (int i = threadIdx.x; i < heads_here * C::D; i += C::THREADS) {
         const int hl = i / C::D, d = i - hl * C::D;
         float m = -INFINITY;
-        for (int c = 0; c < used_chunks; ++c) m = fmaxf(m, __ldcg(part_ml + (slot_base + hl + (int64_t)c * a.n_heads) * 2));
+        for (int c = 0; c < merge_chunks; ++c) m = fmaxf(m, __ldcg(part_ml + (slot_base + hl + (int64_t)c * a.n_heads) * 2));
         float l = 0.f, o = 0.f;
-        for (int c = 0; c < used_chunks; ++c) {
+        for (int c = 0; c < merge_chunks; ++c) {
             const int64_t ps = slot_base + hl + (int64_t)c * a.n_heads;
             const float mc = __ldcg(part_ml + ps * 2);
             if (mc == -INFINITY) continue;

@@ -59,6 +59,11 @@ struct PrefillArgs {
     int bf16;               // 1 = bfloat16, 0 = float16
     int causal;             // 0: every query sees all ctx_len tokens
     int* status;
+    int fixed_nq, fixed_ctx;  // used when cu_q == nullptr (shared-prefix mode)
+    float* part_o;            // non-null: write split partials instead of normalised rows
+    float* part_ml;
+    const int32_t* part_seq_lens;
+    int part_n_chunks, part_chunk_tokens, part_max_tokens;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -216,14 +221,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                        const __grid_constant__ CUtensorMap vmap, const PrefillArgs a) {
     extern __shared__ uint8_t smem_raw[];
     const int req = blockIdx.z, head = blockIdx.y;
-    const int q_begin = a.cu_q[req], n_q = a.cu_q[req + 1] - q_begin;
+    const int q_begin = a.cu_q ? a.cu_q[req] : 0, n_q = a.cu_q ? a.cu_q[req + 1] - q_begin : a.fixed_nq;
     // heaviest blocks (latest queries) first
     const int q_blocks = (n_q + 2 * kTileQ - 1) / (2 * kTileQ);
     const int qb = q_blocks - 1 - (int)blockIdx.x;
     if (qb < 0) return;
-    int ctx = a.ctx_lens[req];
+    int ctx = a.cu_q ? a.ctx_lens[req] : a.fixed_ctx;
     if (ctx > a.max_blocks * 16) ctx = a.max_blocks * 16;
-    if (ctx < n_q || n_q <= 0) {  // inconsistent request: flag it, write nothing
+    if ((a.causal && ctx < n_q) || n_q <= 0 || ctx <= 0) {  // inconsistent request: flag it, write nothing
         if (a.status && threadIdx.x == 0) atomicOr(a.status, SFB_STATUS_EMPTY_REQUEST);
         return;
     }
@@ -466,6 +471,34 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         if (ok && my_tiles > 0) ok = mbar_wait(bar(B_PV_DONE + t), (my_tiles - 1) & 1);
         if (ok && my_tiles > 0) {
             tc_fence_after();
+            if (a.part_o) {
+                // shared-prefix mode: this row is decode request `qrow`; its partial goes to the chunk slot right after
+                // the request's own chunks, in the decode kernel's format (unnormalised O, max in log2 units, sum)
+                const int qrow = q0 + t * kTileQ + row;
+                if (row_valid) {
+                    int len = a.part_seq_lens[qrow];
+                    if (len > a.part_max_tokens) len = a.part_max_tokens;
+                    const int own = max(0, len - ctx);
+                    const int chunk = (own + a.part_chunk_tokens - 1) / a.part_chunk_tokens;
+                    const int64_t pslot = ((int64_t)qrow * a.part_n_chunks + chunk) * a.n_heads + head;
+                    a.part_ml[pslot * 2] = m_used;
+                    a.part_ml[pslot * 2 + 1] = l;
+                }
+#pragma unroll 1
+                for (int ch = 0; ch < 4; ++ch) {
+                    float o[32];
+                    tmem_ld32(lane_base + kColO + ch * 32, o);
+                    if (row_valid) {
+                        int len = a.part_seq_lens[qrow];
+                        if (len > a.part_max_tokens) len = a.part_max_tokens;
+                        const int chunk = (max(0, len - ctx) + a.part_chunk_tokens - 1) / a.part_chunk_tokens;
+                        float* dst = a.part_o + (((int64_t)qrow * a.part_n_chunks + chunk) * a.n_heads + head) * kHeadDim + ch * 32;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                    }
+                }
+            } else {
             const float inv = l > 0.f ? 1.f / l : 0.f;
             uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(q_begin + q0 + t * kTileQ + row) * a.out_stride[0] +
                             (int64_t)head * a.out_stride[1];
@@ -484,6 +517,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                         *reinterpret_cast<uint4*>(dst + ch * 32 + i * 8) = w;
                     }
                 }
+            }
             }
         }
         timed_out = !ok;
@@ -532,7 +566,7 @@ bool encode(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims
 int launch_prefill_tcgen05(const PrefillLaunch& p, cudaStream_t stream) {
     if (p.head_dim != kHeadDim || p.block_size != 16 || (p.dtype != SFB_BF16 && p.dtype != SFB_F16)) return SFB_ERR_UNSUPPORTED;
     if (p.n_heads % p.n_kv_heads || p.n_requests > 65535 || p.n_heads > 65535) return SFB_ERR_UNSUPPORTED;
-    if (reinterpret_cast<uintptr_t>(p.out) % 16 || p.out_stride[0] % 8 || p.out_stride[1] % 8) return SFB_ERR_UNSUPPORTED;
+    if (!p.part_o && (reinterpret_cast<uintptr_t>(p.out) % 16 || p.out_stride[0] % 8 || p.out_stride[1] % 8)) return SFB_ERR_UNSUPPORTED;
     CUtensorMap qmap, kmap, vmap;
     {
         cuuint64_t dims[4] = {128, (cuuint64_t)p.total_q, 2, (cuuint64_t)p.n_heads};
@@ -553,6 +587,9 @@ int launch_prefill_tcgen05(const PrefillLaunch& p, cudaStream_t stream) {
     a.n_heads = p.n_heads; a.n_kv_heads = p.n_kv_heads; a.n_pool_blocks = p.n_pool_blocks;
     a.out_stride[0] = p.out_stride[0]; a.out_stride[1] = p.out_stride[1];
     a.scale = p.scale; a.bf16 = p.dtype == SFB_BF16; a.causal = p.causal; a.status = p.status;
+    a.fixed_nq = p.fixed_nq; a.fixed_ctx = p.fixed_ctx; a.part_o = p.part_o; a.part_ml = p.part_ml;
+    a.part_seq_lens = p.part_seq_lens; a.part_n_chunks = p.part_n_chunks; a.part_chunk_tokens = p.part_chunk_tokens;
+    a.part_max_tokens = p.part_max_tokens;
     dim3 grid((unsigned)ceil_div(p.max_q_tokens, 2 * kTileQ), (unsigned)p.n_heads, (unsigned)p.n_requests);
     static bool attr_set[2] = {false, false};
     if (a.bf16) {

@@ -73,13 +73,14 @@ struct DecodeSplit {
 };
 
 inline DecodeSplit decode_split(int64_t batch, int64_t n_heads, int64_t head_dim, int64_t max_blocks,
-                                int64_t block_size, int64_t chunk_tokens) {
+                                int64_t block_size, int64_t chunk_tokens, int64_t extra_chunks = 0) {
     DecodeSplit s;
     if (chunk_tokens <= 0) chunk_tokens = kDefaultChunkTokens;
     chunk_tokens = ceil_div(chunk_tokens, block_size) * block_size;
     s.chunk_tokens = chunk_tokens;
     s.n_chunks = ceil_div(max_blocks * block_size, chunk_tokens);
     if (s.n_chunks < 1) s.n_chunks = 1;
+    s.n_chunks += extra_chunks;  // e.g. one slot per request for a shared-prefix partial
     s.cnt_offset = kWorkspaceHeader;
     s.ml_offset = s.cnt_offset + ceil_div(batch * n_heads * 4, 256) * 256;  // n_heads >= kv-head groups
     int64_t ml_bytes = batch * s.n_chunks * n_heads * 2 * 4;
@@ -170,6 +171,9 @@ struct DecodeArgs {
     float scale;
     DecodeSplit split;
     char* workspace;  // may be null when split.n_chunks == 1
+    // Shared-prefix mode: the first prefix_tokens tokens of every request were attended by another kernel
+    // whose partial sits in the chunk slot right after the request's own chunks; this launch covers the rest.
+    int prefix_tokens;
 };
 
 int launch_decode_generic(const DecodeArgs& a, cudaStream_t stream);
@@ -231,6 +235,13 @@ struct PrefillLaunch {
     int dtype;
     int causal;
     int* status;
+    // Shared-prefix mode (cu_q == nullptr): one pseudo-request of fixed_nq rows (row i = decode request i) over
+    // fixed_ctx cached tokens; results go out as split partials, not as rows of `out`.
+    int fixed_nq, fixed_ctx;
+    float* part_o;
+    float* part_ml;
+    const int32_t* part_seq_lens;
+    int part_n_chunks, part_chunk_tokens, part_max_tokens;
 };
 int launch_prefill_tcgen05(const PrefillLaunch& p, cudaStream_t stream);
 // token r of the packed query batch -> (table row, attended length) for the decode-kernel route

@@ -170,9 +170,41 @@ def bench_decode(dev, iters, shape, chunk_tokens=0):
             "tokens_per_s": st.batch / (ms / 1e3), "peak_kind": p["kind"], "timing": "CUDA graph replay", "ms_eager_launch": ms_eager}
 
 
+def bench_shared_prefix(dev, iters, n_requests=32):
+    """Decode step right after config 4's prefill: requests that share a 2048-token prefix and own 512 tokens."""
+    pw = wl.make_prefill_workload(n_requests=n_requests)
+    k, v = pw.k_cache.to(dev), pw.v_cache.to(dev)
+    rids = list(pw.block_tables)
+    b = len(rids)
+    width = max(len(t) for t in pw.block_tables.values())
+    tables = torch.zeros((b, width), dtype=torch.int32)
+    for i, r in enumerate(rids):
+        tables[i, : len(pw.block_tables[r])] = torch.tensor(pw.block_tables[r], dtype=torch.int32)
+    tables = tables.to(dev)
+    lens = torch.full((b,), pw.prefix_len + pw.chunk_len, dtype=torch.int32, device=dev)
+    q = pw.q[:b].contiguous().to(dev)
+    out = torch.empty_like(q)
+    pb = pw.prefix_len // 16
+    ws1 = torch.zeros(ops.decode_workspace_bytes(b, pw.n_heads, pw.head_dim, width, 16, 256), dtype=torch.uint8, device=dev)
+    plain = lambda: ops.paged_attention_decode(q, k, v, tables, lens, chunk_tokens=256, workspace=ws1, out=out)
+    from . import _lib
+    ws2 = torch.zeros(int(_lib.load().sfb_shared_prefix_workspace_bytes(b, pw.n_heads, pw.head_dim, width, 16, 256, pb)),
+                      dtype=torch.uint8, device=dev)
+    shared = lambda: ops.paged_attention_decode_shared_prefix(q, k, v, tables, lens, pb, chunk_tokens=256, workspace=ws2, out=out)
+    flush = L2Flush(dev)
+    ms_plain = time_ms_graph(plain, iters, flush=flush)
+    ms_shared = time_ms_graph(shared, iters, flush=flush)
+    e = 2
+    plain_bytes = wl.decode_algorithmic_bytes([pw.prefix_len + pw.chunk_len] * b, pw.n_heads, pw.n_kv_heads, pw.head_dim, e, e, e, False)
+    return {"kernel": "shared-prefix decode (tcgen05 prefix + TMA remainder)", "workload": f"{b} requests, 2048-token shared prefix + 512 own tokens, H 32/8, D 128, bf16",
+            "ms_plain_decode": ms_plain, "ms_shared_prefix": ms_shared, "speedup": ms_plain / ms_shared,
+            "plain_algorithmic_bytes": plain_bytes, "plain_achieved_gbs": plain_bytes / (ms_plain / 1e3) / 1e9,
+            "equivalent_gbs": plain_bytes / (ms_shared / 1e3) / 1e9, "timing": "CUDA graph replay, L2 flushed"}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="prefill,append,norm,decode_c2,decode_c3")
+    ap.add_argument("--only", default="prefill,append,norm,decode_c2,decode_c3,shared_prefix")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--chunk-tokens", type=int, default=0)
     args = ap.parse_args()
@@ -189,6 +221,9 @@ def main() -> None:
     if "norm" in which:
         print(json.dumps(bench_norm(dev, args.iters, 256)), flush=True)
         print(json.dumps(bench_norm(dev, args.iters, 16384)), flush=True)
+    if "shared_prefix" in which:
+        for n in (32, 128, 512):
+            print(json.dumps(bench_shared_prefix(dev, args.iters, n)), flush=True)
     if "decode_c2" in which:
         print(json.dumps(bench_decode(dev, args.iters, wl.C2, args.chunk_tokens)), flush=True)
     if "decode_c3" in which:

@@ -18,7 +18,7 @@ from collections.abc import Mapping, Sequence
 import torch
 
 from . import ops
-from .tables import dense_block_tables, pick_chunk_tokens
+from .tables import dense_block_tables, pick_chunk_tokens, shared_prefix_blocks
 
 
 def paged_attention(
@@ -33,12 +33,16 @@ def paged_attention(
     k_scale: torch.Tensor | None = None,
     v_scale: torch.Tensor | None = None,
     chunk_tokens: int = 0,
+    share_prefix: bool = True,
 ) -> dict[str, torch.Tensor]:
     """PagedAttention with block-table indirection (paged_attention.py:200-227).
 
     ``q [B,H,D]``; ``k_cache``/``v_cache`` ``[NB,block_size,Hkv,D]``; returns
     ``{request_id: [H,D]}``.  ``k_scale``/``v_scale`` (keyword-only, float32
-    ``[NB,Hkv]``) switch to an e4m3 code pool dequantised inside the kernel."""
+    ``[NB,Hkv]``) switch to an e4m3 code pool dequantised inside the kernel.
+    When every table starts with the same physical blocks (a radix-shared prefix of at
+    least 16 blocks, 64 or more requests) and the pool is bf16/fp16 with head_dim 128, that prefix is read once
+    for the whole batch (``share_prefix=False`` turns this off); results are the same."""
     if k_cache.shape[1] != block_size:
         raise ValueError(f"k_cache block dimension {k_cache.shape[1]} != block_size {block_size}")
     if not block_tables:
@@ -49,6 +53,15 @@ def paged_attention(
     dev = q.device
     if chunk_tokens <= 0:
         chunk_tokens = pick_chunk_tokens(lens.tolist())
+    if (share_prefix and k_scale is None and q.dtype in (torch.bfloat16, torch.float16) and q.shape[-1] == 128
+            and block_size == 16 and q.shape[1] // k_cache.shape[2] <= 8):
+        n_shared = shared_prefix_blocks(block_tables, seq_lens, block_size)
+        # below ~64 requests the prefix stays in L2 and the plain kernel is as fast (measured crossover)
+        if n_shared >= 16 and n_shared < dense.shape[1] and len(rids) >= 64:
+            out = ops.paged_attention_decode_shared_prefix(
+                q[: len(rids)], k_cache, v_cache, dense.to(dev, non_blocking=True), lens.to(dev, non_blocking=True),
+                n_shared, scale=scale, chunk_tokens=chunk_tokens)
+            return {rid: out[i] for i, rid in enumerate(rids)}
     out = ops.paged_attention_decode(
         q[: len(rids)], k_cache, v_cache, dense.to(dev, non_blocking=True), lens.to(dev, non_blocking=True),
         k_scale=k_scale, v_scale=v_scale, scale=scale, chunk_tokens=chunk_tokens,

@@ -221,3 +221,38 @@ def prefill_paged(
         workspace.numel() * workspace.element_size(), current_stream(q.device),
     ))
     return out
+
+
+def paged_attention_decode_shared_prefix(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    seq_lens: torch.Tensor,
+    shared_prefix_blocks: int,
+    *,
+    scale: float | None = None,
+    chunk_tokens: int = 0,
+    workspace: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Decode for a batch whose first ``shared_prefix_blocks`` table entries are the same
+    physical blocks in every row (a radix-shared prefix): the prefix is read once for
+    the whole batch.  Same result as :func:`paged_attention_decode`."""
+    lib = _lib.load()
+    if out is None:
+        out = torch.empty_like(q)
+    b, h, d = q.shape
+    need = int(lib.sfb_shared_prefix_workspace_bytes(b, h, d, block_tables.shape[1], k_cache.shape[1], chunk_tokens,
+                                                     shared_prefix_blocks))
+    if need < 0:
+        raise ValueError("invalid shared-prefix workspace query")
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    check(lib.sfb_paged_attention_decode_shared_prefix(
+        desc(q, "q"), desc(k_cache, "k_cache"), desc(v_cache, "v_cache"), desc(block_tables, "block_tables"),
+        desc(seq_lens, "seq_lens"), desc(out, "out"), dtype_code(q.dtype), float(scale) if scale is not None else 0.0,
+        int(shared_prefix_blocks), int(chunk_tokens), workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+        current_stream(q.device),
+    ))
+    return out

@@ -80,3 +80,22 @@ def pick_chunk_tokens(lengths: Sequence[int], n_sm: int = 148) -> int:
         if sum(-(-int(n) // cand) for n in lengths) >= 2 * slots:
             return cand
     return 256
+
+
+def shared_prefix_blocks(block_tables: Mapping[str, Sequence[int]], seq_lens: Mapping[str, int], block_size: int) -> int:
+    """Number of leading table entries that are the same physical blocks in EVERY request and lie
+    wholly inside every request's attended length minus one token (each request keeps at least one
+    token of its own after the prefix).  This is what a radix-cache hit on a common prompt yields
+    (python_runtime/engine/cache/radix_cache.py:68-103: matched blocks are prepended to the table)."""
+    tables = list(block_tables.values())
+    if len(tables) < 2:
+        return 0
+    limit = min(len(t) for t in tables)
+    for rid, t in block_tables.items():
+        length = min(int(seq_lens.get(rid, len(t) * block_size)), len(t) * block_size)
+        limit = min(limit, (length - 1) // block_size)
+    first = tables[0]
+    n = 0
+    while n < limit and all(t[n] == first[n] for t in tables[1:]):
+        n += 1
+    return n

@@ -229,3 +229,51 @@ def test_stale_slots_past_length_are_ignored(cuda):
     out = pkg.paged_attention(q.to(cuda), k2.to(cuda), v2.to(cuda), tables, lens)
     rids = list(tables)
     assert_half_close(stack_outputs(out, rids).cpu(), stack_outputs(want, rids), what="stale slots")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("n_req,prefix_blocks,heads,kv_heads", [(32, 128, 32, 8), (5, 16, 8, 2), (150, 20, 8, 8), (1, 16, 8, 1)])
+def test_shared_prefix_decode_matches_plain_decode(cuda, dtype, n_req, prefix_blocks, heads, kv_heads):
+    """Radix-shared prefix (identical leading block ids in every table): the cascade route
+    (prefix once on the tcgen05 kernel + per-request remainder, merged in-kernel) equals the
+    oracle and the plain decode kernel."""
+    g = torch.Generator().manual_seed(n_req + prefix_blocks)
+    d = 128
+    own = torch.randint(1, 200, (n_req,), generator=g).tolist()
+    own[0] = 1
+    own_blocks = [-(-n // 16) for n in own]
+    nb = prefix_blocks + sum(own_blocks) + 4
+    perm = torch.randperm(nb, generator=g).tolist()
+    shared = perm[:prefix_blocks]
+    tables, lens, at = {}, {}, prefix_blocks
+    for i in range(n_req):
+        tables[f"r{i}"] = shared + perm[at : at + own_blocks[i]]
+        lens[f"r{i}"] = prefix_blocks * 16 + own[i]
+        at += own_blocks[i]
+    q = torch.randn((n_req, heads, d), generator=g).to(dtype)
+    k = torch.randn((nb, 16, kv_heads, d), generator=g).to(dtype)
+    v = torch.randn((nb, 16, kv_heads, d), generator=g).to(dtype)
+    rids = list(tables)
+    from llm_compileforge_b200.tables import shared_prefix_blocks
+
+    assert shared_prefix_blocks(tables, lens, 16) == (prefix_blocks if n_req > 1 else 0)
+    dense, ll, _ = dense_block_tables(tables, lens, 16)
+    dq, dk, dv = q.to(cuda), k.to(cuda), v.to(cuda)
+    plain = ops.paged_attention_decode(dq, dk, dv, dense.to(cuda), ll.to(cuda), chunk_tokens=64)
+    want = stack_outputs(ref.paged_attention_f64(q, k, v, tables, lens), rids)
+    for chunk in (0, 64):
+        ws_bytes = _lib_ws(n_req, heads, d, dense.shape[1], chunk, prefix_blocks)
+        ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=cuda)
+        got = ops.paged_attention_decode_shared_prefix(dq, dk, dv, dense.to(cuda), ll.to(cuda), prefix_blocks, chunk_tokens=chunk, workspace=ws)
+        assert ops.read_status(ws) == 0
+        assert_half_close(got.cpu(), want, what=f"shared prefix chunk {chunk}")
+        assert (got.float() - plain.float()).abs().max() <= 2e-2
+    if n_req > 1:  # the dict API finds the shared prefix by itself
+        auto = pkg.paged_attention(dq, dk, dv, tables, lens)
+        assert_half_close(stack_outputs(auto, rids).cpu(), want, what="auto shared prefix")
+
+
+def _lib_ws(b, h, d, max_blocks, chunk, prefix_blocks):
+    from llm_compileforge_b200 import _lib
+
+    return int(_lib.load().sfb_shared_prefix_workspace_bytes(b, h, d, max_blocks, 16, chunk, prefix_blocks))
