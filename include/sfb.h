@@ -189,6 +189,8 @@ SFB_API int sfb_read_status_static(int32_t* bits, void* stream);
  *   k_tail, v_tail   [B, bs, Hkv, D] src_dtype (F8E4M3 only): unquantised copy of
  *                    each request's open (partially filled) block, owned by the
  *                    caller, read and updated by this call
+ *   tail_rows        [B] int32 or NULL: request r's tail copy is row tail_rows[r]
+ *                    (a stable slot while batch order changes); NULL = row r
  *
  * Token at position p goes to slot (table[p / bs], p % bs) (cache_manager.py:154-159).
  * FP8: after the call every touched (block, kv_head) slice holds exactly
@@ -198,7 +200,8 @@ SFB_API int sfb_read_status_static(int32_t* bits, void* stream);
 SFB_API int sfb_cache_write(const SFBTensor* k_new, const SFBTensor* v_new, const SFBTensor* cu_tokens,
                     const SFBTensor* start_pos, const SFBTensor* block_tables, SFBTensor* k_cache,
                     SFBTensor* v_cache, SFBTensor* k_scale, SFBTensor* v_scale, SFBTensor* k_tail,
-                    SFBTensor* v_tail, int src_dtype, int kv_dtype, int64_t max_new_tokens, void* stream);
+                    SFBTensor* v_tail, const SFBTensor* tail_rows, int src_dtype, int kv_dtype,
+                    int64_t max_new_tokens, void* stream);
 
 /* ── Chunked prefill over the paged pool ────────────────────────────────────
  * Replaces kernels/flash_attention.py:179-202 `flash_attention_fwd` (CPU path

@@ -10,9 +10,10 @@ operator surface:
 The CUDA library is loaded on first use; there is no CPU fallback.
 """
 
+from .cache import PagedKVCache
 from .hal import B200Backend, OpExecutor
 from .kernels_api import FP8KVCacheQuantizer, chunked_prefill, flash_attention_fwd, fused_rms_norm_add, paged_attention
 
-__all__ = ["B200Backend", "OpExecutor", "FP8KVCacheQuantizer", "chunked_prefill", "flash_attention_fwd",
+__all__ = ["B200Backend", "OpExecutor", "PagedKVCache", "FP8KVCacheQuantizer", "chunked_prefill", "flash_attention_fwd",
            "fused_rms_norm_add", "paged_attention"]
 __version__ = "0.1.0"

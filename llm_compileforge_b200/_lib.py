@@ -102,7 +102,7 @@ def load() -> ctypes.CDLL:
     lib.sfb_read_status.restype = c_int
     lib.sfb_read_status.argtypes = [c_void_p, POINTER(c_int32), c_void_p]
     lib.sfb_cache_write.restype = c_int
-    lib.sfb_cache_write.argtypes = [_T] * 11 + [c_int, c_int, c_int64, c_void_p]
+    lib.sfb_cache_write.argtypes = [_T] * 12 + [c_int, c_int, c_int64, c_void_p]
     lib.sfb_quantize_fp8.restype = c_int
     lib.sfb_quantize_fp8.argtypes = [_T, _T, _T, c_int, c_int, c_void_p]
     lib.sfb_dequantize_fp8.restype = c_int

@@ -341,8 +341,8 @@ int sfb_read_status(const void* workspace, int32_t* bits, void* stream) {
 
 int sfb_cache_write(const SFBTensor* k_new, const SFBTensor* v_new, const SFBTensor* cu_tokens,
                     const SFBTensor* start_pos, const SFBTensor* block_tables, SFBTensor* k_cache, SFBTensor* v_cache,
-                    SFBTensor* k_scale, SFBTensor* v_scale, SFBTensor* k_tail, SFBTensor* v_tail, int src_dtype,
-                    int kv_dtype, int64_t max_new_tokens, void* stream) {
+                    SFBTensor* k_scale, SFBTensor* v_scale, SFBTensor* k_tail, SFBTensor* v_tail,
+                    const SFBTensor* tail_rows, int src_dtype, int kv_dtype, int64_t max_new_tokens, void* stream) {
     const int se = dtype_size(src_dtype), kve = dtype_size(kv_dtype);
     if (!se || src_dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "cache_write: source dtype %d", src_dtype);
     if (!kve) return fail(SFB_ERR_INVALID_ARG, "cache_write: pool dtype %d", kv_dtype);
@@ -391,7 +391,13 @@ int sfb_cache_write(const SFBTensor* k_new, const SFBTensor* v_new, const SFBTen
         if ((rc = make_view(v_tail, "v_tail", 4, 4, se, &vt))) return rc;
         if (ks.size[2] != kc.size[0] || ks.size[3] != Hkv || vs.size[2] != kc.size[0] || vs.size[3] != Hkv)
             return fail(SFB_ERR_INVALID_ARG, "cache_write: scales must be [NB, Hkv]");
-        if (kt.size[0] < B || kt.size[1] != bs || kt.size[2] != Hkv || kt.size[3] != D)
+        View tr;
+        if (tail_rows) {
+            if ((rc = make_view(tail_rows, "tail_rows", 1, 1, 4, &tr))) return rc;
+            if (tr.size[3] != B) return fail(SFB_ERR_INVALID_ARG, "cache_write: tail_rows must have one entry per request");
+            a.tail_rows = reinterpret_cast<const int32_t*>(tr.base);
+        }
+        if ((!tail_rows && kt.size[0] < B) || kt.size[1] != bs || kt.size[2] != Hkv || kt.size[3] != D)
             return fail(SFB_ERR_INVALID_ARG, "cache_write: k_tail must be [>=batch, bs, Hkv, D]");
         for (int i = 0; i < 4; ++i)
             if (kt.size[i] != vt.size[i]) return fail(SFB_ERR_INVALID_ARG, "cache_write: k_tail and v_tail shapes differ");

@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(kThreads) cache_write_kernel(AppendArgs a) {
         float* scales = which ? a.v_scale : a.k_scale;
         const int64_t* ss = which ? a.vs_stride : a.ks_stride;
         const int64_t* ts = which ? a.vt_stride : a.kt_stride;
-        ST* tail = reinterpret_cast<ST*>(which ? a.v_tail : a.k_tail) + (int64_t)req * ts[0];
+        ST* tail = reinterpret_cast<ST*>(which ? a.v_tail : a.k_tail) + (int64_t)(a.tail_rows ? a.tail_rows[req] : req) * ts[0];
         if (warp >= a.n_kv_heads) return;
 
         // The warp walks its (block, head) slices with the next slice's rows already in flight

@@ -197,6 +197,7 @@ struct AppendArgs {
     float* v_scale;
     void* k_tail;
     void* v_tail;
+    const int32_t* tail_rows;  // optional: request r's tail copy lives in row tail_rows[r] (stable slot across steps)
     int src_dtype, kv_dtype;
     int batch, n_kv_heads, head_dim, block_size, max_new_tokens;
     int64_t n_pool_blocks;

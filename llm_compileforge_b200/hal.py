@@ -86,7 +86,8 @@ class B200Backend(OpExecutor):
         ``block_table`` is either the reference's dict (then ``seq_lens`` is a
         dict keyword and the result is a dict, like kernels.paged_attention) or a
         dense int32 tensor ``[B,max_blocks]`` (then ``seq_lens`` is an int32
-        tensor and the result is ``[B,H,D]``)."""
+        tensor and the result is ``[B,H,D]``; ``shared_prefix_blocks=n`` selects the
+        shared-prefix route for tables whose first n entries are identical in every row)."""
         q, k_cache, v_cache, table = inputs[:4]
         seq_lens = kw.get("seq_lens", inputs[4] if len(inputs) > 4 else None)
         common = dict(k_scale=kw.get("k_scale"), v_scale=kw.get("v_scale"), scale=kw.get("scale"),
@@ -96,6 +97,10 @@ class B200Backend(OpExecutor):
                                                block_size=kw.get("block_size", k_cache.shape[1]), **common)
         if seq_lens is None:
             raise ValueError("paged_attention with a dense block table needs seq_lens")
+        if kw.get("shared_prefix_blocks"):
+            return ops.paged_attention_decode_shared_prefix(q, k_cache, v_cache, table, seq_lens, int(kw["shared_prefix_blocks"]),
+                                                            scale=kw.get("scale"), chunk_tokens=kw.get("chunk_tokens", 0),
+                                                            workspace=kw.get("workspace"))
         return ops.paged_attention_decode(q, k_cache, v_cache, table, seq_lens, workspace=kw.get("workspace"), **common)
 
     def _op_cache_write(self, inputs: list[Any], **kw: Any) -> None:
@@ -114,7 +119,7 @@ class B200Backend(OpExecutor):
             max_new = int(kw["max_new_tokens"])
         ops.cache_write(key, value, cu, positions, kw["block_tables"], kw["k_cache"], kw["v_cache"],
                         max_new_tokens=max_new, k_scale=kw.get("k_scale"), v_scale=kw.get("v_scale"),
-                        k_tail=kw.get("k_tail"), v_tail=kw.get("v_tail"))
+                        k_tail=kw.get("k_tail"), v_tail=kw.get("v_tail"), tail_rows=kw.get("tail_rows"))
 
     def _op_quantize(self, inputs: list[Any], **kw: Any) -> Any:
         """``quantize(input, dtype="fp8")`` -> ``(codes, scale)`` (HALOps.td:202-206)."""

@@ -97,6 +97,7 @@ def cache_write(
     v_scale: torch.Tensor | None = None,
     k_tail: torch.Tensor | None = None,
     v_tail: torch.Tensor | None = None,
+    tail_rows: torch.Tensor | None = None,
 ) -> None:
     """Scatter new K/V tokens ``[T,Hkv,D]`` into their paged slots; with scales
     and tails given the pool holds e4m3 codes and the write quantises on append."""
@@ -106,7 +107,8 @@ def cache_write(
     check(lib.sfb_cache_write(
         desc(k_new, "k_new"), desc(v_new, "v_new"), desc(cu_tokens, "cu_tokens"), desc(start_pos, "start_pos"),
         desc(block_tables, "block_tables"), desc(kc, "k_cache"), desc(vc, "v_cache"), desc(k_scale, "k_scale"),
-        desc(v_scale, "v_scale"), desc(k_tail, "k_tail"), desc(v_tail, "v_tail"), dtype_code(k_new.dtype),
+        desc(v_scale, "v_scale"), desc(k_tail, "k_tail"), desc(v_tail, "v_tail"), desc(tail_rows, "tail_rows"),
+        dtype_code(k_new.dtype),
         _lib.SFB_F8E4M3 if fp8 else dtype_code(k_cache.dtype), int(max_new_tokens), current_stream(k_new.device),
     ))
 
