@@ -14,7 +14,8 @@ from ctypes import POINTER, Structure, Union, byref, c_char_p, c_float, c_int, c
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libsfb.so")
+# SFB_LIBRARY points at another build of the same library (same ABI), e.g. a system-wide install
+LIB_PATH = os.environ.get("SFB_LIBRARY") or os.path.join(_PKG, "libsfb.so")
 
 SFB_DEVICE_CPU, SFB_DEVICE_CUDA = 1, 2
 
