@@ -13,7 +13,7 @@ partitioned across GPUs (weak scaling, no data-path collective).
 
 One step = one decode iteration of the hot path: quantise-on-append of one new
 token per request into the paged FP8 pool, then paged attention of one query
-token per request over the pool (split kernel + combine).  ``value`` is decode
+token per request over the pool (split-K kernel, partial results merged in-kernel).  ``value`` is decode
 tokens/s with every input already in HBM; ``e2e`` is the same step driven
 through the HAL ``OpExecutor`` with host (pinned) inputs: q, new K/V, block
 tables and lengths are copied to the device and the attention output back to
@@ -326,7 +326,7 @@ def workload_config(shape: wl.DecodeShape, batch: int, args: argparse.Namespace,
                     f"D {shape.head_dim}, block 16, {'e4m3 KV + fp32 scales' if shape.kv_fp8 else 'bf16 KV'}",
         "requests_per_gpu": batch, "partition": "by kv head" if getattr(args, "partition", "request") == "head" and args.gpus > 1 else "by request",
         "chunk_tokens": chunk,
-        "l2": "pool (GBs) >> L2, no flush needed", "step": "kv append (1 token/request) + decode + combine",
+        "l2": "pool (GBs) >> L2, no flush needed", "step": "kv append (1 token/request) + split-K decode (in-kernel merge)",
     }
 
 
@@ -401,7 +401,7 @@ def main() -> None:
         t_end.record()
         sync_all()
     elapsed_ms = t_start.elapsed_time(t_end)
-    decode_ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps  # decode + combine launches
+    decode_ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps  # the decode call: status memset + decode kernel
     status = ops.read_status(workspace)
 
     # ---- end-to-end through the HAL executor with host buffers --------------------
@@ -461,7 +461,7 @@ def main() -> None:
             "data": "synthetic", "config": workload_config(shape, st.batch, args, chunk),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": alg * TRAFFIC_PER_ALGORITHMIC_BYTE, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
-                         "kernel": "paged decode (+combine)", "algorithmic_bytes_per_launch": alg,
+                         "kernel": "decode_tma_kernel (split-K, in-kernel merge)", "algorithmic_bytes_per_launch": alg,
                          "avg_launch_ms": decode_ms},
             "e2e": {"value": total_requests / (e2e_ms / args.steps / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},

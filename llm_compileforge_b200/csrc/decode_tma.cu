@@ -41,11 +41,6 @@ constexpr uint32_t kSpinLimit = 1u << 21;  // bounded waits: a stuck pipeline gi
 
 enum KvKind { KV_E4M3 = 0, KV_BF16 = 1, KV_F16 = 2 };
 
-struct TmaDecodeParams {
-    DecodeArgs a;
-    int head_groups;  // n_kv_heads / HB
-};
-
 // ---------------------------------------------------------------------------
 // PTX wrappers
 // ---------------------------------------------------------------------------

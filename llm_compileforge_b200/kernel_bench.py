@@ -165,7 +165,7 @@ def bench_decode(dev, iters, shape, chunk_tokens=0):
     byts = st.algorithmic_bytes(0)
     p = _peaks()
     gbs = byts / (ms / 1e3) / 1e9
-    return {"kernel": "paged decode (+combine)", "workload": f"{shape.name}, {st.batch} requests, chunk {chunk}", "ms": ms, "bytes": byts,
+    return {"kernel": "decode_tma_kernel (split-K, in-kernel merge)", "workload": f"{shape.name}, {st.batch} requests, chunk {chunk}", "ms": ms, "bytes": byts,
             "achieved_gbs": gbs, "peak_gbs": p["hbm_gbs"], "frac": gbs / p["hbm_gbs"], "frac_of_nominal_8TBs": gbs / 8000.0,
             "tokens_per_s": st.batch / (ms / 1e3), "peak_kind": p["kind"], "timing": "CUDA graph replay", "ms_eager_launch": ms_eager}
 

@@ -139,3 +139,45 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libsfb.so"))
     with pytest.raises(RuntimeError, match="no fallback"):
         _lib.load()
+
+
+def test_prefill_and_shared_prefix_validation():
+    lib = _lib.load()
+    r = ctypes.byref
+    lib.sfb_prefill_paged.restype = ctypes.c_int
+    q = _fake_desc((40, 8, 128), 2)
+    k = _fake_desc((12, 16, 2, 128), 2)
+    t = _fake_desc((3, 4), 4)
+    cu = _fake_desc((4,), 4)
+    ctx = _fake_desc((3,), 4)
+    args = lambda **o: [r(o.get("q", q)), r(k), r(k), r(o.get("t", t)), r(o.get("cu", cu)), r(ctx), r(o.get("q", q)), o.get("dt", _lib.SFB_BF16),
+                        ctypes.c_float(0.0), 1, 40, None, 0, None]
+    assert lib.sfb_prefill_paged(*args(cu=_fake_desc((3,), 4))) == _lib.SFB_ERR_INVALID_ARG      # cu_q needs R+1 entries
+    assert lib.sfb_prefill_paged(*args(t=_fake_desc((2, 4), 4))) == _lib.SFB_ERR_INVALID_ARG      # one table row per request
+    assert lib.sfb_prefill_paged(*args(dt=_lib.SFB_F8E4M3)) == _lib.SFB_ERR_INVALID_ARG
+    assert lib.sfb_prefill_paged(*args(q=_fake_desc((40, 7, 128), 2))) == _lib.SFB_ERR_INVALID_ARG  # 7 heads over 2 kv heads
+    assert lib.sfb_prefill_workspace_bytes(1000) == 256 + 8192
+    # shared-prefix decode
+    fn = lib.sfb_paged_attention_decode_shared_prefix
+    dq = _fake_desc((3, 8, 128), 2)
+    lens = _fake_desc((3,), 4)
+    call = lambda blocks, dt=_lib.SFB_BF16, ws=None, wsb=0: fn(r(dq), r(k), r(k), r(t), r(lens), r(dq), dt, ctypes.c_float(0.0), blocks, 0, ws, wsb, None)
+    assert call(0) == _lib.SFB_ERR_INVALID_ARG and call(4) == _lib.SFB_ERR_INVALID_ARG   # prefix must leave room for own tokens
+    assert call(2, dt=_lib.SFB_F32) in (_lib.SFB_ERR_UNSUPPORTED, _lib.SFB_ERR_INVALID_ARG)
+    assert call(2) == _lib.SFB_ERR_WORKSPACE
+    need = lib.sfb_shared_prefix_workspace_bytes(3, 8, 128, 4, 16, 0, 2)
+    assert need > 256 + 3 * 2 * 8 * (128 + 2) * 4  # own chunk + the prefix partial slot
+    assert lib.sfb_shared_prefix_workspace_bytes(3, 8, 128, 4, 16, 0, 5) < 0
+
+
+def test_static_scratch_size_check_needs_no_gpu():
+    lib = _lib.load()
+    fn = lib.sfb_paged_attention_decode_static
+    fn.restype = ctypes.c_int
+    r = ctypes.byref
+    q = _fake_desc((4096, 64, 128), 2)
+    k = _fake_desc((4, 16, 8, 128), 2)
+    t = _fake_desc((4096, 2), 4)
+    lens = _fake_desc((4096,), 4)
+    rc = fn(r(q), r(k), r(k), None, None, r(t), r(lens), r(q), _lib.SFB_BF16, _lib.SFB_BF16, ctypes.c_float(0.0), ctypes.c_int64(16), None)
+    assert rc == _lib.SFB_ERR_WORKSPACE and b"built-in array" in lib.sfb_last_error()
