@@ -84,7 +84,8 @@ typedef enum {
     SFB_ERR_UNSUPPORTED = -2,  /* valid request this build has no kernel for */
     SFB_ERR_WORKSPACE = -3,    /* workspace missing or too small */
     SFB_ERR_CUDA = -4,         /* a CUDA runtime/driver call failed */
-    SFB_ERR_DEVICE_STATUS = -5 /* a kernel flagged bad data (sfb_read_status) */
+    SFB_ERR_DEVICE_STATUS = -5, /* a kernel flagged bad data (sfb_read_status) */
+    SFB_ERR_OUT_OF_BLOCKS = -6  /* block manager: pool or device table rows exhausted */
 } SFBStatus;
 
 typedef enum {
@@ -118,6 +119,10 @@ SFB_API const char* sfb_status_string(int status);
  *   block_tables [B, max_blocks] int32  row r lists request r's physical blocks
  *   seq_lens     [B] int32            attended tokens; clamped to max_blocks*bs
  *                                       like paged_attention.py:37-48
+ *   table_rows   [B] int32 or NULL    batch position r reads table row
+ *                                       table_rows[r] (block_tables may then have any
+ *                                       number of rows, e.g. the block manager's
+ *                                       device-resident tables); NULL = row r
  *   out          [B, H, D]            q_dtype
  *
  * Query head h reads kv head h / (H / Hkv) (paged_attention.py:57-60); no mask;
@@ -135,9 +140,10 @@ SFB_API int64_t sfb_paged_attention_workspace_bytes(int64_t batch, int64_t n_hea
 
 SFB_API int sfb_paged_attention_decode(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
                                const SFBTensor* k_scale, const SFBTensor* v_scale,
-                               const SFBTensor* block_tables, const SFBTensor* seq_lens, SFBTensor* out,
-                               int q_dtype, int kv_dtype, float scale, int64_t chunk_tokens,
-                               void* workspace, int64_t workspace_bytes, void* stream);
+                               const SFBTensor* block_tables, const SFBTensor* seq_lens,
+                               const SFBTensor* table_rows, SFBTensor* out, int q_dtype, int kv_dtype,
+                               float scale, int64_t chunk_tokens, void* workspace, int64_t workspace_bytes,
+                               void* stream);
 
 /* Copies the workspace status word to the host (synchronises `stream`).
  * Returns SFB_OK when it is zero, SFB_ERR_DEVICE_STATUS otherwise; *bits (may
@@ -169,8 +175,8 @@ SFB_API int sfb_read_status(const void* workspace, int32_t* bits, void* stream);
 SFB_API int sfb_paged_attention_decode_static(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
                                               const SFBTensor* k_scale, const SFBTensor* v_scale,
                                               const SFBTensor* block_tables, const SFBTensor* seq_lens,
-                                              SFBTensor* out, int q_dtype, int kv_dtype, float scale,
-                                              int64_t chunk_tokens, void* stream);
+                                              const SFBTensor* table_rows, SFBTensor* out, int q_dtype,
+                                              int kv_dtype, float scale, int64_t chunk_tokens, void* stream);
 SFB_API int sfb_read_status_static(int32_t* bits, void* stream);
 
 /* ── KV cache write / FP8 quantise-on-append ───────────────────────────────
@@ -281,6 +287,37 @@ SFB_API int sfb_dequantize_fp8(const SFBTensor* codes, const SFBTensor* scales, 
  * _ops_norm.py:35-45). */
 SFB_API int sfb_rms_norm(const SFBTensor* x, const SFBTensor* residual, const SFBTensor* weight, SFBTensor* out,
                  int dtype, float eps, void* stream);
+
+/* ── Block manager with device-resident tables ───────────────────────────────
+ * Replaces BlockManager (runtime/src/cache/block.rs:84-346; Python twin in the
+ * engine): reference-counted physical blocks, LIFO free list, per-request ordered
+ * tables, prefix hits prepended (assign_cached_blocks), share_prefix,
+ * ensure_blocks, free / free_block.  Block ids and their order are identical to
+ * the reference's for the same call sequence.
+ *
+ * sfb_bm_attach_device_tables gives the manager a device array
+ * int32 [rows, max_blocks]; every request then owns a stable row (sfb_bm_row)
+ * and sfb_bm_sync uploads only entries changed since the last sync.  Pass that
+ * array as `block_tables` and the requests' rows as `table_rows` to the decode
+ * entry points.  Negative returns are SFBStatus values (SFB_ERR_OUT_OF_BLOCKS for
+ * the reference's OutOfMemoryError). */
+typedef struct SFBBlockManager SFBBlockManager;
+SFB_API SFBBlockManager* sfb_bm_create(int64_t num_blocks, int64_t block_size);
+SFB_API void sfb_bm_destroy(SFBBlockManager* bm);
+SFB_API int sfb_bm_attach_device_tables(SFBBlockManager* bm, void* d_tables, int64_t rows, int64_t max_blocks);
+SFB_API int64_t sfb_bm_allocate(SFBBlockManager* bm, const char* request_id, int64_t num_tokens, int32_t* out, int64_t cap);
+SFB_API void sfb_bm_free(SFBBlockManager* bm, const char* request_id);
+SFB_API void sfb_bm_free_block(SFBBlockManager* bm, int64_t block_id);
+SFB_API int sfb_bm_assign_cached_blocks(SFBBlockManager* bm, const char* request_id, const int32_t* block_ids, int64_t n);
+SFB_API int sfb_bm_ensure_blocks(SFBBlockManager* bm, const char* request_id, int64_t target_tokens);
+SFB_API int64_t sfb_bm_share_prefix(SFBBlockManager* bm, const char* src_request_id, const char* dst_request_id,
+                                    int64_t prefix_len);
+SFB_API void sfb_bm_increment_ref_count(SFBBlockManager* bm, int64_t block_id);
+SFB_API int64_t sfb_bm_ref_count(const SFBBlockManager* bm, int64_t block_id);
+SFB_API int64_t sfb_bm_num_free_blocks(const SFBBlockManager* bm);
+SFB_API int64_t sfb_bm_get_blocks(const SFBBlockManager* bm, const char* request_id, int32_t* out, int64_t cap);
+SFB_API int64_t sfb_bm_row(const SFBBlockManager* bm, const char* request_id);
+SFB_API int64_t sfb_bm_sync(SFBBlockManager* bm, void* stream);
 
 /* ── `_mlir_ciface_*` convention ─────────────────────────────────────────────
  * The reference's runtime calls compiled kernels as

@@ -26,6 +26,7 @@ SFB_ERR_UNSUPPORTED = -2
 SFB_ERR_WORKSPACE = -3
 SFB_ERR_CUDA = -4
 SFB_ERR_DEVICE_STATUS = -5
+SFB_ERR_OUT_OF_BLOCKS = -6
 
 # SFBDType
 SFB_F32, SFB_BF16, SFB_F16, SFB_F8E4M3 = 0, 1, 2, 3
@@ -99,7 +100,7 @@ def load() -> ctypes.CDLL:
     lib.sfb_paged_attention_workspace_bytes.restype = c_int64
     lib.sfb_paged_attention_workspace_bytes.argtypes = [c_int64] * 6
     lib.sfb_paged_attention_decode.restype = c_int
-    lib.sfb_paged_attention_decode.argtypes = [_T] * 8 + [c_int, c_int, c_float, c_int64, c_void_p, c_int64, c_void_p]
+    lib.sfb_paged_attention_decode.argtypes = [_T] * 9 + [c_int, c_int, c_float, c_int64, c_void_p, c_int64, c_void_p]
     lib.sfb_read_status.restype = c_int
     lib.sfb_read_status.argtypes = [c_void_p, POINTER(c_int32), c_void_p]
     lib.sfb_cache_write.restype = c_int
@@ -112,6 +113,7 @@ def load() -> ctypes.CDLL:
     lib.sfb_rms_norm.argtypes = [_T, _T, _T, _T, c_int, c_float, c_void_p]
     _optional(lib)
     _shared_prefix_protos(lib)
+    _block_manager_protos(lib)
     _lib = lib
     return lib
 
@@ -123,6 +125,30 @@ def _optional(lib: ctypes.CDLL) -> None:
         lib.sfb_prefill_paged.argtypes = [_T] * 7 + [c_int, c_float, c_int, c_int64, c_void_p, c_int64, c_void_p]
         lib.sfb_prefill_workspace_bytes.restype = c_int64
         lib.sfb_prefill_workspace_bytes.argtypes = [c_int64]
+
+
+def _block_manager_protos(lib: ctypes.CDLL) -> None:
+    h, s, i32p = c_void_p, c_char_p, POINTER(c_int32)
+    protos = {
+        "sfb_bm_create": (c_void_p, [c_int64, c_int64]),
+        "sfb_bm_destroy": (None, [h]),
+        "sfb_bm_attach_device_tables": (c_int, [h, c_void_p, c_int64, c_int64]),
+        "sfb_bm_allocate": (c_int64, [h, s, c_int64, i32p, c_int64]),
+        "sfb_bm_free": (None, [h, s]),
+        "sfb_bm_free_block": (None, [h, c_int64]),
+        "sfb_bm_assign_cached_blocks": (c_int, [h, s, i32p, c_int64]),
+        "sfb_bm_ensure_blocks": (c_int, [h, s, c_int64]),
+        "sfb_bm_share_prefix": (c_int64, [h, s, s, c_int64]),
+        "sfb_bm_increment_ref_count": (None, [h, c_int64]),
+        "sfb_bm_ref_count": (c_int64, [h, c_int64]),
+        "sfb_bm_num_free_blocks": (c_int64, [h]),
+        "sfb_bm_get_blocks": (c_int64, [h, s, i32p, c_int64]),
+        "sfb_bm_row": (c_int64, [h, s]),
+        "sfb_bm_sync": (c_int64, [h, c_void_p]),
+    }
+    for name, (res, args) in protos.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
 
 
 def _shared_prefix_protos(lib: ctypes.CDLL) -> None:

@@ -78,6 +78,7 @@ const char* sfb_status_string(int status) {
         case SFB_ERR_WORKSPACE: return "workspace missing or too small";
         case SFB_ERR_CUDA: return "CUDA call failed";
         case SFB_ERR_DEVICE_STATUS: return "kernel flagged bad data";
+        case SFB_ERR_OUT_OF_BLOCKS: return "block pool or table rows exhausted";
         default: return "unknown status";
     }
 }
@@ -90,8 +91,9 @@ int64_t sfb_paged_attention_workspace_bytes(int64_t batch, int64_t n_heads, int6
 
 int sfb_paged_attention_decode(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
                                const SFBTensor* k_scale, const SFBTensor* v_scale, const SFBTensor* block_tables,
-                               const SFBTensor* seq_lens, SFBTensor* out, int q_dtype, int kv_dtype, float scale,
-                               int64_t chunk_tokens, void* workspace, int64_t workspace_bytes, void* stream) {
+                               const SFBTensor* seq_lens, const SFBTensor* table_rows, SFBTensor* out, int q_dtype,
+                               int kv_dtype, float scale, int64_t chunk_tokens, void* workspace, int64_t workspace_bytes,
+                               void* stream) {
     const int qe = dtype_size(q_dtype), kve = dtype_size(kv_dtype);
     if (!qe || q_dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "decode: q dtype %d", q_dtype);
     if (!kve) return fail(SFB_ERR_INVALID_ARG, "decode: kv dtype %d", kv_dtype);
@@ -114,7 +116,14 @@ int sfb_paged_attention_decode(const SFBTensor* q, const SFBTensor* k_cache, con
         if (vk.size[i] != vv.size[i]) return fail(SFB_ERR_INVALID_ARG, "decode: k_cache and v_cache shapes differ");
     if (vo.size[1] != B || vo.size[2] != H || vo.size[3] != D) return fail(SFB_ERR_INVALID_ARG, "decode: out shape differs from q");
     if (Hkv <= 0 || H % Hkv) return fail(SFB_ERR_INVALID_ARG, "decode: %lld query heads not a multiple of %lld kv heads", (long long)H, (long long)Hkv);
-    if (vt.size[2] != B || vl.size[3] != B) return fail(SFB_ERR_INVALID_ARG, "decode: block_tables/seq_lens rows != batch %lld", (long long)B);
+    View vr;
+    if (table_rows) {
+        if ((rc = make_view(table_rows, "table_rows", 1, 1, 4, &vr))) return rc;
+        if (vr.size[3] != B) return fail(SFB_ERR_INVALID_ARG, "decode: table_rows must have one entry per request");
+    } else if (vt.size[2] != B) {
+        return fail(SFB_ERR_INVALID_ARG, "decode: block_tables rows != batch %lld", (long long)B);
+    }
+    if (vl.size[3] != B) return fail(SFB_ERR_INVALID_ARG, "decode: seq_lens rows != batch %lld", (long long)B);
     if (vl.size[3] > 1 && vl.stride[3] != 1) return fail(SFB_ERR_INVALID_ARG, "decode: seq_lens must be contiguous");
     if (bs <= 0 || (D * kve) % 16) return fail(SFB_ERR_UNSUPPORTED, "decode: head_dim*elem (%lld B) must be a multiple of 16", (long long)(D * kve));
     if (!aligned16(vk, 0) || !aligned16(vv, 0)) return fail(SFB_ERR_UNSUPPORTED, "decode: pool base and strides must be 16-byte aligned");
@@ -125,6 +134,8 @@ int sfb_paged_attention_decode(const SFBTensor* q, const SFBTensor* k_cache, con
     a.q = vq.base; a.k = vk.base; a.v = vv.base; a.out = vo.base;
     a.tables = reinterpret_cast<const int32_t*>(vt.base);
     a.seq_lens = reinterpret_cast<const int32_t*>(vl.base);
+    a.table_rows = table_rows ? reinterpret_cast<const int32_t*>(vr.base) : nullptr;
+    a.n_table_rows = vt.size[2];
     a.q_dtype = q_dtype; a.kv_dtype = kv_dtype;
     a.batch = (int)B; a.n_heads = (int)H; a.n_kv_heads = (int)Hkv; a.head_dim = (int)D;
     a.block_size = (int)bs; a.max_blocks = (int)max_blocks; a.n_pool_blocks = NB;
@@ -227,7 +238,7 @@ int sfb_prefill_paged(const SFBTensor* q, const SFBTensor* k_cache, const SFBTen
     if ((rc = launch_prefill_expand(p.cu_q, p.ctx_lens, (int)R, T, p.max_blocks, (int)bs, causal != 0, rows, lens, st))) return rc;
     DecodeArgs a{};
     a.q = vq.base; a.k = vk.base; a.v = vv.base; a.out = vo.base;
-    a.tables = p.tables; a.table_rows = rows; a.seq_lens = lens;
+    a.tables = p.tables; a.table_rows = rows; a.n_table_rows = R; a.seq_lens = lens;
     a.q_dtype = dtype; a.kv_dtype = dtype;
     a.batch = (int)T; a.n_heads = (int)H; a.n_kv_heads = (int)Hkv; a.head_dim = (int)D;
     a.block_size = (int)bs; a.max_blocks = p.max_blocks; a.n_pool_blocks = NB;

@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(kThreads) decode_generic_kernel(DecodeArgs a) 
 #pragma unroll
         for (int i = 0; i < DSLOTS; ++i) acc[g][i] = 0.f;
 
-    const int32_t* table = a.tables + (int64_t)(a.table_rows ? a.table_rows[req] : req) * a.table_stride;
+    const int32_t* table = a.tables + decode_table_row(a, req, status) * a.table_stride;
     const KV* kbase = reinterpret_cast<const KV*>(a.k);
     const KV* vbase = reinterpret_cast<const KV*>(a.v);
 

@@ -43,8 +43,9 @@ int scratch_for_current_device(void** out) {
 
 extern "C" int sfb_paged_attention_decode_static(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
                                                  const SFBTensor* k_scale, const SFBTensor* v_scale,
-                                                 const SFBTensor* block_tables, const SFBTensor* seq_lens, SFBTensor* out,
-                                                 int q_dtype, int kv_dtype, float scale, int64_t chunk_tokens, void* stream) {
+                                                 const SFBTensor* block_tables, const SFBTensor* seq_lens, const SFBTensor* table_rows,
+                                                 SFBTensor* out, int q_dtype, int kv_dtype, float scale, int64_t chunk_tokens,
+                                                 void* stream) {
     if (!q || !k_cache || !block_tables) return sfb::fail(SFB_ERR_INVALID_ARG, "decode_static: q, k_cache and block_tables are required");
     if (q->rank != 3 || k_cache->rank != 4 || block_tables->rank != 2)
         return sfb::fail(SFB_ERR_INVALID_ARG, "decode_static: q must be rank 3, k_cache rank 4, block_tables rank 2");
@@ -61,7 +62,7 @@ extern "C" int sfb_paged_attention_decode_static(const SFBTensor* q, const SFBTe
     if (rc) return rc;
     // The regular entry point zeroes the status word (the only part of the scratch
     // that must start clean; partials are fully overwritten before they are read).
-    return sfb_paged_attention_decode(q, k_cache, v_cache, k_scale, v_scale, block_tables, seq_lens, out, q_dtype, kv_dtype,
+    return sfb_paged_attention_decode(q, k_cache, v_cache, k_scale, v_scale, block_tables, seq_lens, table_rows, out, q_dtype, kv_dtype,
                                       scale, chunk_tokens, scratch, SFB_STATIC_SCRATCH_BYTES, stream);
 }
 

@@ -206,7 +206,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    const int32_t* table = a.tables + (int64_t)(a.table_rows ? a.table_rows[req] : req) * a.table_stride + (a.prefix_tokens >> 4) + blk_begin;
+    const int32_t* table = a.tables + decode_table_row(a, req, status) * a.table_stride + (a.prefix_tokens >> 4) + blk_begin;
     for (int i = threadIdx.x; i < nblk; i += C::THREADS) table_s[i] = table[i];
     __syncthreads();
 

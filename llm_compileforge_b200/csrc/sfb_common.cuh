@@ -156,6 +156,7 @@ struct DecodeArgs {
     const float* v_scale;
     const int32_t* tables;
     const int32_t* table_rows;  // optional: query row r uses table row table_rows[r] (prefill tokens share a row)
+    int64_t n_table_rows;       // rows of `tables`; a table_rows entry outside [0, n) is flagged and row 0 is read
     const int32_t* seq_lens;
     void* out;
     int q_dtype, kv_dtype;
@@ -175,6 +176,19 @@ struct DecodeArgs {
     // whose partial sits in the chunk slot right after the request's own chunks; this launch covers the rest.
     int prefix_tokens;
 };
+
+// Table row of batch position `req`: the position itself, or table_rows[req] when the caller
+// maps positions onto rows of a larger (device-resident) table.  A row outside the table is
+// flagged like a bad block id and row 0 is read instead, so no address leaves the table.
+__device__ __forceinline__ int64_t decode_table_row(const DecodeArgs& a, int req, int* status) {
+    if (!a.table_rows) return req;
+    int64_t row = a.table_rows[req];
+    if (row < 0 || row >= a.n_table_rows) {
+        if (status && threadIdx.x == 0) atomicOr(status, SFB_STATUS_BAD_BLOCK_ID);
+        row = 0;
+    }
+    return row;
+}
 
 int launch_decode_generic(const DecodeArgs& a, cudaStream_t stream);
 int launch_decode_combine(const DecodeArgs& a, cudaStream_t stream);

@@ -42,6 +42,7 @@ def paged_attention_decode(
     chunk_tokens: int = 0,
     workspace: torch.Tensor | None = None,
     out: torch.Tensor | None = None,
+    table_rows: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """Decode attention of ``q [B,H,D]`` over a paged pool ``[NB,bs,Hkv,D]``.
 
@@ -49,7 +50,9 @@ def paged_attention_decode(
     the device.  An e4m3 pool (uint8 or float8_e4m3fn) needs ``k_scale`` /
     ``v_scale`` float32 ``[NB,Hkv]``.  ``workspace`` (uint8) is allocated when
     the split needs one and none is given; pass a persistent one in a serving
-    loop (size from :func:`decode_workspace_bytes`)."""
+    loop (size from :func:`decode_workspace_bytes`).  With ``table_rows`` (int32 ``[B]``) batch
+    position r reads row ``table_rows[r]`` of ``block_tables`` (device-resident tables of
+    :class:`llm_compileforge_b200.block_manager.BlockManager`)."""
     lib = _lib.load()
     fp8 = k_scale is not None
     kc, vc = (_as_codes(k_cache), _as_codes(v_cache)) if fp8 else (k_cache, v_cache)
@@ -64,7 +67,7 @@ def paged_attention_decode(
         raise ValueError(f"decode workspace holds {workspace.numel() * workspace.element_size()} B, {need} needed")
     check(lib.sfb_paged_attention_decode(
         desc(q, "q"), desc(kc, "k_cache"), desc(vc, "v_cache"), desc(k_scale, "k_scale"), desc(v_scale, "v_scale"),
-        desc(block_tables, "block_tables"), desc(seq_lens, "seq_lens"), desc(out, "out"),
+        desc(block_tables, "block_tables"), desc(seq_lens, "seq_lens"), desc(table_rows, "table_rows"), desc(out, "out"),
         dtype_code(q.dtype), kv_code, float(scale) if scale is not None else 0.0, int(chunk_tokens),
         workspace.data_ptr(), workspace.numel() * workspace.element_size(), current_stream(q.device),
     ))

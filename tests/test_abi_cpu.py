@@ -61,7 +61,7 @@ def _fake_desc(shape, elem, device=_lib.SFB_DEVICE_CUDA, ptr=0x1000, strides=Non
 
 def _decode(lib, q, k, v, t, l, o, qd=_lib.SFB_BF16, kvd=_lib.SFB_BF16, ks=None, vs=None, ws=None, ws_bytes=0):
     r = lambda x: None if x is None else ctypes.byref(x)
-    return lib.sfb_paged_attention_decode(r(q), r(k), r(v), r(ks), r(vs), r(t), r(l), r(o), qd, kvd, 0.0, 0, ws, ws_bytes, None)
+    return lib.sfb_paged_attention_decode(r(q), r(k), r(v), r(ks), r(vs), r(t), r(l), None, r(o), qd, kvd, 0.0, 0, ws, ws_bytes, None)
 
 
 def test_decode_argument_validation():
@@ -88,7 +88,7 @@ def test_decode_argument_validation():
     assert _decode(lib, q, k8, k8, t, l, o, kvd=_lib.SFB_F8E4M3) == _lib.SFB_ERR_INVALID_ARG
     # split needs a workspace: 4 blocks * 16 = 64 tokens > chunk 16
     r = ctypes.byref
-    rc = lib.sfb_paged_attention_decode(r(q), r(k), r(k), None, None, r(t), r(l), r(o), _lib.SFB_BF16, _lib.SFB_BF16,
+    rc = lib.sfb_paged_attention_decode(r(q), r(k), r(k), None, None, r(t), r(l), None, r(o), _lib.SFB_BF16, _lib.SFB_BF16,
                                         0.0, 16, None, 0, None)
     assert rc == _lib.SFB_ERR_WORKSPACE
     assert lib.sfb_status_string(rc) == b"workspace missing or too small"
@@ -179,5 +179,5 @@ def test_static_scratch_size_check_needs_no_gpu():
     k = _fake_desc((4, 16, 8, 128), 2)
     t = _fake_desc((4096, 2), 4)
     lens = _fake_desc((4096,), 4)
-    rc = fn(r(q), r(k), r(k), None, None, r(t), r(lens), r(q), _lib.SFB_BF16, _lib.SFB_BF16, ctypes.c_float(0.0), ctypes.c_int64(16), None)
+    rc = fn(r(q), r(k), r(k), None, None, r(t), r(lens), None, r(q), _lib.SFB_BF16, _lib.SFB_BF16, ctypes.c_float(0.0), ctypes.c_int64(16), None)
     assert rc == _lib.SFB_ERR_WORKSPACE and b"built-in array" in lib.sfb_last_error()

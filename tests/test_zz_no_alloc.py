@@ -24,9 +24,9 @@ def _static_decode(q, k, v, tables, lens, chunk, k_scale=None, v_scale=None, kv_
     lib = _lib.load()
     fn = lib.sfb_paged_attention_decode_static
     fn.restype = ctypes.c_int
-    fn.argtypes = [ctypes.POINTER(_lib.SFBTensor)] * 8 + [ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_int64, ctypes.c_void_p]
+    fn.argtypes = [ctypes.POINTER(_lib.SFBTensor)] * 9 + [ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_int64, ctypes.c_void_p]
     out = torch.empty_like(q)
-    rc = fn(desc(q), desc(k), desc(v), desc(k_scale), desc(v_scale), desc(tables), desc(lens), desc(out),
+    rc = fn(desc(q), desc(k), desc(v), desc(k_scale), desc(v_scale), desc(tables), desc(lens), None, desc(out),
             dtype_code(q.dtype), kv_code if kv_code is not None else dtype_code(k.dtype), 0.0, chunk,
             torch.cuda.current_stream().cuda_stream)
     return rc, out
