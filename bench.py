@@ -15,9 +15,11 @@ One step = one decode iteration of the hot path: quantise-on-append of one new
 token per request into the paged FP8 pool, then paged attention of one query
 token per request over the pool (split-K kernel, partial results merged in-kernel).  ``value`` is decode
 tokens/s with every input already in HBM; ``e2e`` is the same step driven
-through the HAL ``OpExecutor`` with host (pinned) inputs: q, new K/V, block
-tables and lengths are copied to the device and the attention output back to
-the host inside the timed region.  The KV pool is device state, as in serving.
+through ``AttentionStepPipeline`` with host (pinned) inputs: every step q, new
+K/V and positions are copied to the device, the block tables are grown on the
+host and their delta sent, and the attention output is copied back to the host,
+all inside the timed region, two steps in flight (one-step-at-a-time figure
+beside it).  The KV pool and the block tables are device state, as in serving.
 
 Inputs are synthetic (seeded); the 22.7 GB code pool is far larger than L2, so
 no flush is needed between steps.
@@ -180,13 +182,17 @@ class DecodeState:
         self.batch = len(self.lengths)
         extra = -(-(steps_total + 1) // bs) + 1  # room for the tokens appended while benchmarking
         self.n_blocks = wl.pool_blocks_for(shape, self.lengths, extra)
-        tables = wl.random_tables(self.lengths, self.n_blocks, 1005 + shape.index + seed_offset, bs, extra)
-        width = max(len(t) for t in tables.values())
-        dense = torch.zeros((self.batch, width), dtype=torch.int32)
-        for i, t in enumerate(tables.values()):
-            dense[i, : len(t)] = torch.as_tensor(t, dtype=torch.int32)
-        self.tables_host = dense.pin_memory()
-        self.tables = dense.to(dev)
+        # Block placement: the block manager hands out ids from a free list left in a seeded random order (a pool that
+        # has served and released other requests), request i owns row i of the device-resident tables.  Tables cover
+        # the device-timed pass up front; the end-to-end pass grows them step by step like a live engine.
+        self.bm = _shuffled_block_manager(self.n_blocks, bs, 1005 + shape.index + seed_offset)
+        width = max(wl.blocks_for(n, bs) for n in self.lengths) + extra
+        self.tables = self.bm.attach_device_tables(self.batch, width, dev)
+        self.rids = [f"req_{i}" for i in range(self.batch)]
+        for rid, n in zip(self.rids, self.lengths):
+            self.bm.allocate(rid, n + steps_total // 3 + 2)
+        assert [self.bm.row(r) for r in self.rids] == list(range(self.batch))
+        self.bm.sync(torch.cuda.current_stream(dev))
         kv_dtype = torch.uint8 if self.fp8 else shape.dtype
         self.k_cache = torch.zeros((self.n_blocks, bs, hkv, d), dtype=kv_dtype, device=dev)
         self.v_cache = torch.zeros_like(self.k_cache)
@@ -231,6 +237,22 @@ class DecodeState:
         e = 2 if s.dtype in (torch.bfloat16, torch.float16) else 4
         return wl.decode_algorithmic_bytes(lens, s.n_heads, s.n_kv_heads, s.head_dim, 1 if self.fp8 else e, e, e, self.fp8,
                                            s.block_size)
+
+
+def _shuffled_block_manager(n_blocks: int, block_size: int, seed: int):
+    """A block manager whose free list is a seeded permutation of the pool: take every block, give each a second
+    holder, drop the request, then release the blocks one by one in permuted order."""
+    from llm_compileforge_b200.block_manager import BlockManager
+
+    bm = BlockManager(n_blocks, block_size)
+    bm.allocate("_all", n_blocks * block_size)
+    for b in range(n_blocks):
+        bm.increment_ref_count(b)
+    bm.free("_all")
+    for b in torch.randperm(n_blocks, generator=torch.Generator().manual_seed(seed)).tolist():
+        bm.free_block(b)
+    assert bm.num_free_blocks() == n_blocks
+    return bm
 
 
 def _rank_lengths(shape: wl.DecodeShape, batch: int | None, offset: int) -> list[int]:
@@ -358,8 +380,8 @@ def main() -> None:
 
         shape = dataclasses.replace(shape, n_heads=shape.n_heads // world, n_kv_heads=shape.n_kv_heads // world)
     total_steps = args.warmup + args.steps
-    # two passes (device-resident, then end-to-end) each append `total_steps` tokens
-    st = DecodeState(shape, args.batch or shape.batch, 2 * total_steps + 2, dev, seed_offset=0 if by_head else rank * 100)
+    # three passes (device-resident, end-to-end one step at a time, end-to-end pipelined) each append `total_steps` tokens
+    st = DecodeState(shape, args.batch or shape.batch, 3 * total_steps + 2, dev, seed_offset=0 if by_head else rank * 100)
     chunk = pick_chunk_tokens(st.lengths, args.chunk_tokens)
     ws_bytes = ops.decode_workspace_bytes(st.batch, shape.n_heads, shape.head_dim, st.tables.shape[1], shape.block_size, chunk)
     workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)
@@ -404,44 +426,51 @@ def main() -> None:
     decode_ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps  # the decode call: status memset + decode kernel
     status = ops.read_status(workspace)
 
-    # ---- end-to-end through the HAL executor with host buffers --------------------
+    # ---- end to end: host buffers in, host result out, through the step pipeline -----------
+    # Every step copies q, new K, new V and positions from pinned host memory, grows the block tables on the host,
+    # sends the table delta, appends, attends, and copies the result back to pinned host memory.  Two passes:
+    # one step at a time (submit, then wait for its result), then with two steps in flight.
+    from llm_compileforge_b200.step_pipeline import AttentionStepPipeline
+
     host_q = st.q.cpu().pin_memory()
     host_k, host_v = st.new_k.cpu().pin_memory(), st.new_v.cpu().pin_memory()
-    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    h2d = (host_q.numel() * host_q.element_size() + 2 * host_k.numel() * host_k.element_size()
-           + st.tables_host.numel() * 4 + 2 * st.batch * 4)
-    d2h = host_out.numel() * host_out.element_size()
+    pipe = AttentionStepPipeline(st.bm, st.k_cache, st.v_cache, max_batch=st.batch, n_heads=shape.n_heads, dtype=shape.dtype,
+                                 chunk_tokens=chunk, depth=2, **fp8kw, **tailkw)
+    sync_all()
 
-    def step_e2e(s: int) -> None:
-        q_d = host_q.to(dev, non_blocking=True)
-        k_d = host_k.to(dev, non_blocking=True)
-        v_d = host_v.to(dev, non_blocking=True)
-        tab = st.tables_host.to(dev, non_blocking=True)
-        pos = st.pos_steps_host[s].to(dev, non_blocking=True)
-        lens = st.len_steps_host[s].to(dev, non_blocking=True)
-        be.execute("cache_write", [k_d, v_d, pos], k_cache=st.k_cache, v_cache=st.v_cache, block_tables=tab,
-                   **fp8kw, **tailkw)
-        o = be.execute("paged_attention", [q_d, st.k_cache, st.v_cache, tab], seq_lens=lens, chunk_tokens=chunk,
-                       workspace=workspace, **fp8kw)
-        host_out.copy_(o, non_blocking=True)
-        torch.cuda.current_stream(dev).synchronize()  # the caller needs the result before the next step
+    def run_e2e(first: int, n: int, in_flight: int) -> tuple[float, int, int]:
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        h2d = d2h = 0
+        t0.record()
+        pending: list[int] = []
+        for i in range(n):
+            pending.append(pipe.submit(st.rids, host_q, host_k, host_v, st.pos_steps_host[first + i]))
+            h2d += pipe.h2d_bytes
+            d2h += pipe.d2h_bytes
+            if len(pending) >= in_flight:
+                pipe.result(pending.pop(0))  # the caller reads every step's result on the host
+        while pending:
+            pipe.result(pending.pop(0))
+        t1.record()
+        torch.cuda.synchronize(dev)
+        return t0.elapsed_time(t1), h2d // max(n, 1), d2h // max(n, 1)
 
     off = total_steps
-    for s in range(args.warmup):
-        step_e2e(off + s)
+    run_e2e(off, args.warmup, 1)
     sync_all()
-    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e_start.record()
-    for i in range(args.steps):
-        step_e2e(off + args.warmup + i)
-    e_end.record()
+    serial_ms, _, _ = run_e2e(off + args.warmup, args.steps, 1)
     sync_all()
-    e2e_ms = e_start.elapsed_time(e_end)
+    off += total_steps
+    run_e2e(off, args.warmup, 2)
+    sync_all()
+    e2e_ms, h2d, d2h = run_e2e(off + args.warmup, args.steps, 2)
+    sync_all()
+    status |= pipe.status()
 
     if world > 1:
-        t = torch.tensor([elapsed_ms, e2e_ms, decode_ms], dtype=torch.float64, device=dev)
+        t = torch.tensor([elapsed_ms, e2e_ms, decode_ms, serial_ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_ms, decode_ms = t.tolist()
+        elapsed_ms, e2e_ms, decode_ms, serial_ms = t.tolist()
         tot = torch.tensor([st.batch], dtype=torch.int64, device=dev)
         dist.all_reduce(tot)
         total_requests = st.batch if by_head else int(tot.item())
@@ -464,7 +493,9 @@ def main() -> None:
                          "kernel": "decode_tma_kernel (split-K, in-kernel merge)", "algorithmic_bytes_per_launch": alg,
                          "avg_launch_ms": decode_ms},
             "e2e": {"value": total_requests / (e2e_ms / args.steps / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h},
+                    "d2h_bytes_per_step": d2h, "steps_in_flight": 2,
+                    "one_step_at_a_time": total_requests / (serial_ms / args.steps / 1e3),
+                    "table_upload": "device-resident tables; only ids of added blocks are sent"},
             "gpu_launches": args.steps * 2,  # per step: cache_write_kernel + decode_tma_kernel (split merge is in-kernel)
             "clocks": clocks.summary(),
             "device_status": status,

@@ -197,6 +197,9 @@ SFB_API int sfb_read_status_static(int32_t* bits, void* stream);
  *                    caller, read and updated by this call
  *   tail_rows        [B] int32 or NULL: request r's tail copy is row tail_rows[r]
  *                    (a stable slot while batch order changes); NULL = row r
+ *   table_rows       [B] int32 or NULL: request r's table is row table_rows[r] of
+ *                    block_tables (which may then have any number of rows); NULL = row r.
+ *                    A request whose table or tail row lies outside its array is skipped.
  *
  * Token at position p goes to slot (table[p / bs], p % bs) (cache_manager.py:154-159).
  * FP8: after the call every touched (block, kv_head) slice holds exactly
@@ -206,8 +209,8 @@ SFB_API int sfb_read_status_static(int32_t* bits, void* stream);
 SFB_API int sfb_cache_write(const SFBTensor* k_new, const SFBTensor* v_new, const SFBTensor* cu_tokens,
                     const SFBTensor* start_pos, const SFBTensor* block_tables, SFBTensor* k_cache,
                     SFBTensor* v_cache, SFBTensor* k_scale, SFBTensor* v_scale, SFBTensor* k_tail,
-                    SFBTensor* v_tail, const SFBTensor* tail_rows, int src_dtype, int kv_dtype,
-                    int64_t max_new_tokens, void* stream);
+                    SFBTensor* v_tail, const SFBTensor* tail_rows, const SFBTensor* table_rows,
+                    int src_dtype, int kv_dtype, int64_t max_new_tokens, void* stream);
 
 /* ── Chunked prefill over the paged pool ────────────────────────────────────
  * Replaces kernels/flash_attention.py:179-202 `flash_attention_fwd` (CPU path
@@ -297,7 +300,8 @@ SFB_API int sfb_rms_norm(const SFBTensor* x, const SFBTensor* residual, const SF
  *
  * sfb_bm_attach_device_tables gives the manager a device array
  * int32 [rows, max_blocks]; every request then owns a stable row (sfb_bm_row)
- * and sfb_bm_sync uploads only entries changed since the last sync.  Pass that
+ * and sfb_bm_sync sends only entries changed since the last sync (one scatter kernel
+ * on the given stream, reading pinned host memory; asynchronous).  Pass that
  * array as `block_tables` and the requests' rows as `table_rows` to the decode
  * entry points.  Negative returns are SFBStatus values (SFB_ERR_OUT_OF_BLOCKS for
  * the reference's OutOfMemoryError). */
@@ -310,6 +314,8 @@ SFB_API void sfb_bm_free(SFBBlockManager* bm, const char* request_id);
 SFB_API void sfb_bm_free_block(SFBBlockManager* bm, int64_t block_id);
 SFB_API int sfb_bm_assign_cached_blocks(SFBBlockManager* bm, const char* request_id, const int32_t* block_ids, int64_t n);
 SFB_API int sfb_bm_ensure_blocks(SFBBlockManager* bm, const char* request_id, int64_t target_tokens);
+SFB_API int sfb_bm_ensure_blocks_batch(SFBBlockManager* bm, const char* const* request_ids, const int64_t* target_tokens,
+                                       int64_t n);
 SFB_API int64_t sfb_bm_share_prefix(SFBBlockManager* bm, const char* src_request_id, const char* dst_request_id,
                                     int64_t prefix_len);
 SFB_API void sfb_bm_increment_ref_count(SFBBlockManager* bm, int64_t block_id);

@@ -104,7 +104,7 @@ def load() -> ctypes.CDLL:
     lib.sfb_read_status.restype = c_int
     lib.sfb_read_status.argtypes = [c_void_p, POINTER(c_int32), c_void_p]
     lib.sfb_cache_write.restype = c_int
-    lib.sfb_cache_write.argtypes = [_T] * 12 + [c_int, c_int, c_int64, c_void_p]
+    lib.sfb_cache_write.argtypes = [_T] * 13 + [c_int, c_int, c_int64, c_void_p]
     lib.sfb_quantize_fp8.restype = c_int
     lib.sfb_quantize_fp8.argtypes = [_T, _T, _T, c_int, c_int, c_void_p]
     lib.sfb_dequantize_fp8.restype = c_int
@@ -138,6 +138,7 @@ def _block_manager_protos(lib: ctypes.CDLL) -> None:
         "sfb_bm_free_block": (None, [h, c_int64]),
         "sfb_bm_assign_cached_blocks": (c_int, [h, s, i32p, c_int64]),
         "sfb_bm_ensure_blocks": (c_int, [h, s, c_int64]),
+        "sfb_bm_ensure_blocks_batch": (c_int, [h, POINTER(c_char_p), POINTER(c_int64), c_int64]),
         "sfb_bm_share_prefix": (c_int64, [h, s, s, c_int64]),
         "sfb_bm_increment_ref_count": (None, [h, c_int64]),
         "sfb_bm_ref_count": (c_int64, [h, c_int64]),

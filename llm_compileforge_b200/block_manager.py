@@ -83,6 +83,23 @@ class BlockManager:
         if rc < 0:
             _raise(rc)
 
+    def ensure_blocks_batch(self, request_ids: Sequence[str], target_tokens: "Sequence[int] | torch.Tensor") -> None:
+        """``ensure_blocks`` for every request of a step in one call (the scheduler's
+        pre-step growth, runtime/src/engine/scheduler.rs:239-246)."""
+        n = len(request_ids)
+        key = tuple(request_ids)
+        if getattr(self, "_batch_key", None) != key:  # the id array is rebuilt only when the batch changes
+            self._batch_key = key
+            self._batch_ids = (ctypes.c_char_p * max(n, 1))(*[r.encode() for r in request_ids])
+        if isinstance(target_tokens, torch.Tensor):
+            t64 = target_tokens.to(dtype=torch.int64, device="cpu").contiguous()
+            targets = ctypes.cast(ctypes.c_void_p(t64.data_ptr()), ctypes.POINTER(ctypes.c_int64))
+        else:
+            targets = (ctypes.c_int64 * max(n, 1))(*[int(t) for t in target_tokens])
+        rc = self._lib.sfb_bm_ensure_blocks_batch(self._h, self._batch_ids, targets, n)
+        if rc < 0:
+            _raise(rc)
+
     def share_prefix(self, src_request_id: str, dst_request_id: str, prefix_len: int) -> list[int]:
         n = self._lib.sfb_bm_share_prefix(self._h, src_request_id.encode(), dst_request_id.encode(), int(prefix_len))
         if n < 0:

@@ -353,7 +353,8 @@ int sfb_read_status(const void* workspace, int32_t* bits, void* stream) {
 int sfb_cache_write(const SFBTensor* k_new, const SFBTensor* v_new, const SFBTensor* cu_tokens,
                     const SFBTensor* start_pos, const SFBTensor* block_tables, SFBTensor* k_cache, SFBTensor* v_cache,
                     SFBTensor* k_scale, SFBTensor* v_scale, SFBTensor* k_tail, SFBTensor* v_tail,
-                    const SFBTensor* tail_rows, int src_dtype, int kv_dtype, int64_t max_new_tokens, void* stream) {
+                    const SFBTensor* tail_rows, const SFBTensor* table_rows, int src_dtype, int kv_dtype,
+                    int64_t max_new_tokens, void* stream) {
     const int se = dtype_size(src_dtype), kve = dtype_size(kv_dtype);
     if (!se || src_dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "cache_write: source dtype %d", src_dtype);
     if (!kve) return fail(SFB_ERR_INVALID_ARG, "cache_write: pool dtype %d", kv_dtype);
@@ -370,7 +371,13 @@ int sfb_cache_write(const SFBTensor* k_new, const SFBTensor* v_new, const SFBTen
     if ((rc = make_view(v_cache, "v_cache", 4, 4, kve, &vc))) return rc;
     const int64_t B = sp.size[3], Hkv = kc.size[2], D = kc.size[3], bs = kc.size[1];
     if (cu.size[3] != B + 1) return fail(SFB_ERR_INVALID_ARG, "cache_write: cu_tokens must have batch+1 = %lld entries", (long long)(B + 1));
-    if (bt.size[2] != B) return fail(SFB_ERR_INVALID_ARG, "cache_write: block_tables rows != batch");
+    View trw;
+    if (table_rows) {
+        if ((rc = make_view(table_rows, "table_rows", 1, 1, 4, &trw))) return rc;
+        if (trw.size[3] != B) return fail(SFB_ERR_INVALID_ARG, "cache_write: table_rows must have one entry per request");
+    } else if (bt.size[2] != B) {
+        return fail(SFB_ERR_INVALID_ARG, "cache_write: block_tables rows != batch");
+    }
     for (int i = 0; i < 4; ++i)
         if (kc.size[i] != vc.size[i]) return fail(SFB_ERR_INVALID_ARG, "cache_write: k_cache and v_cache shapes differ");
     if (kn.size[2] != Hkv || kn.size[3] != D || vn.size[2] != Hkv || vn.size[3] != D || vn.size[1] != kn.size[1])
@@ -387,6 +394,8 @@ int sfb_cache_write(const SFBTensor* k_new, const SFBTensor* v_new, const SFBTen
     a.tables = reinterpret_cast<const int32_t*>(bt.base);
     a.table_stride = bt.stride[2];
     a.max_blocks = (int)bt.size[3];
+    a.table_rows = table_rows ? reinterpret_cast<const int32_t*>(trw.base) : nullptr;
+    a.n_table_rows = bt.size[2];
     a.k_cache = kc.base; a.v_cache = vc.base;
     a.src_dtype = src_dtype; a.kv_dtype = kv_dtype;
     a.batch = (int)B; a.n_kv_heads = (int)Hkv; a.head_dim = (int)D; a.block_size = (int)bs;
@@ -417,6 +426,7 @@ int sfb_cache_write(const SFBTensor* k_new, const SFBTensor* v_new, const SFBTen
         a.ks_stride[0] = ks.stride[2]; a.ks_stride[1] = ks.stride[3];
         a.vs_stride[0] = vs.stride[2]; a.vs_stride[1] = vs.stride[3];
         a.k_tail = kt.base; a.v_tail = vt.base;
+        a.n_tail_rows = kt.size[0];
         for (int i = 0; i < 3; ++i) { a.kt_stride[i] = kt.stride[i]; a.vt_stride[i] = vt.stride[i]; }
     }
     return launch_cache_write(a, static_cast<cudaStream_t>(stream));

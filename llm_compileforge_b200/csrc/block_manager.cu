@@ -40,12 +40,34 @@ struct SFBBlockManager {
     int32_t* d_tables = nullptr;
     int64_t rows = 0, max_blocks = 0;
     std::vector<int64_t> free_rows;
-    std::vector<int32_t> staging;  // keeps upload sources alive until the copies were issued
+    // Changed entries travel as (flat index, block id) pairs in pinned host memory that the
+    // scatter kernel reads in place; two buffers alternate so that filling one never waits
+    // for the kernel that is still reading the other.
+    struct Staging {
+        int2* host = nullptr;
+        int64_t capacity = 0;
+        cudaEvent_t done = nullptr;
+    } staging[2];
+    int next_staging = 0;
+    ~SFBBlockManager() {
+        for (auto& st : staging) {
+            if (st.done) { cudaEventSynchronize(st.done); cudaEventDestroy(st.done); }
+            if (st.host) cudaFreeHost(st.host);
+        }
+    }
 };
 
 using namespace sfb;
 
 namespace {
+
+__global__ void table_scatter_kernel(const int2* __restrict__ pairs, int64_t n, int32_t* __restrict__ tables) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const int2 p = pairs[i];
+        tables[p.x] = p.y;
+    }
+}
 
 int oom(const SFBBlockManager* bm, int64_t needed) {
     return fail(SFB_ERR_OUT_OF_BLOCKS, "OutOfMemory: need %lld blocks but only %lld free (total pool: %lld)", (long long)needed,
@@ -89,7 +111,8 @@ SFBBlockManager* sfb_bm_create(int64_t num_blocks, int64_t block_size) {
 void sfb_bm_destroy(SFBBlockManager* bm) { delete bm; }
 
 int sfb_bm_attach_device_tables(SFBBlockManager* bm, void* d_tables, int64_t rows, int64_t max_blocks) {
-    if (!bm || !d_tables || rows <= 0 || max_blocks <= 0) return fail(SFB_ERR_INVALID_ARG, "block manager: bad device table arguments");
+    if (!bm || !d_tables || rows <= 0 || max_blocks <= 0 || rows > 0x7fffffffLL / max_blocks)
+        return fail(SFB_ERR_INVALID_ARG, "block manager: bad device table arguments");
     if (!bm->requests.empty()) return fail(SFB_ERR_INVALID_ARG, "block manager: attach the device tables before the first allocation");
     bm->d_tables = static_cast<int32_t*>(d_tables);
     bm->rows = rows;
@@ -224,26 +247,48 @@ int64_t sfb_bm_row(const SFBBlockManager* bm, const char* rid) {
     return it == bm->requests.end() ? -1 : it->second.row;
 }
 
-// Uploads every table entry that changed since the previous sync; returns the number of int32 entries sent.
+// block.rs:236-268 for a whole batch: the same as n calls in order; stops at the first failure (its index is in the message).
+int sfb_bm_ensure_blocks_batch(SFBBlockManager* bm, const char* const* rids, const int64_t* target_tokens, int64_t n) {
+    if (!bm || n < 0 || (n > 0 && (!rids || !target_tokens))) return fail(SFB_ERR_INVALID_ARG, "block manager: bad ensure_blocks_batch arguments");
+    for (int64_t i = 0; i < n; ++i) {
+        const int rc = sfb_bm_ensure_blocks(bm, rids[i], target_tokens[i]);
+        if (rc) return rc;
+    }
+    return SFB_OK;
+}
+
+// Sends every table entry that changed since the previous sync to the device tables, as ONE kernel launch on
+// `stream` that scatters (index, id) pairs out of pinned host memory.  Asynchronous: it only ever waits for the
+// launch issued two syncs earlier (the one that last read the staging buffer it is about to refill).
+// Returns the number of int32 entries sent.
 int64_t sfb_bm_sync(SFBBlockManager* bm, void* stream) {
     if (!bm || !bm->d_tables) return fail(SFB_ERR_INVALID_ARG, "block manager: no device tables attached");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int64_t total = 0;
-    for (auto& kv : bm->requests) total += std::max<int64_t>(0, (int64_t)kv.second.table.size() - kv.second.dirty_lo);
-    // one staging buffer, so that sources stay valid after this call returns
-    bm->staging.clear();
-    bm->staging.reserve((size_t)total);
+    for (auto& kv : bm->requests)
+        if (kv.second.row >= 0) total += std::max<int64_t>(0, (int64_t)kv.second.table.size() - kv.second.dirty_lo);
+    if (total == 0) return 0;
+    auto& buf = bm->staging[bm->next_staging];
+    bm->next_staging ^= 1;
+    if (buf.done) SFB_CUDA_CHECK(cudaEventSynchronize(buf.done));
+    else SFB_CUDA_CHECK(cudaEventCreateWithFlags(&buf.done, cudaEventDisableTiming));
+    if (buf.capacity < total) {
+        if (buf.host) SFB_CUDA_CHECK(cudaFreeHost(buf.host));
+        buf.host = nullptr;
+        buf.capacity = std::max<int64_t>(total, std::max<int64_t>(4096, 2 * buf.capacity));
+        SFB_CUDA_CHECK(cudaMallocHost(&buf.host, (size_t)buf.capacity * sizeof(int2)));
+    }
+    int64_t at = 0;
     for (auto& kv : bm->requests) {
         Request& r = kv.second;
-        const int64_t n = (int64_t)r.table.size() - r.dirty_lo;
-        if (n <= 0 || r.row < 0) continue;
-        const size_t at = bm->staging.size();
-        bm->staging.insert(bm->staging.end(), r.table.begin() + r.dirty_lo, r.table.end());
-        SFB_CUDA_CHECK(cudaMemcpyAsync(bm->d_tables + r.row * bm->max_blocks + r.dirty_lo, bm->staging.data() + at, (size_t)n * 4,
-                                       cudaMemcpyHostToDevice, st));
+        if (r.row < 0) continue;
+        const int64_t base = r.row * bm->max_blocks;
+        for (int64_t c = r.dirty_lo; c < (int64_t)r.table.size(); ++c) buf.host[at++] = make_int2((int)(base + c), r.table[(size_t)c]);
         r.dirty_lo = (int64_t)r.table.size();
     }
-    if (total > 0) SFB_CUDA_CHECK(cudaStreamSynchronize(st));  // pageable staging: finish before the buffer is reused
+    table_scatter_kernel<<<(unsigned)ceil_div(total, (int64_t)256), 256, 0, st>>>(buf.host, total, bm->d_tables);
+    SFB_CUDA_CHECK(cudaGetLastError());
+    SFB_CUDA_CHECK(cudaEventRecord(buf.done, st));
     return total;
 }
 

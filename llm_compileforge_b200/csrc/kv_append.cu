@@ -193,6 +193,12 @@ __global__ void __launch_bounds__(kThreads) cache_write_kernel(AppendArgs a) {
     const int64_t src_tok = which ? a.vnew_stride[0] : a.new_stride[0];
     const int64_t src_head = which ? a.vnew_stride[1] : a.new_stride[1];
     const int64_t* ps = which ? a.v_stride : a.k_stride;
+    // rows of the table / tail arrays this request uses; a row outside either array skips the request
+    const int64_t trow = a.table_rows ? a.table_rows[req] : req;
+    if (trow < 0 || trow >= a.n_table_rows) return;
+    const int32_t* table = a.tables + trow * a.table_stride;
+    const int64_t tail_row = a.tail_rows ? a.tail_rows[req] : req;
+    if (FP8 && (tail_row < 0 || tail_row >= a.n_tail_rows)) return;
     const int cpr = dim / N;            // chunks per row
     const int n_chunks = bs * cpr;
 
@@ -209,7 +215,7 @@ __global__ void __launch_bounds__(kThreads) cache_write_kernel(AppendArgs a) {
 
     if constexpr (!FP8) {
         for (; blk <= last_blk; blk += blk_step) {
-            const int64_t phys = a.tables[(int64_t)req * a.table_stride + blk];
+            const int64_t phys = table[blk];
             if (phys < 0 || phys >= a.n_pool_blocks) continue;
             const int lo = blk * bs;
             ST* pool = reinterpret_cast<ST*>(which ? a.v_cache : a.k_cache) + phys * ps[0];
@@ -227,7 +233,7 @@ __global__ void __launch_bounds__(kThreads) cache_write_kernel(AppendArgs a) {
         float* scales = which ? a.v_scale : a.k_scale;
         const int64_t* ss = which ? a.vs_stride : a.ks_stride;
         const int64_t* ts = which ? a.vt_stride : a.kt_stride;
-        ST* tail = reinterpret_cast<ST*>(which ? a.v_tail : a.k_tail) + (int64_t)(a.tail_rows ? a.tail_rows[req] : req) * ts[0];
+        ST* tail = reinterpret_cast<ST*>(which ? a.v_tail : a.k_tail) + tail_row * ts[0];
         if (warp >= a.n_kv_heads) return;
 
         // The warp walks its (block, head) slices with the next slice's rows already in flight
@@ -251,7 +257,7 @@ __global__ void __launch_bounds__(kThreads) cache_write_kernel(AppendArgs a) {
             const bool more = nb <= last_blk;
             if (more) fetch(nb, nh, nxt);
 
-            const int64_t phys = a.tables[(int64_t)req * a.table_stride + blk];
+            const int64_t phys = table[blk];
             if (phys >= 0 && phys < a.n_pool_blocks) {
                 const int lo = blk * bs;
                 const bool still_open = end < lo + bs;  // this block keeps free slots after the call

@@ -212,6 +212,8 @@ struct AppendArgs {
     void* k_tail;
     void* v_tail;
     const int32_t* tail_rows;  // optional: request r's tail copy lives in row tail_rows[r] (stable slot across steps)
+    const int32_t* table_rows; // optional: request r's block table is row table_rows[r] of `tables`
+    int64_t n_table_rows, n_tail_rows;
     int src_dtype, kv_dtype;
     int batch, n_kv_heads, head_dim, block_size, max_new_tokens;
     int64_t n_pool_blocks;

@@ -101,9 +101,12 @@ def cache_write(
     k_tail: torch.Tensor | None = None,
     v_tail: torch.Tensor | None = None,
     tail_rows: torch.Tensor | None = None,
+    table_rows: torch.Tensor | None = None,
 ) -> None:
     """Scatter new K/V tokens ``[T,Hkv,D]`` into their paged slots; with scales
-    and tails given the pool holds e4m3 codes and the write quantises on append."""
+    and tails given the pool holds e4m3 codes and the write quantises on append.
+    ``table_rows`` / ``tail_rows`` (int32 ``[B]``) name each request's row of
+    ``block_tables`` / of the tails when those are stable per-request arrays."""
     lib = _lib.load()
     fp8 = k_scale is not None
     kc, vc = (_as_codes(k_cache), _as_codes(v_cache)) if fp8 else (k_cache, v_cache)
@@ -111,7 +114,7 @@ def cache_write(
         desc(k_new, "k_new"), desc(v_new, "v_new"), desc(cu_tokens, "cu_tokens"), desc(start_pos, "start_pos"),
         desc(block_tables, "block_tables"), desc(kc, "k_cache"), desc(vc, "v_cache"), desc(k_scale, "k_scale"),
         desc(v_scale, "v_scale"), desc(k_tail, "k_tail"), desc(v_tail, "v_tail"), desc(tail_rows, "tail_rows"),
-        dtype_code(k_new.dtype),
+        desc(table_rows, "table_rows"), dtype_code(k_new.dtype),
         _lib.SFB_F8E4M3 if fp8 else dtype_code(k_cache.dtype), int(max_new_tokens), current_stream(k_new.device),
     ))
 
