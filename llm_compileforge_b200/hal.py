@@ -65,6 +65,7 @@ class B200Backend(OpExecutor):
             "rms_norm": self._op_rms_norm,
             "fused_rms_norm_add": self._op_fused_rms_norm_add,
             "flash_attention": self._op_flash_attention,
+            "scaled_dot_product_attention": self._op_scaled_dot_product_attention,
             "chunked_prefill": self._op_chunked_prefill,
         }
 
@@ -145,6 +146,27 @@ class B200Backend(OpExecutor):
         kernels.flash_attention_fwd (``scale``, ``causal`` default True)."""
         return kernels_api.flash_attention_fwd(inputs[0], inputs[1], inputs[2], scale=kw.get("scale"),
                                                causal=kw.get("causal", kw.get("is_causal", True)))
+
+    def _op_scaled_dot_product_attention(self, inputs: list[Any], **kw: Any) -> torch.Tensor:
+        """Dense SDPA with the reference backend's keywords (pytorch_backend/_ops_attention.py:13-53):
+        ``[q, k, v(, attn_mask)]`` each ``[B,H,S,D]``, ``is_causal`` default False, ``scale``, ``dropout_p``.
+        As there, a floating-point (positional) mask given together with ``is_causal=True`` is dropped.
+        Calls that need an explicit mask, dropout or mixed sequence lengths under a causal mask go to the
+        fallback executor (``ValueError`` without one): the kernel masks by position only."""
+        q, k, v = inputs[:3]
+        mask = kw.get("attn_mask")
+        if mask is None and len(inputs) > 3:
+            mask = inputs[3]
+        causal = bool(kw.get("is_causal", False))
+        if mask is not None and mask.dtype.is_floating_point and causal:
+            mask = None
+        own = (mask is None and float(kw.get("dropout_p", 0.0)) == 0.0 and q.dim() == 4 and q.is_cuda
+               and not (causal and q.shape[2] != k.shape[2]) and q.shape[1] % k.shape[1] == 0)
+        if not own:
+            if self._fallback is None:
+                raise ValueError("scaled_dot_product_attention: explicit masks and dropout need a fallback executor")
+            return self._fallback.execute("scaled_dot_product_attention", inputs, **kw)
+        return kernels_api.flash_attention_fwd(q, k, v, scale=kw.get("scale"), causal=causal)
 
     def _op_chunked_prefill(self, inputs: list[Any], **kw: Any) -> torch.Tensor:
         """inputs ``[query [T,H,D], key_cache, value_cache, block_table [R,max_blocks]]``

@@ -98,3 +98,25 @@ def test_prefill_matches_decode_for_last_token(cuda):
     dec = pkg.paged_attention(last_q, dk, dv, pw.block_tables, pw.ctx_lens, scale=pw.scale)
     for i, r in enumerate(pw.block_tables):
         assert (out[r][-1].float() - dec[r].float()).abs().max() <= 2e-2
+
+
+def test_hal_scaled_dot_product_attention(cuda):
+    """HAL op of pytorch_backend/_ops_attention.py:13-53: no mask, is_causal, GQA, and the positional float mask that
+    the reference drops when is_causal=True; an explicit mask without a fallback executor is refused."""
+    g = torch.Generator().manual_seed(11)
+    be = pkg.B200Backend(device=cuda)
+    q = torch.randn((2, 8, 96, 128), generator=g).to(torch.bfloat16)
+    k = torch.randn((2, 2, 96, 128), generator=g).to(torch.bfloat16)
+    v = torch.randn((2, 2, 96, 128), generator=g).to(torch.bfloat16)
+    kx, vx = k.repeat_interleave(4, dim=1), v.repeat_interleave(4, dim=1)
+    for causal in (False, True):
+        got = be.execute("scaled_dot_product_attention", [q.to(cuda), k.to(cuda), v.to(cuda)], is_causal=causal, scale=0.11)
+        want = torch.nn.functional.scaled_dot_product_attention(q.float(), kx.float(), vx.float(), is_causal=causal, scale=0.11)
+        assert_half_close(got.cpu(), want.to(torch.bfloat16), what=f"sdpa causal={causal}")
+    pos = torch.arange(96, dtype=torch.float32).view(1, 1, 96, 1).expand(2, 1, 96, 1).to(cuda)
+    got = be.execute("scaled_dot_product_attention", [q.to(cuda), k.to(cuda), v.to(cuda), pos], is_causal=True)
+    want = torch.nn.functional.scaled_dot_product_attention(q.float(), kx.float(), vx.float(), is_causal=True)
+    assert_half_close(got.cpu(), want.to(torch.bfloat16), what="sdpa positional mask + is_causal")
+    with pytest.raises(ValueError):
+        be.execute("scaled_dot_product_attention", [q.to(cuda), k.to(cuda), v.to(cuda)],
+                   attn_mask=torch.ones((96, 96), dtype=torch.bool, device=cuda))
