@@ -203,6 +203,70 @@ def test_fp8_config3_sampled(cuda):
         assert_half_close(out[r].cpu(), want["x"], what=f"config 3 request {r}")
 
 
+def test_fp8_config5_full_sampled(cuda):
+    """Config 5 at full size on one GPU (2048 requests, ~11 M tokens, 22.7 GB of codes): whole sequences appended
+    group by group through quantise-on-append, one decode over everything; the oracle checks a seeded sample of
+    requests (codes and scales bit for bit, attention output within the half-precision tolerance), and two
+    size-independent properties hold for ALL requests: the output is finite, and it is a convex combination of
+    the request's dequantised V rows, so it lies inside their per-dimension [min, max] envelope (checked on the sample)."""
+    shape = wl.C5
+    lengths = wl.config_lengths(shape)
+    nb = wl.pool_blocks_for(shape, lengths)
+    tables = wl.random_tables(lengths, nb, 1005 + shape.index)
+    hkv, d, bs = shape.n_kv_heads, shape.head_dim, shape.block_size
+    b = len(lengths)
+    rids = list(tables)
+    dense, lens, _ = dense_block_tables(tables, {r: n for r, n in zip(rids, lengths)}, bs)
+    dense_d = dense.to(cuda)
+    kc = torch.zeros((nb, bs, hkv, d), dtype=torch.uint8, device=cuda)
+    vc = torch.zeros_like(kc)
+    ks = torch.ones((nb, hkv), dtype=torch.float32, device=cuda)
+    vs = torch.ones_like(ks)
+    kt = torch.zeros((b, bs, hkv, d), dtype=torch.bfloat16, device=cuda)
+    vt = torch.zeros_like(kt)
+    pick = sorted(torch.randperm(b, generator=torch.Generator().manual_seed(5))[:4].tolist())
+    kept = {}
+    group = 128
+    for lo in range(0, b, group):
+        ls = lengths[lo : lo + group]
+        gen = torch.Generator(device=cuda).manual_seed(500 + lo)
+        total = sum(ls)
+        newk = (torch.randn((total, hkv, d), generator=gen, device=cuda) * 2).to(torch.bfloat16)
+        newv = (torch.randn((total, hkv, d), generator=gen, device=cuda) * 2).to(torch.bfloat16)
+        cu = [0] + list(np.cumsum(ls))
+        ops.cache_write(newk, newv, torch.tensor(cu, dtype=torch.int32, device=cuda), torch.zeros(len(ls), dtype=torch.int32, device=cuda),
+                        dense_d[lo : lo + len(ls)], kc, vc, max_new_tokens=max(ls), k_scale=ks, v_scale=vs,
+                        k_tail=kt[lo : lo + len(ls)], v_tail=vt[lo : lo + len(ls)])
+        for r in pick:
+            if lo <= r < lo + len(ls):
+                kept[r] = (newk[cu[r - lo] : cu[r - lo + 1]].cpu(), newv[cu[r - lo] : cu[r - lo + 1]].cpu())
+        del newk, newv
+    q = torch.randn((b, shape.n_heads, d), generator=torch.Generator(device=cuda).manual_seed(9), device=cuda).to(torch.bfloat16)
+    out = ops.paged_attention_decode(q, kc, vc, dense_d, lens.to(cuda), k_scale=ks, v_scale=vs)
+    assert torch.isfinite(out).all()
+    for r in pick:
+        n = lengths[r]
+        table = tables[rids[r]]
+        local = list(range(len(table)))
+        pool_k = torch.zeros((len(table), bs, hkv, d), dtype=torch.bfloat16)
+        pool_v = torch.zeros_like(pool_k)
+        ref.cache_write(pool_k, kept[r][0], local, range(n))
+        ref.cache_write(pool_v, kept[r][1], local, range(n))
+        wkc, wks = ref.fp8_quantize_pool_fast(pool_k)
+        wvc, wvs = ref.fp8_quantize_pool_fast(pool_v)
+        ids = torch.as_tensor(table, device=cuda)
+        assert torch.equal(kc[ids].cpu(), wkc) and torch.equal(ks[ids].cpu(), wks)
+        assert torch.equal(vc[ids].cpu(), wvc) and torch.equal(vs[ids].cpu(), wvs)
+        v_deq = ref.fp8_dequantize_pool(wvc, wvs)
+        want = ref.paged_attention(q[r : r + 1].float().cpu(), ref.fp8_dequantize_pool(wkc, wks), v_deq, {"x": local}, {"x": n})
+        assert_half_close(out[r].cpu(), want["x"], what=f"config 5 request {r} (length {n})")
+        rows = v_deq.flatten(0, 1)[:n]  # [n, Hkv, D]
+        lo_env = rows.amin(0).repeat_interleave(shape.n_heads // hkv, 0) - 2e-2
+        hi_env = rows.amax(0).repeat_interleave(shape.n_heads // hkv, 0) + 2e-2
+        got = out[r].float().cpu()
+        assert bool(((got >= lo_env) & (got <= hi_env)).all()), "attention output outside the convex hull of V"
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 def test_append_division_is_exact_over_many_scales(cuda, dtype):
     """The append kernel divides through a reciprocal plus one FMA correction; the codes
