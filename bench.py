@@ -62,7 +62,9 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--workload", choices=["c5", "c3", "c2"], default="c5")
     p.add_argument("--batch", type=int, default=0, help="requests per GPU (0 = the configuration's batch)")
     p.add_argument("--chunk-tokens", type=int, default=0, help="KV split size (0 = heuristic)")
-    p.add_argument("--gather", action="store_true", help="all-gather the outputs over NCCL inside the step")
+    p.add_argument("--gather", nargs="?", const="nccl", default=None, choices=["nccl", "peer"],
+                   help="gather the outputs inside the step: nccl = all-gather after the decode; peer (head partition only) = "
+                        "the decode kernel stores its heads into every GPU's output over NVLink, then one signal kernel")
     p.add_argument("--partition", choices=["request", "head"], default="request",
                    help="request: every GPU serves its own requests (weak scaling, default); head: the configuration's "
                         "requests on every GPU with 1/N of the kv heads each (strong scaling, the 8-GPU layout of config 5)")
@@ -386,7 +388,14 @@ def main() -> None:
     ws_bytes = ops.decode_workspace_bytes(st.batch, shape.n_heads, shape.head_dim, st.tables.shape[1], shape.block_size, chunk)
     workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)
     out = torch.empty_like(st.q)
-    gathered = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device=dev) if (args.gather and world > 1) else None
+    gathered = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device=dev) if (args.gather == "nccl" and world > 1) else None
+    peer = None
+    if args.gather == "peer" and world > 1:
+        if not by_head:
+            raise SystemExit("--gather peer goes with --partition head")
+        from llm_compileforge_b200.comm import PeerGather
+
+        peer = PeerGather(st.batch, shape.n_heads, shape.head_dim, shape.dtype, dev)
     # (head partition: rank g's slab is heads [g*H/N, (g+1)*H/N) of every request; `gathered[g]` is that slab)
     be = B200Backend(device=dev)
     fp8kw = dict(k_scale=st.k_scale, v_scale=st.v_scale) if st.fp8 else {}
@@ -397,8 +406,11 @@ def main() -> None:
                         max_new_tokens=1, **fp8kw, **tailkw)
         if ev:
             ev[0].record()
-        ops.paged_attention_decode(st.q, st.k_cache, st.v_cache, st.tables, st.len_steps[s], scale=None,
-                                   chunk_tokens=chunk, workspace=workspace, out=out, **fp8kw)
+        if peer is not None:
+            peer.decode(st.q, st.k_cache, st.v_cache, st.tables, st.len_steps[s], chunk_tokens=chunk, workspace=workspace, **fp8kw)
+        else:
+            ops.paged_attention_decode(st.q, st.k_cache, st.v_cache, st.tables, st.len_steps[s], scale=None,
+                                       chunk_tokens=chunk, workspace=workspace, out=out, **fp8kw)
         if ev:
             ev[1].record()
         if gathered is not None:
@@ -414,6 +426,18 @@ def main() -> None:
     for s in range(args.warmup):
         step_device(s)
     sync_all()
+    gather_check = None
+    if peer is not None:
+        # the peer-stored output of the last warm-up step against decode + NCCL all-gather of the same step
+        ops.paged_attention_decode(st.q, st.k_cache, st.v_cache, st.tables, st.len_steps[args.warmup - 1], scale=None,
+                                   chunk_tokens=chunk, workspace=workspace, out=out, **fp8kw)
+        parts = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device=dev)
+        dist.all_gather_into_tensor(parts, out)
+        same = torch.equal(parts.permute(1, 0, 2, 3).reshape(peer.out.shape), peer.out) and not peer.timed_out()
+        flag = torch.tensor([int(same)], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        gather_check = "peer-stored output == decode + NCCL all-gather on every rank" if int(flag.item()) else "MISMATCH"
+        sync_all()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
@@ -496,10 +520,15 @@ def main() -> None:
                     "d2h_bytes_per_step": d2h, "steps_in_flight": 2,
                     "one_step_at_a_time": total_requests / (serial_ms / args.steps / 1e3),
                     "table_upload": "device-resident tables; only ids of added blocks are sent"},
-            "gpu_launches": args.steps * 2,  # per step: cache_write_kernel + decode_tma_kernel (split merge is in-kernel)
+            # per step: cache_write_kernel + decode_tma_kernel (split merge is in-kernel) (+ the peer signal kernel)
+            "gpu_launches": args.steps * (3 if peer is not None else 2),
             "clocks": clocks.summary(),
-            "device_status": status,
+            "device_status": status | (4 if (peer is not None and peer.timed_out()) else 0),
         }
+        if args.gather:
+            line["config"]["gather"] = args.gather
+        if gather_check:
+            line["gather_check"] = gather_check
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(shape, st.lengths, min(args.cpu_sample, st.batch), repeats=3)
         print(json.dumps(line), flush=True)

@@ -291,6 +291,35 @@ SFB_API int sfb_dequantize_fp8(const SFBTensor* codes, const SFBTensor* scales, 
 SFB_API int sfb_rms_norm(const SFBTensor* x, const SFBTensor* residual, const SFBTensor* weight, SFBTensor* out,
                  int dtype, float eps, void* stream);
 
+/* ── Head-partitioned decode with the output gathered in-kernel ─────────────────
+ * The reference's tensor-parallel attention ends in an all-gather of the per-rank
+ * heads through its Communicator (python_runtime/hal/communicator.py:17-72,
+ * runtime/src/comm/).  Here GPU `rank` of `world` (<= 8, one node) holds kv heads
+ * [rank*Hkv, (rank+1)*Hkv) of the pool and the matching H query heads, and the
+ * decode kernel stores its [B, H, D] result directly into heads [rank*H, (rank+1)*H)
+ * of EVERY GPU's [B, H*world, D] output (plain peer stores over NVLink; no TMA, no
+ * multicast).  `out_all` describes this GPU's copy; peer_out[p] is the base address
+ * of GPU p's copy (peer_out[rank] the local one; all copies have out_all's layout).
+ * The buffers must be mapped for peer access by the caller (CUDA IPC / symmetric
+ * memory).  Follow it on the same stream with sfb_peer_signal_wait: after that the
+ * local copy is complete.  Only the shapes of the TMA decode kernel are supported. */
+SFB_API int sfb_paged_attention_decode_gather(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
+                                              const SFBTensor* k_scale, const SFBTensor* v_scale,
+                                              const SFBTensor* block_tables, const SFBTensor* seq_lens,
+                                              const SFBTensor* table_rows, SFBTensor* out_all, void* const* peer_out,
+                                              int world, int rank, int q_dtype, int kv_dtype, float scale,
+                                              int64_t chunk_tokens, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Tells every peer that this GPU's stores of step `step` have landed and waits (bounded:
+ * about a second, then SFB_STATUS_WAIT_TIMEOUT is OR-ed into *status, a device int32 or
+ * NULL) until every peer has said the same.  peer_flags[p] = GPU p's device array of
+ * `world` uint32 slots, zero before the first step; `step` must grow by one per call.
+ * `phases`: SFB_PEER_SIGNAL | SFB_PEER_WAIT in one launch (the multi-GPU use), or one of
+ * them alone (ranks emulated on ONE device must queue all signals before any wait). */
+enum { SFB_PEER_SIGNAL = 1, SFB_PEER_WAIT = 2 };
+SFB_API int sfb_peer_signal_wait(void* const* peer_flags, int world, int rank, uint32_t step, int phases, void* status,
+                                 void* stream);
+
 /* ── Block manager with device-resident tables ───────────────────────────────
  * Replaces BlockManager (runtime/src/cache/block.rs:84-346; Python twin in the
  * engine): reference-counted physical blocks, LIFO free list, per-request ordered

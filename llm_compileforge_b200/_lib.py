@@ -27,6 +27,7 @@ SFB_ERR_WORKSPACE = -3
 SFB_ERR_CUDA = -4
 SFB_ERR_DEVICE_STATUS = -5
 SFB_ERR_OUT_OF_BLOCKS = -6
+SFB_PEER_SIGNAL, SFB_PEER_WAIT = 1, 2
 
 # SFBDType
 SFB_F32, SFB_BF16, SFB_F16, SFB_F8E4M3 = 0, 1, 2, 3
@@ -114,6 +115,11 @@ def load() -> ctypes.CDLL:
     _optional(lib)
     _shared_prefix_protos(lib)
     _block_manager_protos(lib)
+    lib.sfb_paged_attention_decode_gather.restype = c_int
+    lib.sfb_paged_attention_decode_gather.argtypes = [_T] * 9 + [POINTER(c_void_p), c_int, c_int, c_int, c_int, c_float, c_int64,
+                                                                c_void_p, c_int64, c_void_p]
+    lib.sfb_peer_signal_wait.restype = c_int
+    lib.sfb_peer_signal_wait.argtypes = [POINTER(c_void_p), c_int, c_int, ctypes.c_uint32, c_int, c_void_p, c_void_p]
     _lib = lib
     return lib
 

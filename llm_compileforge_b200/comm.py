@@ -112,3 +112,51 @@ def kv_head_shard(t: torch.Tensor, rank: int, world_size: int, dim: int) -> torc
         raise ValueError(f"axis of {n} heads does not divide over {world_size} ranks")
     per = n // world_size
     return t.narrow(dim, rank * per, per)
+
+
+class PeerGather:
+    """Output buffers for head-partitioned decode whose all-gather happens inside the decode kernel.
+
+    Every rank allocates the whole ``[batch, heads_per_rank * world, head_dim]`` output plus a ``uint32 [world]`` flag
+    array in peer-mapped (symmetric) memory; rank g's decode stores its heads into every rank's copy
+    (:func:`ops.paged_attention_decode_gather`) and :meth:`signal_wait` closes the step.  One node, at most 8 ranks.
+    The NCCL path (:meth:`TorchDistCommunicator.gather_heads`) stays the portable fallback for callers that cannot map peers.
+    """
+
+    def __init__(self, batch: int, heads_per_rank: int, head_dim: int, dtype: torch.dtype, device: torch.device,
+                 group: "dist.ProcessGroup | None" = None) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        grp = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(grp), dist.get_world_size(grp)
+        if self.world > 8:
+            raise ValueError("PeerGather covers one node: at most 8 ranks")
+        self.device = device
+        self.out = symm_mem.empty((batch, heads_per_rank * self.world, head_dim), dtype=dtype, device=device)
+        self._out_hdl = symm_mem.rendezvous(self.out, grp)
+        self.flags = symm_mem.empty((self.world,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self._flag_hdl = symm_mem.rendezvous(self.flags, grp)
+        self.out_ptrs = [int(p) for p in self._out_hdl.buffer_ptrs]
+        self.flag_ptrs = [int(p) for p in self._flag_hdl.buffer_ptrs]
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.step = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(grp)  # every rank's flags are zero before anybody signals
+
+    def decode(self, q, k_cache, v_cache, block_tables, seq_lens, **kw) -> torch.Tensor:
+        from . import ops
+
+        ops.paged_attention_decode_gather(q, k_cache, v_cache, block_tables, seq_lens, self.out, self.out_ptrs, self.rank, **kw)
+        self.signal_wait()
+        return self.out
+
+    def signal_wait(self) -> None:
+        from . import ops
+
+        self.step += 1
+        ops.peer_signal_wait(self.flag_ptrs, self.rank, self.step, self.status, self.device)
+
+    def timed_out(self) -> bool:
+        """True when a wait gave up (synchronises)."""
+        return bool(int(self.status.item()) != 0)

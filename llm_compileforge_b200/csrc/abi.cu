@@ -89,11 +89,12 @@ int64_t sfb_paged_attention_workspace_bytes(int64_t batch, int64_t n_heads, int6
     return decode_split(batch, n_heads, head_dim, max_blocks, block_size, chunk_tokens).total_bytes;
 }
 
-int sfb_paged_attention_decode(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
-                               const SFBTensor* k_scale, const SFBTensor* v_scale, const SFBTensor* block_tables,
-                               const SFBTensor* seq_lens, const SFBTensor* table_rows, SFBTensor* out, int q_dtype,
-                               int kv_dtype, float scale, int64_t chunk_tokens, void* workspace, int64_t workspace_bytes,
-                               void* stream) {
+// `world` > 0: `out` is this GPU's copy of the whole [B, H * world, D] output and peer_out[0..world) are the base
+// addresses of every GPU's copy (this GPU's own included); the heads computed here are written into all of them.
+static int decode_impl(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache, const SFBTensor* k_scale,
+                       const SFBTensor* v_scale, const SFBTensor* block_tables, const SFBTensor* seq_lens,
+                       const SFBTensor* table_rows, SFBTensor* out, int q_dtype, int kv_dtype, float scale, int64_t chunk_tokens,
+                       void* workspace, int64_t workspace_bytes, void* stream, void* const* peer_out, int world, int rank) {
     const int qe = dtype_size(q_dtype), kve = dtype_size(kv_dtype);
     if (!qe || q_dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "decode: q dtype %d", q_dtype);
     if (!kve) return fail(SFB_ERR_INVALID_ARG, "decode: kv dtype %d", kv_dtype);
@@ -114,7 +115,9 @@ int sfb_paged_attention_decode(const SFBTensor* q, const SFBTensor* k_cache, con
     if (vk.size[3] != D || vv.size[3] != D) return fail(SFB_ERR_INVALID_ARG, "decode: head_dim of q (%lld) and pools differ", (long long)D);
     for (int i = 0; i < 4; ++i)
         if (vk.size[i] != vv.size[i]) return fail(SFB_ERR_INVALID_ARG, "decode: k_cache and v_cache shapes differ");
-    if (vo.size[1] != B || vo.size[2] != H || vo.size[3] != D) return fail(SFB_ERR_INVALID_ARG, "decode: out shape differs from q");
+    const int64_t out_heads = world > 0 ? H * world : H;
+    if (vo.size[1] != B || vo.size[2] != out_heads || vo.size[3] != D)
+        return fail(SFB_ERR_INVALID_ARG, "decode: out must be [%lld, %lld, %lld]", (long long)B, (long long)out_heads, (long long)D);
     if (Hkv <= 0 || H % Hkv) return fail(SFB_ERR_INVALID_ARG, "decode: %lld query heads not a multiple of %lld kv heads", (long long)H, (long long)Hkv);
     View vr;
     if (table_rows) {
@@ -141,6 +144,14 @@ int sfb_paged_attention_decode(const SFBTensor* q, const SFBTensor* k_cache, con
     a.block_size = (int)bs; a.max_blocks = (int)max_blocks; a.n_pool_blocks = NB;
     a.q_stride[0] = vq.stride[1]; a.q_stride[1] = vq.stride[2];
     a.out_stride[0] = vo.stride[1]; a.out_stride[1] = vo.stride[2];
+    if (world > 0) {
+        // this GPU's heads start at head rank * H of every copy; all copies share the local copy's strides
+        const int64_t head_off = (int64_t)rank * H * vo.stride[2] * qe;
+        const int64_t local_off = static_cast<const char*>(vo.base) - static_cast<const char*>(peer_out[rank]);
+        a.out = static_cast<char*>(vo.base) + head_off;
+        a.n_peers = world;
+        for (int p = 0; p < world; ++p) a.peer_out[p] = static_cast<char*>(peer_out[p]) + local_off + head_off;
+    }
     for (int i = 0; i < 3; ++i) { a.k_stride[i] = vk.stride[i]; a.v_stride[i] = vv.stride[i]; }
     a.table_stride = vt.stride[2];
     a.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
@@ -174,8 +185,31 @@ int sfb_paged_attention_decode(const SFBTensor* q, const SFBTensor* k_cache, con
     }
     rc = launch_decode_tma(a, st);  // merges its own partials; SFB_ERR_UNSUPPORTED when the shape is not covered
     if (rc != SFB_ERR_UNSUPPORTED) return rc;
+    if (world > 0) return fail(SFB_ERR_UNSUPPORTED, "decode_gather: only shapes of the TMA decode kernel (16-bit query, block 16, 16-byte aligned rows)");
     if ((rc = launch_decode_generic(a, st))) return rc;
     return launch_decode_combine(a, st);
+}
+
+int sfb_paged_attention_decode(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
+                               const SFBTensor* k_scale, const SFBTensor* v_scale, const SFBTensor* block_tables,
+                               const SFBTensor* seq_lens, const SFBTensor* table_rows, SFBTensor* out, int q_dtype,
+                               int kv_dtype, float scale, int64_t chunk_tokens, void* workspace, int64_t workspace_bytes,
+                               void* stream) {
+    return decode_impl(q, k_cache, v_cache, k_scale, v_scale, block_tables, seq_lens, table_rows, out, q_dtype, kv_dtype, scale,
+                       chunk_tokens, workspace, workspace_bytes, stream, nullptr, 0, 0);
+}
+
+int sfb_paged_attention_decode_gather(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
+                                      const SFBTensor* k_scale, const SFBTensor* v_scale, const SFBTensor* block_tables,
+                                      const SFBTensor* seq_lens, const SFBTensor* table_rows, SFBTensor* out_all,
+                                      void* const* peer_out, int world, int rank, int q_dtype, int kv_dtype, float scale,
+                                      int64_t chunk_tokens, void* workspace, int64_t workspace_bytes, void* stream) {
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || !peer_out)
+        return fail(SFB_ERR_INVALID_ARG, "decode_gather: world must be 1..8, rank inside it, peer_out given");
+    for (int p = 0; p < world; ++p)
+        if (!peer_out[p] || reinterpret_cast<uintptr_t>(peer_out[p]) % 16) return fail(SFB_ERR_INVALID_ARG, "decode_gather: peer_out[%d] is null or not 16-byte aligned", p);
+    return decode_impl(q, k_cache, v_cache, k_scale, v_scale, block_tables, seq_lens, table_rows, out_all, q_dtype, kv_dtype, scale,
+                       chunk_tokens, workspace, workspace_bytes, stream, peer_out, world, rank);
 }
 
 int64_t sfb_prefill_workspace_bytes(int64_t total_q_tokens) {

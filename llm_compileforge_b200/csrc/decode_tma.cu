@@ -157,6 +157,20 @@ struct State {
     float l[2];
 };
 
+// Output store: into `out`, or - when the heads of a batch are split over GPUs and every GPU wants the whole
+// output - to the same element offset of every peer's buffer (plain stores over NVLink; this GPU's own buffer is
+// one of the peers).  The peers learn that the data has landed from the signal kernel that follows on the stream.
+template <typename QT, typename V>
+__device__ __forceinline__ void store_out(const DecodeArgs& a, QT* out, int64_t off, V v) {
+    if (a.n_peers == 0) {
+        *reinterpret_cast<V*>(out + off) = v;
+        return;
+    }
+#pragma unroll
+    for (int p = 0; p < 8; ++p)
+        if (p < a.n_peers) *reinterpret_cast<V*>(reinterpret_cast<QT*>(a.peer_out[p]) + off) = v;
+}
+
 template <int KV, int NSUB, int HB, int BPS, int STAGES, bool QBF16>
 __global__ void __launch_bounds__(Cfg<KV, NSUB, HB, BPS, STAGES>::THREADS, Cfg<KV, NSUB, HB, BPS, STAGES>::MIN_BLOCKS)
 decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const DecodeArgs a) {
@@ -178,7 +192,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         if (chunk == 0) {
             if (status && threadIdx.x == 0 && hg == 0) atomicOr(status, SFB_STATUS_EMPTY_REQUEST);
             for (int i = threadIdx.x; i < HB * group * C::D; i += C::THREADS)
-                out[req * a.out_stride[0] + (hg * HB * group + i / C::D) * a.out_stride[1] + i % C::D] = from_float<QT>(0.f);
+                store_out(a, out, req * a.out_stride[0] + (hg * HB * group + i / C::D) * a.out_stride[1] + i % C::D, from_float<QT>(0.f));
         }
         return;
     }
@@ -458,7 +472,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             const float l = st.l[col];
             if (merge_chunks == 1) {
                 const float inv = l > 0.f ? 1.f / l : 0.f;
-                QT* dst = out + req * a.out_stride[0] + (int64_t)head * a.out_stride[1];
+                const int64_t dst = req * a.out_stride[0] + (int64_t)head * a.out_stride[1];
 #pragma unroll
                 for (int sub = 0; sub < NSUB; ++sub) {
                     const int d0 = sub * C::EPR + rowk * C::EPC;
@@ -470,7 +484,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             const int mt = sub * (C::EPC / 2) + q4 * 4 + k;
                             w[k] = pack2<QBF16>(st.o[mt][col] * inv, st.o[mt][2 + col] * inv);
                         }
-                        *reinterpret_cast<uint4*>(dst + d0 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                        store_out(a, out, dst + d0 + q4 * 8, make_uint4(w[0], w[1], w[2], w[3]));
                     }
                 }
             } else {
@@ -549,8 +563,8 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             const int i = threadIdx.x + k * C::THREADS;
             if (i < n_items) {
                 const int hl = i / VPR, v4 = i - hl * VPR;
-                QT* dst = out + req * a.out_stride[0] + (int64_t)(hg * heads_here + hl) * a.out_stride[1] + v4 * 4;
-                *reinterpret_cast<uint2*>(dst) = make_uint2(pack2<QBF16>(acc[k].x, acc[k].y), pack2<QBF16>(acc[k].z, acc[k].w));
+                store_out(a, out, req * a.out_stride[0] + (int64_t)(hg * heads_here + hl) * a.out_stride[1] + v4 * 4,
+                          make_uint2(pack2<QBF16>(acc[k].x, acc[k].y), pack2<QBF16>(acc[k].z, acc[k].w)));
             }
         }
         return;
@@ -569,7 +583,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             l = fmaf(__ldcg(part_ml + ps * 2 + 1), f, l);
             o = fmaf(__ldcg(part_o + ps * C::D + d), f, o);
         }
-        out[req * a.out_stride[0] + (int64_t)(hg * heads_here + hl) * a.out_stride[1] + d] = from_float<QT>(l > 0.f ? o / l : 0.f);
+        store_out(a, out, req * a.out_stride[0] + (int64_t)(hg * heads_here + hl) * a.out_stride[1] + d, from_float<QT>(l > 0.f ? o / l : 0.f));
     }
 }
 

@@ -156,6 +156,8 @@ struct DecodeArgs {
     const float* v_scale;
     const int32_t* tables;
     const int32_t* table_rows;  // optional: query row r uses table row table_rows[r] (prefill tokens share a row)
+    void* peer_out[8];          // n_peers > 0: every output store goes to the same offset in each of these buffers
+    int n_peers;                // (head-partitioned multi-GPU decode: each GPU writes its heads into every GPU's copy)
     int64_t n_table_rows;       // rows of `tables`; a table_rows entry outside [0, n) is flagged and row 0 is read
     const int32_t* seq_lens;
     void* out;

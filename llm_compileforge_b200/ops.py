@@ -74,6 +74,61 @@ def paged_attention_decode(
     return out
 
 
+def paged_attention_decode_gather(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    seq_lens: torch.Tensor,
+    out_all: torch.Tensor,
+    peer_out_ptrs: "list[int]",
+    rank: int,
+    *,
+    k_scale: torch.Tensor | None = None,
+    v_scale: torch.Tensor | None = None,
+    scale: float | None = None,
+    chunk_tokens: int = 0,
+    workspace: torch.Tensor | None = None,
+    table_rows: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Decode of this GPU's heads (``q [B,H,D]`` against its kv-head shard of the pool) whose result is stored
+    into heads ``[rank*H, (rank+1)*H)`` of every GPU's ``[B, H*world, D]`` output: ``out_all`` is the local copy,
+    ``peer_out_ptrs[p]`` the device address of GPU p's copy (peer-mapped by the caller, same layout).  Follow it
+    with :func:`peer_signal_wait` on the same stream; then ``out_all`` is complete."""
+    import ctypes
+
+    lib = _lib.load()
+    world = len(peer_out_ptrs)
+    fp8 = k_scale is not None
+    kc, vc = (_as_codes(k_cache), _as_codes(v_cache)) if fp8 else (k_cache, v_cache)
+    b, h, d = q.shape
+    need = decode_workspace_bytes(b, h, d, block_tables.shape[1], k_cache.shape[1], chunk_tokens)
+    if workspace is None:
+        workspace = torch.zeros(need, dtype=torch.uint8, device=q.device)
+    ptrs = (ctypes.c_void_p * world)(*[int(x) for x in peer_out_ptrs])
+    check(lib.sfb_paged_attention_decode_gather(
+        desc(q, "q"), desc(kc, "k_cache"), desc(vc, "v_cache"), desc(k_scale, "k_scale"), desc(v_scale, "v_scale"),
+        desc(block_tables, "block_tables"), desc(seq_lens, "seq_lens"), desc(table_rows, "table_rows"), desc(out_all, "out_all"),
+        ptrs, world, int(rank), dtype_code(q.dtype), _lib.SFB_F8E4M3 if fp8 else dtype_code(k_cache.dtype),
+        float(scale) if scale is not None else 0.0, int(chunk_tokens), workspace.data_ptr(), workspace.numel(),
+        current_stream(q.device),
+    ))
+    return out_all
+
+
+def peer_signal_wait(peer_flag_ptrs: "list[int]", rank: int, step: int, status: torch.Tensor | None, device: torch.device,
+                     phases: int = 3) -> None:
+    """Signal step ``step`` to every peer and wait (bounded) for theirs; ``peer_flag_ptrs[p]`` is the device address of
+    GPU p's ``uint32 [world]`` flag array, ``status`` an int32 device tensor that collects ``SFB_STATUS_WAIT_TIMEOUT``;
+    ``phases`` 1 = signal only, 2 = wait only, 3 = both (ranks emulated on one device queue all signals before any wait)."""
+    import ctypes
+
+    world = len(peer_flag_ptrs)
+    ptrs = (ctypes.c_void_p * world)(*[int(x) for x in peer_flag_ptrs])
+    check(_lib.load().sfb_peer_signal_wait(ptrs, world, int(rank), ctypes.c_uint32(step & 0xFFFFFFFF), int(phases),
+                                           status.data_ptr() if status is not None else None, current_stream(device)))
+
+
 def read_status(workspace: torch.Tensor) -> int:
     """Status bits left by the last decode call that used ``workspace``
     (synchronises the current stream)."""
