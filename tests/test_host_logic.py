@@ -63,3 +63,31 @@ def test_backend_dispatch_and_fallback():
         B200Backend().execute("softmax", [torch.zeros(2)])
     with pytest.raises(ValueError, match="fp8"):
         be.execute("quantize", [torch.zeros(2)], dtype="int8")
+
+
+def test_b200_hardware_spec_has_the_loader_schema():
+    """hardware_specs/b200.yaml follows the key set of the reference's hardware_specs/*.yaml (python_runtime/hal/
+    hardware_spec.py: ComputeUnit, MemoryLevel, Interconnect fields) and quotes the measured roofline denominators."""
+    import json
+    import os
+
+    import yaml
+
+    import llm_compileforge_b200 as pkg
+
+    root = os.path.dirname(os.path.abspath(pkg.__file__))
+    spec = yaml.safe_load(open(os.path.join(root, "hardware_specs", "b200.yaml")))
+    assert set(spec) == {"name", "compute_units", "memory_levels", "interconnects", "op_latency_us"}
+    for cu in spec["compute_units"]:
+        assert {"name", "fp32_tflops", "fp16_tflops", "bf16_tflops", "int8_tops", "int4_tops"} <= set(cu)
+    for ml in spec["memory_levels"]:
+        assert set(ml) == {"name", "size_gb", "bandwidth_gbs", "latency_ns"}
+    for ic in spec["interconnects"]:
+        assert set(ic) == {"name", "bandwidth_gbs", "latency_us", "topology"}
+    assert "default" in spec["op_latency_us"] and "paged_attention" in spec["op_latency_us"]
+    peaks_path = os.path.join(os.path.dirname(root), "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peaks = json.load(open(peaks_path))
+        hbm = [m for m in spec["memory_levels"] if m["name"].startswith("HBM")][0]
+        tensor = [c for c in spec["compute_units"] if "Tensor" in c["name"]][0]
+        assert abs(hbm["bandwidth_gbs"] - peaks["hbm_gbs"]) < 1 and abs(tensor["bf16_tflops"] - peaks["bf16_tflops_sustained"]) < 1
