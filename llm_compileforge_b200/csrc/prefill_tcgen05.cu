@@ -10,18 +10,22 @@
 // head h / (H / Hkv).
 //
 // One thread block = 256 query tokens (two 128-row tiles) of one (request, query head):
-//   warp 8    TMA producer: both Q tiles once, then per 128-token KV tile sixteen
+//   warp 16   TMA producer: both Q tiles once, then per 128-token KV tile sixteen
 //             [16 tokens x 128 B] boxes for K and sixteen for V, two stages each
-//   warp 9    issues tcgen05.mma: S_t = Q_t K^T (128x128x128, both operands K-major
+//   warp 17   issues tcgen05.mma: S_t = Q_t K^T (128x128x128, both operands K-major
 //             in 128B-swizzled shared memory) and O_t += P_t V with P_t read from
 //             tensor memory and V as an MN-major shared-memory operand, alternating
 //             between the two query tiles so that one tile's MMAs run while the
 //             other tile's rows are in the softmax warps
-//   warps 0-7 two softmax warpgroups, one thread per query row: tcgen05.ld the S
-//             row, running max / sum in log2 units, P written as bf16/fp16 over the
-//             first half of S's own tensor-memory columns, O rescaled in tensor
-//             memory only when the max grew by more than 2^8 (the stale max stays
-//             exact in fp32), final O / l written out
+//   warps 0-15 softmax: eight warps per query tile, two threads per query row (64 key
+//             columns each; a warp can only reach its own 32 tensor-memory lanes, so
+//             warps w and w+4 share lanes and split the columns).  With two warps per SM
+//             sub-partition on a tile, one warp's FFMA / pack instructions issue while the
+//             other's ex2 occupy the XU pipe.  tcgen05.ld the S half row, half-row maxima
+//             exchanged through shared memory (mbarrier, bounded wait), running max / sum
+//             in log2 units, P written as bf16/fp16 over the thread's own S columns,
+//             O rescaled in tensor memory only when the max grew by more than 2^8 (the
+//             stale max stays exact in fp32), partial sums added in the epilogue, O / l out
 // Tensor memory: per query tile S|P (128 columns) and O (128) = 512 columns in all.
 // Bound: tensor pipe (4*D*Sq*Skv flops per head against ~1.4 PFLOP/s dense).
 
@@ -39,7 +43,8 @@ constexpr int kTileKV = 128;
 constexpr int kHeadDim = 128;
 constexpr int kSubBytes = kTileKV * 128;     // one [128 rows][128 B] swizzled sub-tile
 constexpr int kTileBytes = 2 * kSubBytes;    // D = 128 16-bit values = two sub-tiles
-constexpr int kThreads = 320;  // 2 softmax warpgroups, TMA warp, MMA warp
+constexpr int kThreads = 576;  // 2 x 8 softmax warps (one group per query tile), TMA warp, MMA warp
+constexpr int kTmaWarp = 16, kMmaWarp = 17;
 constexpr uint32_t kSpin = 1u << 21;  // bounded waits: a stuck pipeline gives up (status bit) within about a second
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;    // log2 units
@@ -128,7 +133,7 @@ __device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a, uint64_t b, uint3
         ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, float (&v)[32]) {
     uint32_t* r = reinterpret_cast<uint32_t*>(v);
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
@@ -139,7 +144,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
           "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    tmem_ld32_issue(taddr, v);
+    tmem_wait_ld();
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
     const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
@@ -206,9 +215,11 @@ enum {
     B_S_FULL = 9,    // +query tile
     B_P_FULL = 11,   // +query tile
     B_PV_DONE = 13,  // +query tile
-    B_COUNT = 15
+    B_X_FULL = 15,   // +query tile: half-row maxima / sums exchanged between the two threads of a row
+    B_COUNT = 17
 };
-constexpr int kSmemBytes = 6 * kTileBytes + B_COUNT * 8 + 16 + 1024;  // 2 Q tiles, 2 K stages, 2 V stages
+constexpr int kXchFloats = 2 * 2 * kTileQ;  // [query tile][column half][row]
+constexpr int kSmemBytes = 6 * kTileBytes + B_COUNT * 8 + 16 + kXchFloats * 4 + 1024;  // 2 Q tiles, 2 K stages, 2 V stages
 
 // Tensor-memory columns of query tile t: S (fp32, 128 columns) at t*256, with P (16-bit pairs,
 // 64 columns) written over its first half once the row has been read; O (fp32) at t*256 + 128.
@@ -251,6 +262,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     const uint32_t q_s = base, k_s = base + 2 * kTileBytes, v_s = base + 4 * kTileBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + 6 * kTileBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
+    float* xch = reinterpret_cast<float*>(tmem_slot + 4);
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
@@ -262,20 +274,21 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             mbar_init(bar(B_V_FULL + s), 1);
             mbar_init(bar(B_V_EMPTY + s), 1);
             mbar_init(bar(B_S_FULL + s), 1);
-            mbar_init(bar(B_P_FULL + s), 4);
+            mbar_init(bar(B_P_FULL + s), 8);
+            mbar_init(bar(B_X_FULL + s), 8);
             mbar_init(bar(B_PV_DONE + s), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 9) tmem_alloc(smem_u32(tmem_slot), 512);
+    if (warp == kMmaWarp) tmem_alloc(smem_u32(tmem_slot), 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     bool timed_out = false;
 
-    if (warp == 8) {
+    if (warp == kTmaWarp) {
         // ============================ TMA producer ============================
         if (lane == 0) {
             mbar_expect_tx(bar(B_Q_FULL), 2 * kTileBytes);
@@ -313,7 +326,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             if (lane >= 16) tma_load_5d(v_s + s * kTileBytes + dst_off, &vmap, bar(B_V_FULL + s), sub, kvh, phys);
             phys = next_phys;
         }
-    } else if (warp == 9) {
+    } else if (warp == kMmaWarp) {
         // ============================ MMA issuer ==============================
         // Issue order PV0(j), QK0(j+1), PV1(j), QK1(j+1): while one query tile's rows are in the
         // softmax warps, the tensor pipe works on the other tile.
@@ -337,7 +350,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)  // 16 KV tokens per instruction
-                    mma_ts(tmem + t * kColTile + kColO, tmem + t * kColTile + ks * 8,
+                    mma_ts(tmem + t * kColTile + kColO, tmem + t * kColTile + (ks >> 2) * 64 + (ks & 3) * 8,
                            smem_desc(v_s + s * kTileBytes + ks * 2048, kSubBytes, 1024), idesc_pv, (j > 0 || ks > 0));
                 tc_commit(bar(B_PV_DONE + t));
                 return true;
@@ -365,89 +378,113 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             }
             timed_out = !ok;
         }
-    } else {
+    } else if (warp < 16) {
         // ======================= softmax / correction / epilogue ==============
-        const int t = warp >> 2;                 // query tile of this warpgroup
-        const int row = threadIdx.x & 127;       // tensor-memory lane
-        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + t * kColTile;
-        const int rows = rows_t[t], my_tiles = tiles_t[t];
-        const bool row_valid = row < rows;
-        const int pos = (row_valid && a.causal) ? ctx - n_q + q0 + t * kTileQ + row : ctx - 1;  // padding rows see everything
+        // Eight warps per query tile.  Warp w owns tensor-memory lanes 32*(w&3).. (its hardware window) and key
+        // columns 64*((w>>2)&1).. of its tile: two threads share a query row, exchange their half-row maxima
+        // through shared memory (an mbarrier with bounded waits orders it) and keep partial sums that are only
+        // added up in the epilogue.
+        const int my_t = warp >> 3;          // query tile of this 8-warp group
+        const int hf = (warp >> 2) & 1;
+        const int row = threadIdx.x & 127;
+        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const float sl2 = a.scale * kLog2e;
         float m_used = -INFINITY, l = 0.f;
-        bool ok = true;
-        for (int j = 0; j < my_tiles && ok; ++j) {
-            if (!mbar_wait(bar(B_S_FULL + t), j & 1)) { ok = false; break; }
+        const int pos = (row < rows_t[my_t] && a.causal) ? ctx - n_q + q0 + my_t * kTileQ + row : ctx - 1;  // padding rows see everything
+
+        auto exchange = [&](int t, uint32_t parity, float mine, float& other) -> bool {
+            xch[(t * 2 + hf) * kTileQ + row] = mine;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_X_FULL + t));
+            if (!mbar_wait(bar(B_X_FULL + t), parity)) return false;
+            other = xch[(t * 2 + (hf ^ 1)) * kTileQ + row];
+            return true;
+        };
+
+        auto softmax_tile = [&](int t, int j) -> bool {
+            const uint32_t s_addr = lane_addr + t * kColTile + hf * 64;  // this thread's 64 score columns
+            if (!mbar_wait(bar(B_S_FULL + t), j & 1)) return false;
             tc_fence_after();
-            const int kv0 = j * kTileKV;
+            const int kv0 = j * kTileKV + hf * 64;
             // tcgen05.ld / st are warp-collective: the masked / unmasked choice must be uniform across the warp
-            const bool full = __all_sync(0xffffffffu, kv0 + kTileKV - 1 <= pos);  // no row of this warp needs masking
-            float mx = -INFINITY;
+            const bool full = __all_sync(0xffffffffu, kv0 + 63 <= pos);
+            float mx0 = -INFINITY, mx1 = -INFINITY;
             if (full) {
 #pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
+                for (int ch = 0; ch < 2; ++ch) {
                     float v[32];
-                    tmem_ld32(lane_base + ch * 32, v);
+                    tmem_ld32(s_addr + ch * 32, v);
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) mx = max3(mx, v[i], v[i + 1]);
+                    for (int i = 0; i < 32; i += 4) {
+                        mx0 = max3(mx0, v[i], v[i + 1]);
+                        mx1 = max3(mx1, v[i + 2], v[i + 3]);
+                    }
                 }
             } else {
 #pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
+                for (int ch = 0; ch < 2; ++ch) {
                     float v[32];
-                    tmem_ld32(lane_base + ch * 32, v);
+                    tmem_ld32(s_addr + ch * 32, v);
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (kv0 + ch * 32 + i <= pos) mx = fmaxf(mx, v[i]);
+                        if (kv0 + ch * 32 + i <= pos) mx0 = fmaxf(mx0, v[i]);
                 }
             }
+            float mx = fmaxf(mx0, mx1), other;
+            if (!exchange(t, j & 1, mx, other)) return false;
+            mx = fmaxf(mx, other);
             const float m_new = fmaxf(m_used, mx * sl2);
             if (j == 0) {
                 m_used = m_new;
             } else {
-                const bool need = m_new > m_used + kRescaleThreshold;
+                const bool need = m_new > m_used + kRescaleThreshold;  // the same for both threads of a row
                 if (__any_sync(0xffffffffu, need)) {
                     // O is only touched between PV products: wait for the previous one
-                    if (!mbar_wait(bar(B_PV_DONE + t), (j - 1) & 1)) { ok = false; break; }
+                    if (!mbar_wait(bar(B_PV_DONE + t), (j - 1) & 1)) return false;
                     tc_fence_after();
                     const float f = need ? fast_exp2(m_used - m_new) : 1.f;
                     l *= f;
                     if (need) m_used = m_new;
 #pragma unroll 1
-                    for (int ch = 0; ch < 4; ++ch) {
+                    for (int ch = 0; ch < 2; ++ch) {
                         float o[32];
-                        tmem_ld32(lane_base + kColO + ch * 32, o);
+                        tmem_ld32(lane_addr + t * kColTile + kColO + hf * 64 + ch * 32, o);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) o[i] *= f;
-                        tmem_st32(lane_base + kColO + ch * 32, o);
+                        tmem_st32(lane_addr + t * kColTile + kColO + hf * 64 + ch * 32, o);
                     }
                     tmem_wait_st();
                 }
             }
-            // P chunk ch (16 columns) lands on S columns that chunk <= ch has already read
+            // P (16-bit pairs, 32 columns) goes over the first half of this thread's own score columns
             const float neg_m = -m_used;
             float l0 = 0.f, l1 = 0.f;
             if (full) {
+                // packed fp32 pairs: one FFMA2 scales and shifts two scores, one FADD2 adds two probabilities
+                const float2 sl2v = make_float2(sl2, sl2), nmv = make_float2(neg_m, neg_m);
+                float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
+                for (int ch = 0; ch < 2; ++ch) {
                     float v[32];
-                    tmem_ld32(lane_base + ch * 32, v);
+                    tmem_ld32(s_addr + ch * 32, v);
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float p0 = fast_exp2(fmaf(v[2 * i], sl2, neg_m));
-                        const float p1 = fast_exp2(fmaf(v[2 * i + 1], sl2, neg_m));
-                        l0 += p0;
-                        l1 += p1;
-                        pk[i] = pack2<BF16>(p0, p1);
+                        const float2 x = __ffma2_rn(make_float2(v[2 * i], v[2 * i + 1]), sl2v, nmv);
+                        const float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                        if (i & 1) acc1 = __fadd2_rn(acc1, pr);
+                        else acc0 = __fadd2_rn(acc0, pr);
+                        pk[i] = pack2<BF16>(pr.x, pr.y);
                     }
-                    tmem_st16(lane_base + ch * 16, pk);
+                    tmem_st16(s_addr + ch * 16, pk);  // P chunk ch lands on score columns that chunk <= ch has already read
                 }
+                l0 = acc0.x + acc1.x;
+                l1 = acc0.y + acc1.y;
             } else {
 #pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
+                for (int ch = 0; ch < 2; ++ch) {
                     float v[32];
-                    tmem_ld32(lane_base + ch * 32, v);
+                    tmem_ld32(s_addr + ch * 32, v);
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
@@ -458,7 +495,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                         l1 += p1;
                         pk[i] = pack2<BF16>(p0, p1);
                     }
-                    tmem_st16(lane_base + ch * 16, pk);
+                    tmem_st16(s_addr + ch * 16, pk);
                 }
             }
             l += l0 + l1;
@@ -466,58 +503,68 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_P_FULL + t));
-        }
-        // ---- epilogue: O / l
-        if (ok && my_tiles > 0) ok = mbar_wait(bar(B_PV_DONE + t), (my_tiles - 1) & 1);
-        if (ok && my_tiles > 0) {
+            return true;
+        };
+
+        bool ok = true;
+        for (int j = 0; j < tiles_t[my_t] && ok; ++j) ok = softmax_tile(my_t, j);
+        // ---- epilogue: O / l, each thread its 64 output columns
+        for (int t = my_t; t == my_t; ++t) {
+            const int my_tiles = tiles_t[t];
+            if (!ok || my_tiles <= 0) continue;
+            if (!mbar_wait(bar(B_PV_DONE + t), (my_tiles - 1) & 1)) { ok = false; continue; }
             tc_fence_after();
+            float l_other;
+            if (!exchange(t, my_tiles & 1, l, l_other)) { ok = false; continue; }
+            const float l_row = l + l_other;
+            const bool row_valid = row < rows_t[t];
+            const uint32_t o_addr = lane_addr + t * kColTile + kColO + hf * 64;
             if (a.part_o) {
                 // shared-prefix mode: this row is decode request `qrow`; its partial goes to the chunk slot right after
                 // the request's own chunks, in the decode kernel's format (unnormalised O, max in log2 units, sum)
                 const int qrow = q0 + t * kTileQ + row;
+                int64_t pslot = 0;
                 if (row_valid) {
                     int len = a.part_seq_lens[qrow];
                     if (len > a.part_max_tokens) len = a.part_max_tokens;
-                    const int own = max(0, len - ctx);
-                    const int chunk = (own + a.part_chunk_tokens - 1) / a.part_chunk_tokens;
-                    const int64_t pslot = ((int64_t)qrow * a.part_n_chunks + chunk) * a.n_heads + head;
-                    a.part_ml[pslot * 2] = m_used;
-                    a.part_ml[pslot * 2 + 1] = l;
+                    const int chunk = (max(0, len - ctx) + a.part_chunk_tokens - 1) / a.part_chunk_tokens;
+                    pslot = ((int64_t)qrow * a.part_n_chunks + chunk) * a.n_heads + head;
+                    if (hf == 0) {
+                        a.part_ml[pslot * 2] = m_used;
+                        a.part_ml[pslot * 2 + 1] = l_row;
+                    }
                 }
 #pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
+                for (int ch = 0; ch < 2; ++ch) {
                     float o[32];
-                    tmem_ld32(lane_base + kColO + ch * 32, o);
+                    tmem_ld32(o_addr + ch * 32, o);
                     if (row_valid) {
-                        int len = a.part_seq_lens[qrow];
-                        if (len > a.part_max_tokens) len = a.part_max_tokens;
-                        const int chunk = (max(0, len - ctx) + a.part_chunk_tokens - 1) / a.part_chunk_tokens;
-                        float* dst = a.part_o + (((int64_t)qrow * a.part_n_chunks + chunk) * a.n_heads + head) * kHeadDim + ch * 32;
+                        float* dst = a.part_o + pslot * kHeadDim + hf * 64 + ch * 32;
 #pragma unroll
                         for (int i = 0; i < 8; ++i)
                             *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
                     }
                 }
             } else {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(q_begin + q0 + t * kTileQ + row) * a.out_stride[0] +
-                            (int64_t)head * a.out_stride[1];
+                const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+                uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(q_begin + q0 + t * kTileQ + row) * a.out_stride[0] +
+                                (int64_t)head * a.out_stride[1] + hf * 64;
 #pragma unroll 1
-            for (int ch = 0; ch < 4; ++ch) {
-                float o[32];
-                tmem_ld32(lane_base + kColO + ch * 32, o);
-                if (row_valid) {
+                for (int ch = 0; ch < 2; ++ch) {
+                    float o[32];
+                    tmem_ld32(o_addr + ch * 32, o);
+                    if (row_valid) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint4 w;
-                        w.x = pack2<BF16>(o[8 * i] * inv, o[8 * i + 1] * inv);
-                        w.y = pack2<BF16>(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
-                        w.z = pack2<BF16>(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
-                        w.w = pack2<BF16>(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
-                        *reinterpret_cast<uint4*>(dst + ch * 32 + i * 8) = w;
+                        for (int i = 0; i < 4; ++i) {
+                            uint4 w;
+                            w.x = pack2<BF16>(o[8 * i] * inv, o[8 * i + 1] * inv);
+                            w.y = pack2<BF16>(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
+                            w.z = pack2<BF16>(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
+                            w.w = pack2<BF16>(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
+                            *reinterpret_cast<uint4*>(dst + ch * 32 + i * 8) = w;
+                        }
                     }
                 }
-            }
             }
         }
         timed_out = !ok;
@@ -526,7 +573,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     // ---- teardown: every warp arrives here; tensor memory is released before exit
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == kMmaWarp) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }
