@@ -354,6 +354,20 @@ SFB_API int64_t sfb_bm_get_blocks(const SFBBlockManager* bm, const char* request
 SFB_API int64_t sfb_bm_row(const SFBBlockManager* bm, const char* request_id);
 SFB_API int64_t sfb_bm_sync(SFBBlockManager* bm, void* stream);
 
+/* ── RMSNorm fused into the following matmul ───────────────────────────────────
+ * Replaces fused_rms_norm_matmul (python_runtime/hal/pytorch_backend/_ops_norm.py:47-65):
+ *   y = (x * rsqrt(mean(x^2, -1) + eps) * rms_weight) @ mat_weight,  x [M, K], mat_weight [K, N].
+ * The row factor commutes with the contraction, so the weight is folded once
+ * (sfb_fold_norm_weight: folded = diag(rms_weight) mat_weight; weights are static while
+ * serving) and sfb_fused_rms_norm_matmul runs y = rstd(x) * (x @ folded) on the tensor
+ * cores from the raw activations, taking each row's sum of squares from the tiles it
+ * multiplies.  bf16 / fp16, fp32 accumulation, one rounding of y; K and N multiples of 8,
+ * rows contiguous and 16-byte aligned.  `status` (device int32 or NULL) receives
+ * SFB_STATUS_WAIT_TIMEOUT if a bounded wait inside the kernel ran out. */
+SFB_API int sfb_fold_norm_weight(const SFBTensor* rms_weight, const SFBTensor* mat_weight, SFBTensor* folded, int dtype, void* stream);
+SFB_API int sfb_fused_rms_norm_matmul(const SFBTensor* x, const SFBTensor* folded_weight, SFBTensor* out, int dtype, float eps,
+                                      void* status, void* stream);
+
 /* ── `_mlir_ciface_*` convention ─────────────────────────────────────────────
  * The reference's runtime calls compiled kernels as
  *   void _mlir_ciface_<name>(void* sret, const memref* in0, ...)

@@ -466,6 +466,41 @@ int sfb_cache_write(const SFBTensor* k_new, const SFBTensor* v_new, const SFBTen
     return launch_cache_write(a, static_cast<cudaStream_t>(stream));
 }
 
+int sfb_fold_norm_weight(const SFBTensor* rms_weight, const SFBTensor* mat_weight, SFBTensor* folded, int dtype, void* stream) {
+    if (dtype != SFB_BF16 && dtype != SFB_F16) return fail(SFB_ERR_UNSUPPORTED, "fold_norm_weight: bf16 or fp16");
+    View vg, vw, vf;
+    int rc;
+    if ((rc = make_view(rms_weight, "rms_weight", 1, 1, 2, &vg))) return rc;
+    if ((rc = make_view(mat_weight, "mat_weight", 2, 2, 2, &vw))) return rc;
+    if ((rc = make_view(folded, "folded", 2, 2, 2, &vf))) return rc;
+    const int64_t K = vw.size[2], N = vw.size[3];
+    if (vg.size[3] != K || vf.size[2] != K || vf.size[3] != N) return fail(SFB_ERR_INVALID_ARG, "fold_norm_weight: rms_weight [K], mat_weight and folded [K, N]");
+    if (vg.stride[3] != 1 && K > 1) return fail(SFB_ERR_UNSUPPORTED, "fold_norm_weight: rms_weight must be contiguous");
+    if (N % 8 || vw.stride[3] != 1 || vf.stride[3] != 1 || !aligned16(vw, 2) || !aligned16(vf, 2))
+        return fail(SFB_ERR_UNSUPPORTED, "fold_norm_weight: N a multiple of 8, rows contiguous and 16-byte aligned");
+    if (K == 0 || N == 0) return SFB_OK;
+    return launch_fold_norm_weight(vg.base, vw.base, vf.base, K, N, vw.stride[2], vf.stride[2], dtype, static_cast<cudaStream_t>(stream));
+}
+
+int sfb_fused_rms_norm_matmul(const SFBTensor* x, const SFBTensor* folded_weight, SFBTensor* out, int dtype, float eps, void* status,
+                              void* stream) {
+    if (dtype != SFB_BF16 && dtype != SFB_F16) return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: bf16 or fp16 (other types go to the fallback executor)");
+    View vx, vw, vo;
+    int rc;
+    if ((rc = make_view(x, "x", 2, 2, 2, &vx))) return rc;
+    if ((rc = make_view(folded_weight, "folded_weight", 2, 2, 2, &vw))) return rc;
+    if ((rc = make_view(out, "out", 2, 2, 2, &vo))) return rc;
+    const int64_t M = vx.size[2], K = vx.size[3], N = vw.size[3];
+    if (vw.size[2] != K || vo.size[2] != M || vo.size[3] != N) return fail(SFB_ERR_INVALID_ARG, "fused_rms_norm_matmul: x [M, K], weight [K, N], out [M, N]");
+    if (K % 8 || N % 8 || vx.stride[3] != 1 || vw.stride[3] != 1 || vo.stride[3] != 1 || !aligned16(vx, 2) || !aligned16(vw, 2) || !aligned16(vo, 2))
+        return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: K and N multiples of 8, rows contiguous and 16-byte aligned");
+    if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: dimension too large");
+    if (M == 0 || N == 0) return SFB_OK;
+    if (K == 0) return fail(SFB_ERR_INVALID_ARG, "fused_rms_norm_matmul: K is zero");
+    return launch_norm_matmul(vx.base, vx.stride[2], vw.base, vw.stride[2], vo.base, vo.stride[2], M, N, K, eps, dtype,
+                              static_cast<int*>(status), static_cast<cudaStream_t>(stream));
+}
+
 static int quant_views(const SFBTensor* x, const SFBTensor* codes, const SFBTensor* scales, int x_dtype, int granularity,
                        const char* op, View* vx, View* vc, View* vs) {
     const int xe = dtype_size(x_dtype);

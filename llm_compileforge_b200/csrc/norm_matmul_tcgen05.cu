@@ -1,0 +1,359 @@
+// RMSNorm fused into the matmul that follows it, on the sm_100a tensor cores.
+//
+// Replaces the reference's `fused_rms_norm_matmul`
+// (python_runtime/hal/pytorch_backend/_ops_norm.py:47-65; sf-dialect SfPasses.td:91-92 fuses
+// rms_norm -> matmul into it):   y = ( x * rsqrt(mean(x^2) + eps) * g ) @ W,   x [M, K], g [K], W [K, N].
+//
+// The row factor commutes with the contraction:  y[m, :] = rstd[m] * ( x[m, :] @ (diag(g) W) ).
+// So the weight is folded once (fold_norm_weight_kernel: Wg = diag(g) W, weights are static in serving), the
+// GEMM runs on the RAW activations straight out of HBM - the normalised activations are never written or
+// re-read - and the sum of squares of each row is taken from the very A tiles the tensor core consumes,
+// by the epilogue warps, while the MMAs run; rstd scales the accumulators on their way out.
+//
+// One thread block = one 128 x 256 tile of y:
+//   warp 4    TMA producer: per 64-wide K step a [128 rows x 128 B] box of x (K-major, 128B swizzle) and four
+//             [64 k x 128 B] boxes of Wg (N-major), four stages
+//   warp 5    issues tcgen05.mma.cta_group::1.kind::f16, M 128, N 256, K 16, four per stage, accumulator =
+//             256 tensor-memory columns of fp32; tcgen05.commit frees the stage / publishes the accumulator
+//   warps 0-3 one thread per output row: reads its row of every A stage from shared memory (16-byte chunks in
+//             a rotated order, so a quarter-warp never hits one bank twice; the swizzle only permutes chunks
+//             inside the row, the sum does not care), then tcgen05.ld the accumulator row, times rstd, 16-bit
+//             pack, 16-byte stores
+// Every wait is bounded; a stuck pipeline sets SFB_STATUS_WAIT_TIMEOUT in *status and the block leaves
+// through the common teardown, which releases tensor memory.
+// Bound: tensor pipe, 2*M*N*K flops; HBM traffic is x once per N tile (L2 keeps it) and Wg once per M tile.
+
+#include <cuda.h>
+
+#include <mutex>
+
+#include "sfb_common.cuh"
+
+namespace sfb {
+namespace {
+
+constexpr int kTileM = 128, kTileN = 256, kStepK = 64, kStages = 4;
+constexpr int kABytes = kTileM * kStepK * 2;       // 16 KB
+constexpr int kBBlockBytes = kStepK * 128;         // one [64 k][64 n] block: 8 KB
+constexpr int kBBytes = (kTileN / 64) * kBBlockBytes;  // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kThreads = 192;
+constexpr uint32_t kSpin = 1u << 21;
+
+enum { B_FULL = 0, B_EMPTY = kStages, B_ACC = 2 * kStages, B_COUNT = 2 * kStages + 1 };
+constexpr int kSmemBytes = kStages * kStageBytes + B_COUNT * 8 + 16 + 1024;
+
+struct GemmArgs {
+    void* out;
+    int64_t out_stride;  // elements between output rows
+    int M, N, K;
+    float eps;
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpin; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+        "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// Shared-memory matrix descriptor (sm_100 format): start address, leading and stride byte offsets in
+// 16-byte units, version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fff);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor for kind::f16: fp32 accumulate, 16-bit A/B, A K-major, B MN-major, M x N tile.
+__host__ __device__ constexpr uint32_t instr_desc(bool bf16, int m, int n) {
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (1u << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    uint32_t r;
+    if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+template <bool BF16>
+__device__ __forceinline__ float sumsq8(uint4 w) {  // sum of squares of eight 16-bit values
+    float s = 0.f;
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float lo, hi;
+        if constexpr (BF16) {
+            lo = __uint_as_float(u[i] << 16);
+            hi = __uint_as_float(u[i] & 0xffff0000u);
+        } else {
+            const __half2 h = *reinterpret_cast<const __half2*>(&u[i]);
+            lo = __low2float(h);
+            hi = __high2float(h);
+        }
+        s = fmaf(lo, lo, s);
+        s = fmaf(hi, hi, s);
+    }
+    return s;
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const GemmArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * kTileN, m0 = blockIdx.y * kTileM;
+    const int n_k = (a.K + kStepK - 1) / kStepK;  // a ragged last step reads zeros (TMA fills what lies outside the matrices)
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + kStages * kStageBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    auto a_stage = [&](int s) { return base + (uint32_t)s * kStageBytes; };
+    auto b_stage = [&](int s) { return base + (uint32_t)s * kStageBytes + kABytes; };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar(B_FULL + s), 1);
+            mbar_init(bar(B_EMPTY + s), 5);  // the MMA warp's commit + the four row-statistics warps
+        }
+        mbar_init(bar(B_ACC), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 5) tmem_alloc(smem_u32(tmem_slot), kTileN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    bool timed_out = false;
+
+    if (warp == 4) {
+        // ============================ TMA producer ============================
+        if (lane == 0) {
+            for (int kb = 0; kb < n_k; ++kb) {
+                const int s = kb % kStages;
+                if (!mbar_wait(bar(B_EMPTY + s), ((kb / kStages) & 1) ^ 1)) { timed_out = true; break; }
+                mbar_expect_tx(bar(B_FULL + s), kStageBytes);
+                tma_load_2d(a_stage(s), &amap, bar(B_FULL + s), kb * kStepK, m0);
+#pragma unroll
+                for (int nb = 0; nb < kTileN / 64; ++nb)
+                    tma_load_2d(b_stage(s) + nb * kBBlockBytes, &bmap, bar(B_FULL + s), n0 + nb * 64, kb * kStepK);
+            }
+        }
+    } else if (warp == 5) {
+        // ============================ MMA issuer ==============================
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BF16, kTileM, kTileN);
+            bool ok = true;
+            for (int kb = 0; kb < n_k && ok; ++kb) {
+                const int s = kb % kStages;
+                ok = mbar_wait(bar(B_FULL + s), (kb / kStages) & 1);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < kStepK / 16; ++ks)
+                    mma_ss(tmem, smem_desc(a_stage(s) + ks * 32, 16, 1024), smem_desc(b_stage(s) + ks * 2048, kBBlockBytes, 1024), idesc,
+                           (kb > 0 || ks > 0));
+                tc_commit(bar(B_EMPTY + s));
+            }
+            if (ok) tc_commit(bar(B_ACC));
+            timed_out = !ok;
+        }
+    } else {
+        // ================= row statistics, then the epilogue ==================
+        const int row = threadIdx.x;  // 0..127 = tensor-memory lane = row of the tile
+        float ss = 0.f;
+        bool ok = true;
+        for (int kb = 0; kb < n_k && ok; ++kb) {
+            const int s = kb % kStages;
+            ok = mbar_wait(bar(B_FULL + s), (kb / kStages) & 1);
+            if (!ok) break;
+            const uint4* rowp = reinterpret_cast<const uint4*>(base_ptr + (size_t)s * kStageBytes + (size_t)row * 128);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) ss += sumsq8<BF16>(rowp[(c + row) & 7]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_EMPTY + s));
+        }
+        if (ok) ok = mbar_wait(bar(B_ACC), 0);
+        if (ok) {
+            tc_fence_after();
+            const float rstd = rsqrtf(ss / (float)a.K + a.eps);
+            const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+            const bool row_ok = m0 + row < a.M;
+            uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(m0 + row) * a.out_stride + n0;
+#pragma unroll 1
+            for (int ch = 0; ch < kTileN / 32; ++ch) {
+                float v[32];
+                tmem_ld32(lane_base + ch * 32, v);
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (n0 + ch * 32 + i * 8 < a.N) {  // N is a multiple of 8: a 16-byte piece is inside or outside as a whole
+                            uint4 w;
+                            w.x = pack2<BF16>(v[8 * i] * rstd, v[8 * i + 1] * rstd);
+                            w.y = pack2<BF16>(v[8 * i + 2] * rstd, v[8 * i + 3] * rstd);
+                            w.z = pack2<BF16>(v[8 * i + 4] * rstd, v[8 * i + 5] * rstd);
+                            w.w = pack2<BF16>(v[8 * i + 6] * rstd, v[8 * i + 7] * rstd);
+                            *reinterpret_cast<uint4*>(dst + ch * 32 + i * 8) = w;
+                        }
+                    }
+                }
+            }
+        }
+        timed_out = !ok;
+    }
+    if (timed_out && a.status && lane == 0) atomicOr(a.status, SFB_STATUS_WAIT_TIMEOUT);
+    // ---- teardown: every warp arrives here; tensor memory is released before exit
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTileN);
+    }
+}
+
+template <typename T>
+__global__ void fold_norm_weight_kernel(const T* __restrict__ g, const T* __restrict__ w, T* __restrict__ out, int64_t K, int64_t N,
+                                        int64_t w_stride, int64_t out_stride) {
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;  // eight columns per thread
+    if (i >= K * N) return;
+    const int64_t k = i / N, n = i - k * N;  // N is a multiple of 8
+    const float gk = to_float(g[k]);
+    const uint4 raw = *reinterpret_cast<const uint4*>(w + k * w_stride + n);
+    const T* x = reinterpret_cast<const T*>(&raw);
+    uint4 res;
+    T* y = reinterpret_cast<T*>(&res);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = from_float<T>(to_float(x[j]) * gk);
+    *reinterpret_cast<uint4*>(out + k * out_stride + n) = res;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static std::once_flag once;
+    static EncodeTiledFn fn = nullptr;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 2-D map over a row-major 16-bit matrix [rows, cols] with a [box_rows x 64 columns] (128-byte wide) box.
+bool encode_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t row_stride_elems, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)row_stride_elems * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    const cuuint32_t es[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+int launch_fold_norm_weight(const void* g, const void* w, void* out, int64_t K, int64_t N, int64_t w_stride, int64_t out_stride,
+                            int dtype, cudaStream_t stream) {
+    const int64_t groups = K * N / 8;
+    const unsigned blocks = (unsigned)ceil_div(groups, (int64_t)256);
+    if (dtype == SFB_BF16)
+        fold_norm_weight_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(g), static_cast<const __nv_bfloat16*>(w),
+                                                            static_cast<__nv_bfloat16*>(out), K, N, w_stride, out_stride);
+    else
+        fold_norm_weight_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __half*>(g), static_cast<const __half*>(w),
+                                                            static_cast<__half*>(out), K, N, w_stride, out_stride);
+    SFB_CUDA_CHECK(cudaGetLastError());
+    return SFB_OK;
+}
+
+int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t wg_stride, void* out, int64_t out_stride, int64_t M,
+                       int64_t N, int64_t K, float eps, int dtype, int* status, cudaStream_t stream) {
+    CUtensorMap amap, bmap;
+    if (!encode_2d(&amap, x, M, K, x_stride, kTileM) || !encode_2d(&bmap, wg, K, N, wg_stride, kStepK))
+        return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: tensor map encoding failed (16-byte aligned bases and row strides are required)");
+    GemmArgs a{};
+    a.out = out; a.out_stride = out_stride;
+    a.M = (int)M; a.N = (int)N; a.K = (int)K;
+    a.eps = eps; a.status = status;
+    const dim3 grid((unsigned)ceil_div(N, (int64_t)kTileN), (unsigned)ceil_div(M, (int64_t)kTileM));
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(norm_matmul_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(norm_matmul_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    });
+    SFB_CUDA_CHECK(attr_err);
+    if (dtype == SFB_BF16) norm_matmul_tcgen05_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(amap, bmap, a);
+    else norm_matmul_tcgen05_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(amap, bmap, a);
+    SFB_CUDA_CHECK(cudaGetLastError());
+    return SFB_OK;
+}
+
+}  // namespace sfb

@@ -67,7 +67,9 @@ class B200Backend(OpExecutor):
             "flash_attention": self._op_flash_attention,
             "scaled_dot_product_attention": self._op_scaled_dot_product_attention,
             "chunked_prefill": self._op_chunked_prefill,
+            "fused_rms_norm_matmul": self._op_fused_rms_norm_matmul,
         }
+        self._folded: dict[tuple, torch.Tensor] = {}
 
     def supported_ops(self) -> list[str]:
         return sorted(self._ops)
@@ -167,6 +169,26 @@ class B200Backend(OpExecutor):
                 raise ValueError("scaled_dot_product_attention: explicit masks and dropout need a fallback executor")
             return self._fallback.execute("scaled_dot_product_attention", inputs, **kw)
         return kernels_api.flash_attention_fwd(q, k, v, scale=kw.get("scale"), causal=causal)
+
+    def _op_fused_rms_norm_matmul(self, inputs: list[Any], **kw: Any) -> torch.Tensor:
+        """``[x, rms_weight, mat_weight]`` with ``eps`` (default 1e-5), as pytorch_backend/_ops_norm.py:47-65:
+        ``rms_norm(x) * rms_weight @ mat_weight``, result in x's dtype.  The folded weight ``diag(rms_weight) mat_weight``
+        is built on first use of a weight pair and kept (keyed by the two tensors' storage and version counters).
+        fp32 and unaligned shapes go to the fallback executor."""
+        x, g, w = inputs[0], inputs[1], inputs[-1]
+        own = (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and w.dtype == x.dtype and g.dtype == x.dtype and w.dim() == 2
+               and w.shape[0] == x.shape[-1] and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0 and w.stride(1) == 1 and x.stride(-1) == 1)
+        if not own:
+            if self._fallback is None:
+                raise ValueError("fused_rms_norm_matmul: bf16 / fp16 with K and N multiples of 8, or a fallback executor")
+            return self._fallback.execute("fused_rms_norm_matmul", inputs, **kw)
+        key = (g.data_ptr(), g._version, w.data_ptr(), w._version, tuple(w.shape))
+        folded = self._folded.get(key)
+        if folded is None:
+            if len(self._folded) >= 256:
+                self._folded.clear()
+            folded = self._folded[key] = ops.fold_norm_weight(g.contiguous(), w)
+        return ops.fused_rms_norm_matmul(x, folded, eps=kw.get("eps", 1e-5))
 
     def _op_chunked_prefill(self, inputs: list[Any], **kw: Any) -> torch.Tensor:
         """inputs ``[query [T,H,D], key_cache, value_cache, block_table [R,max_blocks]]``

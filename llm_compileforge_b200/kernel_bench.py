@@ -97,6 +97,26 @@ def bench_prefill(dev, iters):
             "status": ops.read_status(ws)}
 
 
+def bench_norm_matmul(dev, iters, m=16384, k=4096, n=6144):
+    """Llama-3-8B's input norm + fused QKV projection over 16384 tokens (prefill-sized), and the same weight at 256 rows."""
+    x, rw, w, eps = wl.make_norm_matmul_inputs(m, k, n)
+    x, rw, w = x.to(dev), rw.to(dev), w.to(dev)
+    folded = ops.fold_norm_weight(rw, w)
+    out = torch.empty((m, n), dtype=x.dtype, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    fn = lambda: ops.fused_rms_norm_matmul(x, folded, eps=eps, out=out, status=status)
+    ms = time_ms(fn, iters)
+    xn = torch.empty_like(x)
+    lib = lambda: torch.matmul(ops.rms_norm(x, rw, eps=eps, out=xn), w, out=out)  # unfused: norm kernel, then the library GEMM
+    ms_lib = time_ms(lib, iters)
+    flops = 2.0 * m * n * k
+    pk = _peaks()
+    return {"kernel": "norm_matmul_tcgen05", "workload": f"rms_norm + matmul, x [{m}, {k}] bf16, W [{k}, {n}]", "ms": ms,
+            "flops": flops, "achieved_tflops": flops / ms / 1e9, "peak_tflops": pk["bf16_tflops_sustained"],
+            "frac": flops / ms / 1e9 / pk["bf16_tflops_sustained"], "frac_of_burst": flops / ms / 1e9 / pk["bf16_tflops"],
+            "ms_unfused_norm_then_library_gemm": ms_lib, "peak_kind": pk["kind"], "status": int(status.item())}
+
+
 def bench_append(dev, iters):
     shape = wl.C3
     lengths = wl.config_lengths(shape)
@@ -204,7 +224,7 @@ def bench_shared_prefix(dev, iters, n_requests=32):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="prefill,append,norm,decode_c2,decode_c3,shared_prefix")
+    ap.add_argument("--only", default="prefill,norm_matmul,append,norm,decode_c2,decode_c3,shared_prefix")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--chunk-tokens", type=int, default=0)
     args = ap.parse_args()
@@ -216,6 +236,9 @@ def main() -> None:
     sys.path.insert(0, ROOT)
     if "prefill" in which:
         print(json.dumps(bench_prefill(dev, args.iters)), flush=True)
+    if "norm_matmul" in which:
+        print(json.dumps(bench_norm_matmul(dev, args.iters)), flush=True)
+        print(json.dumps(bench_norm_matmul(dev, args.iters, m=256)), flush=True)
     if "append" in which:
         print(json.dumps(bench_append(dev, args.iters)), flush=True)
     if "norm" in which:

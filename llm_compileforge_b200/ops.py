@@ -319,3 +319,29 @@ def paged_attention_decode_shared_prefix(
         current_stream(q.device),
     ))
     return out
+
+
+def fold_norm_weight(rms_weight: torch.Tensor, mat_weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``diag(rms_weight) @ mat_weight`` (``[K] , [K,N] -> [K,N]``): the weight :func:`fused_rms_norm_matmul` multiplies by.
+    Done once per weight pair; weights do not change while serving."""
+    if out is None:
+        out = torch.empty_like(mat_weight)
+    check(_lib.load().sfb_fold_norm_weight(desc(rms_weight, "rms_weight"), desc(mat_weight, "mat_weight"), desc(out, "folded"),
+                                           dtype_code(mat_weight.dtype), current_stream(mat_weight.device)))
+    return out
+
+
+def fused_rms_norm_matmul(x: torch.Tensor, folded_weight: torch.Tensor, eps: float = 1e-5, out: torch.Tensor | None = None,
+                          status: torch.Tensor | None = None) -> torch.Tensor:
+    """``rms_norm(x) @ W`` with the norm's weight already folded into ``folded_weight`` (:func:`fold_norm_weight`):
+    ``x [..., K]`` bf16 / fp16, result ``[..., N]``; one tcgen05 GEMM on the raw activations, the row factor applied to the
+    accumulators.  ``status`` (int32 ``[1]`` on the device) collects the kernel's timeout bit."""
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    n = folded_weight.shape[1]
+    if out is None:
+        out = torch.empty((x2.shape[0], n), dtype=x.dtype, device=x.device)
+    out2 = out.reshape(-1, n)
+    check(_lib.load().sfb_fused_rms_norm_matmul(desc(x2, "x"), desc(folded_weight, "folded_weight"), desc(out2, "out"), dtype_code(x.dtype),
+                                                float(eps), status.data_ptr() if status is not None else None, current_stream(x.device)))
+    return out2.reshape(*x.shape[:-1], n)

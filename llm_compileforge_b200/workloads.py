@@ -243,3 +243,13 @@ def make_rms_norm_inputs(rows: int = 256, hidden: int = 4096, dtype: torch.dtype
     x = torch.randn((rows, hidden), generator=g).to(dtype)
     w = (1.0 + 0.02 * torch.randn((hidden,), generator=g)).to(dtype)
     return x, w, 1e-5
+
+
+def make_norm_matmul_inputs(m: int, k: int, n: int, dtype: torch.dtype = torch.bfloat16, seed: int = 1007):
+    """Inputs of ``fused_rms_norm_matmul``: activations N(0,1), norm weight N(1, 0.02), matrix N(0, 1/K) (a projection
+    with unit-variance outputs); eps 1e-5 as in the reference's operator default."""
+    g = _gen(seed)
+    x = torch.randn((m, k), generator=g).to(dtype)
+    rms_w = (1.0 + 0.02 * torch.randn((k,), generator=g)).to(dtype)
+    mat_w = (torch.randn((k, n), generator=g) / math.sqrt(k)).to(dtype)
+    return x, rms_w, mat_w, 1e-5

@@ -2,7 +2,7 @@
 
 Usage (only where the reference checkout is available):
 
-    python tests/golden/make_golden.py /path/to/LLM-CompileForge
+    python tests/golden/make_golden.py /path/to/LLM-CompileForge [--only-norm-matmul]
 
 The reference's functions are imported from that checkout (never copied) and
 run on seeded inputs; inputs and outputs are saved as small ``.npz`` fixtures.
@@ -38,6 +38,27 @@ def dense_tables(tables: dict[str, list[int]]) -> np.ndarray:
     for i, t in enumerate(tables.values()):
         out[i, : len(t)] = t
     return out
+
+
+def norm_matmul_fixture(ref_root: str) -> None:
+    """norm_matmul.npz: the reference backend's fused_rms_norm_matmul (pytorch_backend/_ops_norm.py:47-65) on seeded
+    inputs that tests rebuild from the same generator; only the outputs are stored."""
+    sys.path.insert(0, ref_root)
+    sys.path.insert(0, REPO)
+    from python_runtime.hal.pytorch_backend import PyTorchBackend
+
+    from llm_compileforge_b200 import workloads as wl
+
+    torch.set_num_threads(1)
+    hal = PyTorchBackend("cpu")
+    blob = {}
+    for name, (m, k, n, dt) in {"bf16_a": (70, 256, 264, torch.bfloat16), "bf16_b": (130, 1000, 512, torch.bfloat16),
+                                "f16_a": (5, 64, 8, torch.float16)}.items():
+        x, g, w, eps = wl.make_norm_matmul_inputs(m, k, n, dt)
+        out = hal.execute("fused_rms_norm_matmul", [x, g, w], eps=eps)
+        blob[name + ".out"] = bits(out) if dt == torch.bfloat16 else out.numpy()
+        blob[name + ".shape"] = np.array([m, k, n])
+    np.savez_compressed(os.path.join(HERE, "norm_matmul.npz"), **blob)
 
 
 def main(ref_root: str) -> None:
@@ -235,10 +256,15 @@ def main(ref_root: str) -> None:
     blob["prefill_small.q_sum"] = np.float64(pw.q.double().sum().item())
     np.savez_compressed(os.path.join(HERE, "prefill.npz"), **blob)
 
+    norm_matmul_fixture(ref_root)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if "--only-norm-matmul" in sys.argv:  # adds that one fixture without rewriting the others
+        norm_matmul_fixture(root)
+    else:
+        main(root)

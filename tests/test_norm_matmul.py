@@ -1,0 +1,89 @@
+"""fused_rms_norm_matmul: the oracle restatement against fixtures made by the reference's backend (CPU), and the
+tcgen05 kernel against both (GPU).  Tolerance: the output is one bf16 / fp16 rounding of an fp32 result whose inputs
+differ from the reference's by one extra rounding of the folded weight, so |diff| <= 2e-2 on unit-variance outputs
+and cosine deficit <= 1e-4, the same bounds as the other half-precision operators."""
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_half_close, from_bits, golden
+from llm_compileforge_b200 import workloads as wl
+from oracle import reference_port as ref
+
+CASES = {"bf16_a": torch.bfloat16, "bf16_b": torch.bfloat16, "f16_a": torch.float16}
+
+
+def assert_close_one_ulp(got: torch.Tensor, want: torch.Tensor, what: str) -> None:
+    """2e-2 absolute plus one bf16 unit in the last place of the reference value (2^-7 relative covers it): a result that
+    sits on a rounding boundary may land on either neighbour, and at |y| >= 4 one bf16 step is already 3.1e-2."""
+    from helpers import COS_DEFICIT, cos_deficit
+
+    g, w = got.double(), want.double()
+    excess = ((g - w).abs() - 2.0 ** -7 * w.abs()).max().item()
+    assert excess <= 2e-2, f"{what}: |diff| exceeds 2e-2 + 1 ulp by {excess - 2e-2:.3e}"
+    assert cos_deficit(got, want) <= COS_DEFICIT, what
+
+
+def _want(g, name, dtype):
+    raw = g[name + ".out"]
+    return from_bits(raw, torch.bfloat16) if dtype == torch.bfloat16 else torch.from_numpy(raw)
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_oracle_matches_reference_fixture(name):
+    g = golden("norm_matmul.npz")
+    m, k, n = (int(v) for v in g[name + ".shape"])
+    x, rw, w, eps = wl.make_norm_matmul_inputs(m, k, n, CASES[name])
+    torch.set_num_threads(1)
+    got = ref.fused_rms_norm_matmul(x, rw, w, eps)
+    assert got.dtype == CASES[name]
+    assert torch.equal(got, _want(g, name, CASES[name]))  # same operators in the same order: bit for bit
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", list(CASES))
+def test_kernel_matches_reference_fixture(name):
+    import llm_compileforge_b200 as pkg
+
+    dev = torch.device("cuda:0")
+    g = golden("norm_matmul.npz")
+    m, k, n = (int(v) for v in g[name + ".shape"])
+    x, rw, w, eps = wl.make_norm_matmul_inputs(m, k, n, CASES[name])
+    got = pkg.B200Backend(device=dev).execute("fused_rms_norm_matmul", [x.to(dev), rw.to(dev), w.to(dev)], eps=eps)
+    assert got.dtype == CASES[name] and tuple(got.shape) == (m, n)
+    assert_half_close(got.cpu(), _want(g, name, CASES[name]), what=name)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,k,n", [(1, 64, 8), (128, 64, 256), (129, 72, 264), (300, 4096, 1024), (1000, 520, 776), (2048, 1024, 2304)])
+def test_kernel_matches_oracle_ragged(m, k, n):
+    """Ragged M / N / K (rows past M, columns past N and a partial last K step are zero-filled by TMA and never stored),
+    several K rounds of the four-stage ring, strided input rows; status word stays clean."""
+    from llm_compileforge_b200 import ops
+
+    dev = torch.device("cuda:0")
+    x, rw, w, eps = wl.make_norm_matmul_inputs(m, k, n, torch.bfloat16, seed=m + k + n)
+    wide = torch.zeros((m, k + 8), dtype=torch.bfloat16)
+    wide[:, :k] = x
+    xs = wide.to(dev)[:, :k]  # row stride k + 8
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    folded = ops.fold_norm_weight(rw.to(dev), w.to(dev))
+    assert torch.equal(folded.cpu(), (rw.float()[:, None] * w.float()).to(torch.bfloat16))
+    got = ops.fused_rms_norm_matmul(xs, folded, eps=eps, status=status)
+    want = ref.fused_rms_norm_matmul(x, rw, w, eps)
+    assert int(status.item()) == 0
+    assert_close_one_ulp(got.cpu(), want, what=f"{m}x{k}x{n}")
+    # linearity in the weight: doubling W doubles y exactly (a power of two commutes with every rounding)
+    got2 = ops.fused_rms_norm_matmul(xs, ops.fold_norm_weight(rw.to(dev), (w * 2).to(dev)), eps=eps)
+    assert torch.equal(got2, got * 2)
+
+
+@pytest.mark.gpu
+def test_fp32_goes_to_the_fallback_or_is_refused():
+    import llm_compileforge_b200 as pkg
+
+    dev = torch.device("cuda:0")
+    x, rw, w, eps = wl.make_norm_matmul_inputs(4, 64, 8, torch.float32)
+    with pytest.raises(ValueError):
+        pkg.B200Backend(device=dev).execute("fused_rms_norm_matmul", [x.to(dev), rw.to(dev), w.to(dev)], eps=eps)
