@@ -362,11 +362,15 @@ SFB_API int64_t sfb_bm_sync(SFBBlockManager* bm, void* stream);
  * serving) and sfb_fused_rms_norm_matmul runs y = rstd(x) * (x @ folded) on the tensor
  * cores from the raw activations, taking each row's sum of squares from the tiles it
  * multiplies.  bf16 / fp16, fp32 accumulation, one rounding of y; K and N multiples of 8,
- * rows contiguous and 16-byte aligned.  `status` (device int32 or NULL) receives
- * SFB_STATUS_WAIT_TIMEOUT if a bounded wait inside the kernel ran out. */
+ * rows contiguous and 16-byte aligned.  `workspace` (device, may be NULL) of
+ * sfb_fused_rms_norm_matmul_workspace_bytes(M) bytes: its first word is the status word
+ * (sfb_read_status; SFB_STATUS_WAIT_TIMEOUT if a bounded wait inside the kernel ran out),
+ * the rest holds per-row statistics when M is large enough for a statistics pre-pass to pay
+ * (2048 rows up); without it the statistics are always taken inside the GEMM kernel. */
+SFB_API int64_t sfb_fused_rms_norm_matmul_workspace_bytes(int64_t rows);
 SFB_API int sfb_fold_norm_weight(const SFBTensor* rms_weight, const SFBTensor* mat_weight, SFBTensor* folded, int dtype, void* stream);
 SFB_API int sfb_fused_rms_norm_matmul(const SFBTensor* x, const SFBTensor* folded_weight, SFBTensor* out, int dtype, float eps,
-                                      void* status, void* stream);
+                                      void* workspace, int64_t workspace_bytes, void* stream);
 
 /* ── `_mlir_ciface_*` convention ─────────────────────────────────────────────
  * The reference's runtime calls compiled kernels as

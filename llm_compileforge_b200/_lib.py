@@ -121,7 +121,9 @@ def load() -> ctypes.CDLL:
     lib.sfb_fold_norm_weight.restype = c_int
     lib.sfb_fold_norm_weight.argtypes = [_T, _T, _T, c_int, c_void_p]
     lib.sfb_fused_rms_norm_matmul.restype = c_int
-    lib.sfb_fused_rms_norm_matmul.argtypes = [_T, _T, _T, c_int, c_float, c_void_p, c_void_p]
+    lib.sfb_fused_rms_norm_matmul.argtypes = [_T, _T, _T, c_int, c_float, c_void_p, c_int64, c_void_p]
+    lib.sfb_fused_rms_norm_matmul_workspace_bytes.restype = c_int64
+    lib.sfb_fused_rms_norm_matmul_workspace_bytes.argtypes = [c_int64]
     lib.sfb_peer_signal_wait.restype = c_int
     lib.sfb_peer_signal_wait.argtypes = [POINTER(c_void_p), c_int, c_int, ctypes.c_uint32, c_int, c_void_p, c_void_p]
     _lib = lib

@@ -482,8 +482,13 @@ int sfb_fold_norm_weight(const SFBTensor* rms_weight, const SFBTensor* mat_weigh
     return launch_fold_norm_weight(vg.base, vw.base, vf.base, K, N, vw.stride[2], vf.stride[2], dtype, static_cast<cudaStream_t>(stream));
 }
 
-int sfb_fused_rms_norm_matmul(const SFBTensor* x, const SFBTensor* folded_weight, SFBTensor* out, int dtype, float eps, void* status,
-                              void* stream) {
+int64_t sfb_fused_rms_norm_matmul_workspace_bytes(int64_t rows) {
+    if (rows < 0) return SFB_ERR_INVALID_ARG;
+    return kWorkspaceHeader + ceil_div(rows * 4, 256) * 256;
+}
+
+int sfb_fused_rms_norm_matmul(const SFBTensor* x, const SFBTensor* folded_weight, SFBTensor* out, int dtype, float eps, void* workspace,
+                              int64_t workspace_bytes, void* stream) {
     if (dtype != SFB_BF16 && dtype != SFB_F16) return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: bf16 or fp16 (other types go to the fallback executor)");
     View vx, vw, vo;
     int rc;
@@ -497,8 +502,15 @@ int sfb_fused_rms_norm_matmul(const SFBTensor* x, const SFBTensor* folded_weight
     if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: dimension too large");
     if (M == 0 || N == 0) return SFB_OK;
     if (K == 0) return fail(SFB_ERR_INVALID_ARG, "fused_rms_norm_matmul: K is zero");
-    return launch_norm_matmul(vx.base, vx.stride[2], vw.base, vw.stride[2], vo.base, vo.stride[2], M, N, K, eps, dtype,
-                              static_cast<int*>(status), static_cast<cudaStream_t>(stream));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int* status = nullptr;
+    float* rstd = nullptr;
+    if (workspace && workspace_bytes >= kWorkspaceHeader) {
+        status = static_cast<int*>(workspace);
+        SFB_CUDA_CHECK(cudaMemsetAsync(status, 0, 4, st));
+        if (workspace_bytes >= sfb_fused_rms_norm_matmul_workspace_bytes(M)) rstd = reinterpret_cast<float*>(static_cast<char*>(workspace) + kWorkspaceHeader);
+    }
+    return launch_norm_matmul(vx.base, vx.stride[2], vw.base, vw.stride[2], vo.base, vo.stride[2], M, N, K, eps, dtype, status, rstd, st);
 }
 
 static int quant_views(const SFBTensor* x, const SFBTensor* codes, const SFBTensor* scales, int x_dtype, int granularity,

@@ -7,8 +7,10 @@
 // The row factor commutes with the contraction:  y[m, :] = rstd[m] * ( x[m, :] @ (diag(g) W) ).
 // So the weight is folded once (fold_norm_weight_kernel: Wg = diag(g) W, weights are static in serving), the
 // GEMM runs on the RAW activations straight out of HBM - the normalised activations are never written or
-// re-read - and the sum of squares of each row is taken from the very A tiles the tensor core consumes,
-// by the epilogue warps, while the MMAs run; rstd scales the accumulators on their way out.
+// re-read - and rstd scales the accumulators on their way out.  Where rstd comes from depends on M: for few rows
+// (decode) the epilogue warps take each row's sum of squares from the very A tiles the tensor core consumes, while
+// the MMAs run, so the operator stays one launch; those shared-memory reads cost the MMAs about a tenth of their
+// operand bandwidth, so for many rows (prefill) a pre-pass (row_rstd_kernel, x read once) supplies rstd instead.
 //
 // One thread block = one 128 x 256 tile of y:
 //   warp 4    TMA producer: per 64-wide K step a [128 rows x 128 B] box of x (K-major, 128B swizzle) and four
@@ -39,6 +41,7 @@ constexpr int kBBytes = (kTileN / 64) * kBBlockBytes;  // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kThreads = 192;
 constexpr uint32_t kSpin = 1u << 21;
+constexpr int64_t kPrepassRows = 2048;  // from this many rows on, row statistics come from a pre-pass instead of the A tiles
 
 enum { B_FULL = 0, B_EMPTY = kStages, B_ACC = 2 * kStages, B_COUNT = 2 * kStages + 1 };
 constexpr int kSmemBytes = kStages * kStageBytes + B_COUNT * 8 + 16 + 1024;
@@ -49,6 +52,7 @@ struct GemmArgs {
     int M, N, K;
     float eps;
     int* status;
+    const float* rstd;  // per-row rsqrt(mean(x^2) + eps) from the statistics pre-pass; nullptr: taken in this kernel from the A tiles
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -153,7 +157,7 @@ __device__ __forceinline__ float sumsq8(uint4 w) {  // sum of squares of eight 1
     return s;
 }
 
-template <bool BF16>
+template <bool BF16, bool STATS>
 __global__ void __launch_bounds__(kThreads, 1)
 norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const GemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
@@ -173,7 +177,7 @@ norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(bar(B_FULL + s), 1);
-            mbar_init(bar(B_EMPTY + s), 5);  // the MMA warp's commit + the four row-statistics warps
+            mbar_init(bar(B_EMPTY + s), STATS ? 5 : 1);  // the MMA warp's commit (+ the four row-statistics warps)
         }
         mbar_init(bar(B_ACC), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -223,7 +227,7 @@ norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
         const int row = threadIdx.x;  // 0..127 = tensor-memory lane = row of the tile
         float ss = 0.f;
         bool ok = true;
-        for (int kb = 0; kb < n_k && ok; ++kb) {
+        for (int kb = 0; STATS && kb < n_k && ok; ++kb) {
             const int s = kb % kStages;
             ok = mbar_wait(bar(B_FULL + s), (kb / kStages) & 1);
             if (!ok) break;
@@ -236,7 +240,7 @@ norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
         if (ok) ok = mbar_wait(bar(B_ACC), 0);
         if (ok) {
             tc_fence_after();
-            const float rstd = rsqrtf(ss / (float)a.K + a.eps);
+            const float rstd = STATS ? rsqrtf(ss / (float)a.K + a.eps) : (m0 + row < a.M ? a.rstd[m0 + row] : 0.f);
             const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
             const bool row_ok = m0 + row < a.M;
             uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(m0 + row) * a.out_stride + n0;
@@ -269,6 +273,19 @@ norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
         tc_fence_after();
         tmem_dealloc(tmem, kTileN);
     }
+}
+
+// One warp per row: rstd[m] = rsqrt(mean(x[m, :]^2) + eps), 16-byte loads.
+template <bool BF16>
+__global__ void row_rstd_kernel(const uint16_t* __restrict__ x, int64_t x_stride, int M, int K, float eps, float* __restrict__ rstd) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= M) return;
+    const uint4* p = reinterpret_cast<const uint4*>(x + (int64_t)row * x_stride);
+    float ss = 0.f;
+    for (int i = lane; i < K / 8; i += 32) ss += sumsq8<BF16>(__ldg(p + i));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) rstd[row] = rsqrtf(ss / (float)K + eps);
 }
 
 template <typename T>
@@ -333,27 +350,32 @@ int launch_fold_norm_weight(const void* g, const void* w, void* out, int64_t K, 
 }
 
 int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t wg_stride, void* out, int64_t out_stride, int64_t M,
-                       int64_t N, int64_t K, float eps, int dtype, int* status, cudaStream_t stream) {
+                       int64_t N, int64_t K, float eps, int dtype, int* status, float* rstd_scratch, cudaStream_t stream) {
     CUtensorMap amap, bmap;
     if (!encode_2d(&amap, x, M, K, x_stride, kTileM) || !encode_2d(&bmap, wg, K, N, wg_stride, kStepK))
         return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: tensor map encoding failed (16-byte aligned bases and row strides are required)");
+    const bool bf16 = dtype == SFB_BF16;
+    const bool prepass = rstd_scratch != nullptr && M >= kPrepassRows;
+    if (prepass) {
+        const unsigned blocks = (unsigned)ceil_div(M, (int64_t)8);
+        if (bf16) row_rstd_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(x), x_stride, (int)M, (int)K, eps, rstd_scratch);
+        else row_rstd_kernel<false><<<blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(x), x_stride, (int)M, (int)K, eps, rstd_scratch);
+        SFB_CUDA_CHECK(cudaGetLastError());
+    }
     GemmArgs a{};
     a.out = out; a.out_stride = out_stride;
     a.M = (int)M; a.N = (int)N; a.K = (int)K;
     a.eps = eps; a.status = status;
+    a.rstd = prepass ? rstd_scratch : nullptr;
     const dim3 grid((unsigned)ceil_div(N, (int64_t)kTileN), (unsigned)ceil_div(M, (int64_t)kTileM));
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(norm_matmul_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (attr_err == cudaSuccess)
-            attr_err = cudaFuncSetAttribute(norm_matmul_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    });
-    SFB_CUDA_CHECK(attr_err);
-    if (dtype == SFB_BF16) norm_matmul_tcgen05_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(amap, bmap, a);
-    else norm_matmul_tcgen05_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(amap, bmap, a);
-    SFB_CUDA_CHECK(cudaGetLastError());
-    return SFB_OK;
+    auto launch = [&](auto kernel) -> int {
+        SFB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        kernel<<<grid, kThreads, kSmemBytes, stream>>>(amap, bmap, a);
+        SFB_CUDA_CHECK(cudaGetLastError());
+        return SFB_OK;
+    };
+    if (bf16) return prepass ? launch(norm_matmul_tcgen05_kernel<true, false>) : launch(norm_matmul_tcgen05_kernel<true, true>);
+    return prepass ? launch(norm_matmul_tcgen05_kernel<false, false>) : launch(norm_matmul_tcgen05_kernel<false, true>);
 }
 
 }  // namespace sfb

@@ -283,6 +283,6 @@ int launch_rms_norm(const NormArgs& a, cudaStream_t stream);
 int launch_fold_norm_weight(const void* g, const void* w, void* out, int64_t K, int64_t N, int64_t w_stride, int64_t out_stride,
                             int dtype, cudaStream_t stream);
 int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t wg_stride, void* out, int64_t out_stride, int64_t M,
-                       int64_t N, int64_t K, float eps, int dtype, int* status, cudaStream_t stream);
+                       int64_t N, int64_t K, float eps, int dtype, int* status, float* rstd_scratch, cudaStream_t stream);
 
 }  // namespace sfb

@@ -332,16 +332,23 @@ def fold_norm_weight(rms_weight: torch.Tensor, mat_weight: torch.Tensor, out: to
 
 
 def fused_rms_norm_matmul(x: torch.Tensor, folded_weight: torch.Tensor, eps: float = 1e-5, out: torch.Tensor | None = None,
-                          status: torch.Tensor | None = None) -> torch.Tensor:
+                          workspace: torch.Tensor | None = None) -> torch.Tensor:
     """``rms_norm(x) @ W`` with the norm's weight already folded into ``folded_weight`` (:func:`fold_norm_weight`):
     ``x [..., K]`` bf16 / fp16, result ``[..., N]``; one tcgen05 GEMM on the raw activations, the row factor applied to the
-    accumulators.  ``status`` (int32 ``[1]`` on the device) collects the kernel's timeout bit."""
+    accumulators.  ``workspace`` (uint8, :func:`norm_matmul_workspace_bytes`; allocated when missing) carries the status word
+    (:func:`read_status`) and, from 2048 rows up, the per-row statistics of a pre-pass."""
     k = x.shape[-1]
     x2 = x.reshape(-1, k)
     n = folded_weight.shape[1]
     if out is None:
         out = torch.empty((x2.shape[0], n), dtype=x.dtype, device=x.device)
     out2 = out.reshape(-1, n)
+    if workspace is None:
+        workspace = torch.empty(norm_matmul_workspace_bytes(x2.shape[0]), dtype=torch.uint8, device=x.device)
     check(_lib.load().sfb_fused_rms_norm_matmul(desc(x2, "x"), desc(folded_weight, "folded_weight"), desc(out2, "out"), dtype_code(x.dtype),
-                                                float(eps), status.data_ptr() if status is not None else None, current_stream(x.device)))
+                                                float(eps), workspace.data_ptr(), workspace.numel(), current_stream(x.device)))
     return out2.reshape(*x.shape[:-1], n)
+
+
+def norm_matmul_workspace_bytes(rows: int) -> int:
+    return int(_lib.load().sfb_fused_rms_norm_matmul_workspace_bytes(int(rows)))
