@@ -12,11 +12,13 @@
 // the MMAs run, so the operator stays one launch; those shared-memory reads cost the MMAs about a tenth of their
 // operand bandwidth, so for many rows (prefill) a pre-pass (row_rstd_kernel, x read once) supplies rstd instead.
 //
-// One thread block = one 128 x 256 tile of y:
+// Persistent thread blocks (one per SM) walk the 128 x 256 tiles of y; the accumulator is double-buffered in tensor
+// memory (2 x 256 columns), so tile i drains through the epilogue warps while tile i+1's MMAs run:
 //   warp 4    TMA producer: per 64-wide K step a [128 rows x 128 B] box of x (K-major, 128B swizzle) and four
 //             [64 k x 128 B] boxes of Wg (N-major), four stages
 //   warp 5    issues tcgen05.mma.cta_group::1.kind::f16, M 128, N 256, K 16, four per stage, accumulator =
-//             256 tensor-memory columns of fp32; tcgen05.commit frees the stage / publishes the accumulator
+//             256 tensor-memory columns of fp32 (two of them, alternating); tcgen05.commit frees the stage /
+//             publishes the accumulator
 //   warps 0-3 one thread per output row: reads its row of every A stage from shared memory (16-byte chunks in
 //             a rotated order, so a quarter-warp never hits one bank twice; the swizzle only permutes chunks
 //             inside the row, the sum does not care), then tcgen05.ld the accumulator row, times rstd, 16-bit
@@ -27,6 +29,7 @@
 
 #include <cuda.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "sfb_common.cuh"
@@ -37,19 +40,19 @@ namespace {
 constexpr int kTileM = 128, kTileN = 256, kStepK = 64, kStages = 4;
 constexpr int kABytes = kTileM * kStepK * 2;       // 16 KB
 constexpr int kBBlockBytes = kStepK * 128;         // one [64 k][64 n] block: 8 KB
-constexpr int kBBytes = (kTileN / 64) * kBBlockBytes;  // 32 KB
-constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kThreads = 192;
 constexpr uint32_t kSpin = 1u << 21;
 constexpr int64_t kPrepassRows = 2048;  // from this many rows on, row statistics come from a pre-pass instead of the A tiles
 
-enum { B_FULL = 0, B_EMPTY = kStages, B_ACC = 2 * kStages, B_COUNT = 2 * kStages + 1 };
-constexpr int kSmemBytes = kStages * kStageBytes + B_COUNT * 8 + 16 + 1024;
+enum { B_FULL = 0, B_EMPTY = kStages, B_ACC_FULL = 2 * kStages, B_ACC_EMPTY = 2 * kStages + 2, B_COUNT = 2 * kStages + 4 };
+constexpr int smem_bytes(int tn) { return kStages * (kABytes + (tn / 64) * kBBlockBytes) + B_COUNT * 8 + 16 + 1024; }
+constexpr int kNarrowN = 64;  // column width of the tiles used when 256-wide tiles would leave most SMs without one
 
 struct GemmArgs {
     void* out;
     int64_t out_stride;  // elements between output rows
     int M, N, K;
+    int tiles_n, tiles_total;
     float eps;
     int* status;
     const float* rstd;  // per-row rsqrt(mean(x^2) + eps) from the statistics pre-pass; nullptr: taken in this kernel from the A tiles
@@ -157,95 +160,116 @@ __device__ __forceinline__ float sumsq8(uint4 w) {  // sum of squares of eight 1
     return s;
 }
 
-template <bool BF16, bool STATS>
+template <bool BF16, bool STATS, int TN>
 __global__ void __launch_bounds__(kThreads, 1)
 norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const GemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kTileN, m0 = blockIdx.y * kTileM;
+    constexpr int kStage = kABytes + (TN / 64) * kBBlockBytes;  // bytes per pipeline stage
     const int n_k = (a.K + kStepK - 1) / kStepK;  // a ragged last step reads zeros (TMA fills what lies outside the matrices)
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + kStages * kStageBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + kStages * kStage);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
-    auto a_stage = [&](int s) { return base + (uint32_t)s * kStageBytes; };
-    auto b_stage = [&](int s) { return base + (uint32_t)s * kStageBytes + kABytes; };
+    auto a_stage = [&](int s) { return base + (uint32_t)s * kStage; };
+    auto b_stage = [&](int s) { return base + (uint32_t)s * kStage + kABytes; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(bar(B_FULL + s), 1);
             mbar_init(bar(B_EMPTY + s), STATS ? 5 : 1);  // the MMA warp's commit (+ the four row-statistics warps)
         }
-        mbar_init(bar(B_ACC), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(B_ACC_FULL + i), 1);
+            mbar_init(bar(B_ACC_EMPTY + i), 4);  // the four epilogue warps
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 5) tmem_alloc(smem_u32(tmem_slot), kTileN);
+    if (warp == 5) tmem_alloc(smem_u32(tmem_slot), 2 * TN);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     bool timed_out = false;
 
+    // Persistent: thread block b works on tiles b, b + gridDim.x, ...; tile index -> (row block, column block) with the
+    // column block running fastest, so the blocks in flight share a few row blocks of x.  `it` counts this block's
+    // tiles, g = it * n_k + kb its K steps: stage g % kStages, accumulator it & 1.
     if (warp == 4) {
         // ============================ TMA producer ============================
         if (lane == 0) {
-            for (int kb = 0; kb < n_k; ++kb) {
-                const int s = kb % kStages;
-                if (!mbar_wait(bar(B_EMPTY + s), ((kb / kStages) & 1) ^ 1)) { timed_out = true; break; }
-                mbar_expect_tx(bar(B_FULL + s), kStageBytes);
-                tma_load_2d(a_stage(s), &amap, bar(B_FULL + s), kb * kStepK, m0);
+            int g = 0;
+            for (int tile = blockIdx.x; tile < a.tiles_total && !timed_out; tile += gridDim.x) {
+                const int m0 = (tile / a.tiles_n) * kTileM, n0 = (tile % a.tiles_n) * TN;
+                for (int kb = 0; kb < n_k; ++kb, ++g) {
+                    const int s = g % kStages;
+                    if (!mbar_wait(bar(B_EMPTY + s), ((g / kStages) & 1) ^ 1)) { timed_out = true; break; }
+                    mbar_expect_tx(bar(B_FULL + s), kStage);
+                    tma_load_2d(a_stage(s), &amap, bar(B_FULL + s), kb * kStepK, m0);
 #pragma unroll
-                for (int nb = 0; nb < kTileN / 64; ++nb)
-                    tma_load_2d(b_stage(s) + nb * kBBlockBytes, &bmap, bar(B_FULL + s), n0 + nb * 64, kb * kStepK);
+                    for (int nb = 0; nb < TN / 64; ++nb)
+                        tma_load_2d(b_stage(s) + nb * kBBlockBytes, &bmap, bar(B_FULL + s), n0 + nb * 64, kb * kStepK);
+                }
             }
         }
     } else if (warp == 5) {
         // ============================ MMA issuer ==============================
         if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc(BF16, kTileM, kTileN);
+            constexpr uint32_t idesc = instr_desc(BF16, kTileM, TN);
             bool ok = true;
-            for (int kb = 0; kb < n_k && ok; ++kb) {
-                const int s = kb % kStages;
-                ok = mbar_wait(bar(B_FULL + s), (kb / kStages) & 1);
+            int g = 0, it = 0;
+            for (int tile = blockIdx.x; tile < a.tiles_total && ok; tile += gridDim.x, ++it) {
+                const int buf = it & 1;
+                ok = mbar_wait(bar(B_ACC_EMPTY + buf), ((it >> 1) & 1) ^ 1);  // the epilogue has drained this accumulator
                 if (!ok) break;
                 tc_fence_after();
+                for (int kb = 0; kb < n_k && ok; ++kb, ++g) {
+                    const int s = g % kStages;
+                    ok = mbar_wait(bar(B_FULL + s), (g / kStages) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < kStepK / 16; ++ks)
-                    mma_ss(tmem, smem_desc(a_stage(s) + ks * 32, 16, 1024), smem_desc(b_stage(s) + ks * 2048, kBBlockBytes, 1024), idesc,
-                           (kb > 0 || ks > 0));
-                tc_commit(bar(B_EMPTY + s));
+                    for (int ks = 0; ks < kStepK / 16; ++ks)
+                        mma_ss(tmem + buf * TN, smem_desc(a_stage(s) + ks * 32, 16, 1024),
+                               smem_desc(b_stage(s) + ks * 2048, kBBlockBytes, 1024), idesc, (kb > 0 || ks > 0));
+                    tc_commit(bar(B_EMPTY + s));
+                }
+                if (ok) tc_commit(bar(B_ACC_FULL + buf));
             }
-            if (ok) tc_commit(bar(B_ACC));
             timed_out = !ok;
         }
     } else {
         // ================= row statistics, then the epilogue ==================
         const int row = threadIdx.x;  // 0..127 = tensor-memory lane = row of the tile
-        float ss = 0.f;
         bool ok = true;
-        for (int kb = 0; STATS && kb < n_k && ok; ++kb) {
-            const int s = kb % kStages;
-            ok = mbar_wait(bar(B_FULL + s), (kb / kStages) & 1);
-            if (!ok) break;
-            const uint4* rowp = reinterpret_cast<const uint4*>(base_ptr + (size_t)s * kStageBytes + (size_t)row * 128);
+        int g = 0, it = 0;
+        for (int tile = blockIdx.x; tile < a.tiles_total && ok; tile += gridDim.x, ++it) {
+            const int m0 = (tile / a.tiles_n) * kTileM, n0 = (tile % a.tiles_n) * TN;
+            const int buf = it & 1;
+            float ss = 0.f;
+            for (int kb = 0; STATS && kb < n_k && ok; ++kb, ++g) {
+                const int s = g % kStages;
+                ok = mbar_wait(bar(B_FULL + s), (g / kStages) & 1);
+                if (!ok) break;
+                const uint4* rowp = reinterpret_cast<const uint4*>(base_ptr + (size_t)s * kStage + (size_t)row * 128);
 #pragma unroll
-            for (int c = 0; c < 8; ++c) ss += sumsq8<BF16>(rowp[(c + row) & 7]);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(B_EMPTY + s));
-        }
-        if (ok) ok = mbar_wait(bar(B_ACC), 0);
-        if (ok) {
+                for (int c = 0; c < 8; ++c) ss += sumsq8<BF16>(rowp[(c + row) & 7]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_EMPTY + s));
+            }
+            if (ok) ok = mbar_wait(bar(B_ACC_FULL + buf), (it >> 1) & 1);
+            if (!ok) break;
             tc_fence_after();
-            const float rstd = STATS ? rsqrtf(ss / (float)a.K + a.eps) : (m0 + row < a.M ? a.rstd[m0 + row] : 0.f);
-            const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
             const bool row_ok = m0 + row < a.M;
+            const float rstd = STATS ? rsqrtf(ss / (float)a.K + a.eps) : (row_ok ? a.rstd[m0 + row] : 0.f);
+            const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16) + buf * TN;
             uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(m0 + row) * a.out_stride + n0;
 #pragma unroll 1
-            for (int ch = 0; ch < kTileN / 32; ++ch) {
+            for (int ch = 0; ch < TN / 32; ++ch) {
                 float v[32];
                 tmem_ld32(lane_base + ch * 32, v);
                 if (row_ok) {
@@ -262,6 +286,10 @@ norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
                     }
                 }
             }
+            // the accumulator goes back to the MMA warp: the next-but-one tile may overwrite it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + buf));
         }
         timed_out = !ok;
     }
@@ -271,7 +299,7 @@ norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
     __syncthreads();
     if (warp == 5) {
         tc_fence_after();
-        tmem_dealloc(tmem, kTileN);
+        tmem_dealloc(tmem, 2 * TN);
     }
 }
 
@@ -367,15 +395,33 @@ int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t 
     a.M = (int)M; a.N = (int)N; a.K = (int)K;
     a.eps = eps; a.status = status;
     a.rstd = prepass ? rstd_scratch : nullptr;
-    const dim3 grid((unsigned)ceil_div(N, (int64_t)kTileN), (unsigned)ceil_div(M, (int64_t)kTileM));
-    auto launch = [&](auto kernel) -> int {
-        SFB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        kernel<<<grid, kThreads, kSmemBytes, stream>>>(amap, bmap, a);
+    int dev = 0, sms = 0;
+    SFB_CUDA_CHECK(cudaGetDevice(&dev));
+    SFB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int64_t m_tiles = ceil_div(M, (int64_t)kTileM);
+    // few rows (decode): 256-wide tiles would give fewer thread blocks than SMs and each would stream its whole
+    // column block of the weight alone; 64-wide tiles spread the weight over four times as many blocks, two per SM
+    const bool narrow = m_tiles * ceil_div(N, (int64_t)kTileN) < sms;
+    const int tn = narrow ? kNarrowN : kTileN;
+    const int64_t tiles_n = ceil_div(N, (int64_t)tn), tiles = tiles_n * m_tiles;
+    if (tiles > 0x7fffffffLL) return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: too many tiles");
+    a.tiles_n = (int)tiles_n;
+    a.tiles_total = (int)tiles;
+    const dim3 grid((unsigned)std::min<int64_t>(tiles, narrow ? 2 * sms : sms));  // persistent thread blocks walk the tiles
+    auto launch = [&](auto kernel, int smem) -> int {
+        SFB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        kernel<<<grid, kThreads, smem, stream>>>(amap, bmap, a);
         SFB_CUDA_CHECK(cudaGetLastError());
         return SFB_OK;
     };
-    if (bf16) return prepass ? launch(norm_matmul_tcgen05_kernel<true, false>) : launch(norm_matmul_tcgen05_kernel<true, true>);
-    return prepass ? launch(norm_matmul_tcgen05_kernel<false, false>) : launch(norm_matmul_tcgen05_kernel<false, true>);
+    if (narrow) {
+        constexpr int sm = smem_bytes(kNarrowN);
+        if (bf16) return prepass ? launch(norm_matmul_tcgen05_kernel<true, false, kNarrowN>, sm) : launch(norm_matmul_tcgen05_kernel<true, true, kNarrowN>, sm);
+        return prepass ? launch(norm_matmul_tcgen05_kernel<false, false, kNarrowN>, sm) : launch(norm_matmul_tcgen05_kernel<false, true, kNarrowN>, sm);
+    }
+    constexpr int sm = smem_bytes(kTileN);
+    if (bf16) return prepass ? launch(norm_matmul_tcgen05_kernel<true, false, kTileN>, sm) : launch(norm_matmul_tcgen05_kernel<true, true, kTileN>, sm);
+    return prepass ? launch(norm_matmul_tcgen05_kernel<false, false, kTileN>, sm) : launch(norm_matmul_tcgen05_kernel<false, true, kTileN>, sm);
 }
 
 }  // namespace sfb
