@@ -95,23 +95,32 @@ __global__ void __launch_bounds__(kThreads) rms_norm_vec_kernel(NormArgs a) {
     T* out = reinterpret_cast<T*>(a.out) + row * a.out_stride;
     const T* w = reinterpret_cast<const T*>(a.weight);
     const int n_chunks = (int)(a.hidden / N);
-    float vals[CH][N];
+    // The row stays in registers as the raw 16-byte words (and the residual's, when there is one): half the registers
+    // of the unpacked floats, so more rows are in flight per SM; unpacking twice costs a few ALU instructions.
+    uint4 raw[CH], rraw[RES ? CH : 1];
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < CH; ++j) {
         const int c = threadIdx.x + j * kThreads;
         if (c < n_chunks) {
-            uint4 raw = ldg_stream(x + (int64_t)c * N);
-            Pack<T>::unpack(raw, vals[j]);
+            raw[j] = ldg_stream(x + (int64_t)c * N);
+            if (RES) rraw[j] = ldg_stream(res + (int64_t)c * N);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+        const int c = threadIdx.x + j * kThreads;
+        if (c < n_chunks) {
+            float v[N];
+            Pack<T>::unpack(raw[j], v);
             if (RES) {
                 float r[N];
-                uint4 rr = ldg_stream(res + (int64_t)c * N);
-                Pack<T>::unpack(rr, r);
+                Pack<T>::unpack(rraw[j], r);
 #pragma unroll
-                for (int e = 0; e < N; ++e) vals[j][e] += r[e];
+                for (int e = 0; e < N; ++e) v[e] += r[e];
             }
 #pragma unroll
-            for (int e = 0; e < N; ++e) ss = fmaf(vals[j][e], vals[j][e], ss);
+            for (int e = 0; e < N; ++e) ss = fmaf(v[e], v[e], ss);
         }
     }
     ss = block_sum(ss, scratch);
@@ -120,16 +129,23 @@ __global__ void __launch_bounds__(kThreads) rms_norm_vec_kernel(NormArgs a) {
     for (int j = 0; j < CH; ++j) {
         const int c = threadIdx.x + j * kThreads;
         if (c < n_chunks) {
-            float o[N];
+            float v[N], o[N];
+            Pack<T>::unpack(raw[j], v);
+            if (RES) {
+                float r[N];
+                Pack<T>::unpack(rraw[j], r);
+#pragma unroll
+                for (int e = 0; e < N; ++e) v[e] += r[e];
+            }
             if (w) {
                 float wv[N];
                 uint4 wr = *reinterpret_cast<const uint4*>(w + (int64_t)c * N);
                 Pack<T>::unpack(wr, wv);
 #pragma unroll
-                for (int e = 0; e < N; ++e) o[e] = vals[j][e] * inv * wv[e];
+                for (int e = 0; e < N; ++e) o[e] = v[e] * inv * wv[e];
             } else {
 #pragma unroll
-                for (int e = 0; e < N; ++e) o[e] = vals[j][e] * inv;
+                for (int e = 0; e < N; ++e) o[e] = v[e] * inv;
             }
             *reinterpret_cast<uint4*>(out + (int64_t)c * N) = Pack<T>::pack(o);
         }

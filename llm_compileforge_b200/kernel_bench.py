@@ -162,12 +162,13 @@ def bench_norm(dev, iters, rows):
     out = torch.empty_like(x)
     fn = lambda: ops.rms_norm(x, w, eps, out=out)
     ms = time_ms(fn, iters, flush=L2Flush(dev))
+    ms_copy = time_ms(lambda: out.copy_(x), iters, flush=L2Flush(dev))  # a plain copy of the same bytes, for scale
     byts = wl.rms_norm_algorithmic_bytes(rows, x.shape[1], 2)
     p = _peaks()
     gbs = byts / (ms / 1e3) / 1e9
     return {"kernel": "rms_norm_vec_kernel", "workload": f"[{rows}, 4096] bf16, eps 1e-5, L2 flushed between iterations", "ms": ms,
             "bytes": byts, "achieved_gbs": gbs, "peak_gbs": p["hbm_gbs"], "frac": gbs / p["hbm_gbs"],
-            "frac_of_nominal_8TBs": gbs / 8000.0, "peak_kind": p["kind"]}
+            "frac_of_nominal_8TBs": gbs / 8000.0, "peak_kind": p["kind"], "ms_copy_same_bytes": ms_copy}
 
 
 def bench_decode(dev, iters, shape, chunk_tokens=0):

@@ -181,3 +181,59 @@ def test_static_scratch_size_check_needs_no_gpu():
     lens = _fake_desc((4096,), 4)
     rc = fn(r(q), r(k), r(k), None, None, r(t), r(lens), None, r(q), _lib.SFB_BF16, _lib.SFB_BF16, ctypes.c_float(0.0), ctypes.c_int64(16), None)
     assert rc == _lib.SFB_ERR_WORKSPACE and b"built-in array" in lib.sfb_last_error()
+
+
+def test_gather_signal_and_norm_matmul_validate_arguments():
+    """The newer entry points reject bad calls before touching the device."""
+    lib = _lib.load()
+    r = ctypes.byref
+    q = _fake_desc((2, 8, 128), 2)
+    k = _fake_desc((4, 16, 2, 128), 2)
+    t = _fake_desc((2, 2), 4)
+    lens = _fake_desc((2,), 4)
+    out_all = _fake_desc((2, 16, 128), 2)
+    two = (ctypes.c_void_p * 2)(0x2000, 0x3000)
+    # world outside 1..8, rank outside the world, missing peer table, misaligned peer
+    common = (r(q), r(k), r(k), None, None, r(t), r(lens), None, r(out_all))
+    tail = (_lib.SFB_BF16, _lib.SFB_BF16, 0.0, 16, None, 0, None)
+    assert lib.sfb_paged_attention_decode_gather(*common, two, 9, 0, *tail) == _lib.SFB_ERR_INVALID_ARG
+    assert lib.sfb_paged_attention_decode_gather(*common, two, 2, 2, *tail) == _lib.SFB_ERR_INVALID_ARG
+    assert lib.sfb_paged_attention_decode_gather(*common, None, 2, 0, *tail) == _lib.SFB_ERR_INVALID_ARG
+    odd = (ctypes.c_void_p * 2)(0x2000, 0x3004)
+    assert lib.sfb_paged_attention_decode_gather(*common, odd, 2, 0, *tail) == _lib.SFB_ERR_INVALID_ARG
+    # the whole output must have world * H heads
+    small = _fake_desc((2, 8, 128), 2)
+    assert lib.sfb_paged_attention_decode_gather(r(q), r(k), r(k), None, None, r(t), r(lens), None, r(small), two, 2, 0, *tail) == _lib.SFB_ERR_INVALID_ARG
+    assert b"out must be" in lib.sfb_last_error()
+    assert lib.sfb_peer_signal_wait(two, 0, 0, 1, 3, None, None) == _lib.SFB_ERR_INVALID_ARG
+    assert lib.sfb_peer_signal_wait(two, 2, 0, 1, 4, None, None) == _lib.SFB_ERR_INVALID_ARG
+    assert lib.sfb_peer_signal_wait(None, 2, 0, 1, 3, None, None) == _lib.SFB_ERR_INVALID_ARG
+
+    x = _fake_desc((64, 256), 2)
+    w = _fake_desc((256, 512), 2)
+    y = _fake_desc((64, 512), 2)
+    g = _fake_desc((256,), 2)
+    assert lib.sfb_fused_rms_norm_matmul(r(x), r(w), r(y), _lib.SFB_F32, 1e-5, None, 0, None) == _lib.SFB_ERR_UNSUPPORTED
+    assert lib.sfb_fused_rms_norm_matmul(r(x), r(_fake_desc((128, 512), 2)), r(y), _lib.SFB_BF16, 1e-5, None, 0, None) == _lib.SFB_ERR_INVALID_ARG
+    assert lib.sfb_fused_rms_norm_matmul(r(x), r(_fake_desc((256, 516), 2)), r(_fake_desc((64, 516), 2)), _lib.SFB_BF16, 1e-5, None, 0, None) == _lib.SFB_ERR_UNSUPPORTED
+    assert lib.sfb_fold_norm_weight(r(_fake_desc((255,), 2)), r(w), r(w), _lib.SFB_BF16, None) == _lib.SFB_ERR_INVALID_ARG
+    assert lib.sfb_fold_norm_weight(r(g), r(w), r(w), _lib.SFB_F32, None) == _lib.SFB_ERR_UNSUPPORTED
+    assert lib.sfb_fused_rms_norm_matmul_workspace_bytes(1000) == 256 + 4096
+    assert lib.sfb_fused_rms_norm_matmul_workspace_bytes(-1) == _lib.SFB_ERR_INVALID_ARG
+
+
+def test_block_manager_rejects_bad_handles_and_arguments():
+    lib = _lib.load()
+    assert not lib.sfb_bm_create(0, 16) and not lib.sfb_bm_create(16, 0)
+    bm = lib.sfb_bm_create(8, 4)
+    try:
+        assert lib.sfb_bm_allocate(bm, b"a", -1, None, 0) == _lib.SFB_ERR_INVALID_ARG
+        assert lib.sfb_bm_allocate(bm, b"a", 100, None, 0) == _lib.SFB_ERR_OUT_OF_BLOCKS
+        assert lib.sfb_bm_get_blocks(bm, b"nobody", None, 0) == _lib.SFB_ERR_INVALID_ARG
+        assert lib.sfb_bm_row(bm, b"nobody") == -1
+        assert lib.sfb_bm_sync(bm, None) == _lib.SFB_ERR_INVALID_ARG  # no device tables attached
+        assert lib.sfb_bm_attach_device_tables(bm, None, 4, 4) == _lib.SFB_ERR_INVALID_ARG
+        assert lib.sfb_bm_ref_count(bm, 99) == -1
+        assert lib.sfb_bm_allocate(bm, b"a", 6, None, 0) == 2 and lib.sfb_bm_num_free_blocks(bm) == 6
+    finally:
+        lib.sfb_bm_destroy(bm)
