@@ -68,6 +68,9 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--partition", choices=["request", "head"], default="request",
                    help="request: every GPU serves its own requests (weak scaling, default); head: the configuration's "
                         "requests on every GPU with 1/N of the kv heads each (strong scaling, the 8-GPU layout of config 5)")
+    p.add_argument("--kernel", choices=["decode", "append", "norm", "prefill", "norm_matmul"], default="decode",
+                   help="decode (default): the headline step.  The others print one line for that kernel of the path alone "
+                        "(device time against its roofline, the oracle port timed on the host cores beside it); 1 GPU")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--cpu-sample", type=int, default=48, help="requests in the CPU-baseline sample")
     return p.parse_args()
@@ -344,6 +347,71 @@ def run_reference(args: argparse.Namespace, rank: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def _best_of(fn, repeats: int = 3) -> float:
+    """Seconds of the fastest of `repeats` calls after one warm-up call."""
+    fn()
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        fn()
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def run_kernel_line(args: argparse.Namespace) -> None:
+    """One JSON line for a single kernel of the path (not the headline step): device time from the kernel benchmark of
+    the package, the reference's CPU algorithm (oracle port) on a bounded sample of the same workload beside it."""
+    from llm_compileforge_b200 import kernel_bench as kb
+    from oracle import reference_port as ref
+
+    dev = torch.device("cuda", 0)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    iters = max(args.steps, 3)
+    if args.kernel == "append":
+        r = kb.bench_append(dev, iters)
+        n_tok, hkv, d = 262144, 8, 128
+        g = torch.Generator().manual_seed(5)
+        pool = (torch.randn((n_tok // 16, 16, hkv, d), generator=g) * 2).to(torch.bfloat16)
+        sec = _best_of(lambda: ref.fp8_quantize_pool_fast(pool))
+        cpu_bytes = wl.append_algorithmic_bytes(n_tok, hkv, d, 2) / 2  # one of K / V
+        metric, unit, value, bound = "fp8_quantize_on_append_GBps", "GB/s", r["achieved_gbs"], "hbm"
+        cpu = {"value": cpu_bytes / sec / 1e9, "unit": unit, "cores": cores, "kind": "port",
+               "sample": f"{n_tok} tokens of one of K/V (Hkv 8, D 128) through the per-(block, head) quantiser, best of 3, {sec:.3f} s"}
+        roof = {"bound": bound, "achieved": value, "peak": r["peak_gbs"], "unit": unit, "frac": r["frac"], "traffic": None}
+    elif args.kernel == "norm":
+        r = kb.bench_norm(dev, iters, 16384)
+        x, w, eps = wl.make_rms_norm_inputs(rows=16384, hidden=4096)
+        sec = _best_of(lambda: ref.rms_norm_hal(x, w, eps))
+        metric, unit, value, bound = "rms_norm_GBps", "GB/s", r["achieved_gbs"], "hbm"
+        cpu = {"value": wl.rms_norm_algorithmic_bytes(16384, 4096, 2) / sec / 1e9, "unit": unit, "cores": cores, "kind": "port",
+               "sample": f"the same [16384, 4096] bf16 rows, best of 3, {sec:.3f} s"}
+        roof = {"bound": bound, "achieved": value, "peak": r["peak_gbs"], "unit": unit, "frac": r["frac"], "traffic": None}
+    elif args.kernel == "prefill":
+        r = kb.bench_prefill(dev, iters)
+        pw = wl.make_prefill_workload(n_requests=1)
+        rid = next(iter(pw.block_tables))
+        sec = _best_of(lambda: ref.chunked_prefill(pw.q, pw.k_cache, pw.v_cache, pw.block_tables[rid], pw.ctx_lens[rid], scale=pw.scale))
+        metric, unit, value, bound = "chunked_prefill_TFLOPs", "TFLOP/s", r["achieved_tflops"], "tensor"
+        cpu = {"value": wl.prefill_flops(1, pw.n_heads, pw.head_dim, pw.chunk_len, pw.prefix_len) / sec / 1e12, "unit": unit, "cores": cores,
+               "kind": "port", "sample": f"one of the 32 requests (2048-token prefix + 512-token chunk), best of 3, {sec:.3f} s"}
+        roof = {"bound": bound, "achieved": value, "peak": r["peak_tflops"], "unit": unit, "frac": r["frac"], "traffic": None}
+    else:
+        r = kb.bench_norm_matmul(dev, iters)
+        x, g, w, eps = wl.make_norm_matmul_inputs(2048, 4096, 6144)
+        sec = _best_of(lambda: ref.fused_rms_norm_matmul(x, g, w, eps))
+        metric, unit, value, bound = "fused_rms_norm_matmul_TFLOPs", "TFLOP/s", r["achieved_tflops"], "tensor"
+        cpu = {"value": 2.0 * 2048 * 4096 * 6144 / sec / 1e12, "unit": unit, "cores": cores, "kind": "port",
+               "sample": f"2048 of the 16384 rows against the same [4096, 6144] weight, best of 3, {sec:.3f} s"}
+        roof = {"bound": bound, "achieved": value, "peak": r["peak_tflops"], "unit": unit, "frac": r["frac"], "traffic": None}
+    roof["peak_kind"] = f"of {r['peak_kind']}"
+    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": iters, "warmup": 3, "ms_per_step": r["ms"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic",
+            "config": {"workload": r["workload"], "kernel": r["kernel"]}, "roofline": roof, "cpu_baseline": cpu,
+            "device_status": r.get("status", 0)}
+    print(json.dumps(line), flush=True)
+
+
 def workload_config(shape: wl.DecodeShape, batch: int, args: argparse.Namespace, chunk: int) -> dict:
     return {
         "workload": f"{shape.name} paged decode, {batch} requests per GPU, H {shape.n_heads}/{shape.n_kv_heads}, "
@@ -361,6 +429,12 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.kernel != "decode":
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py --kernel needs a CUDA device")
+        if rank == 0:
+            run_kernel_line(args)
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
