@@ -56,7 +56,11 @@ def test_kernel_matches_reference_fixture(name):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("m,k,n", [(1, 64, 8), (128, 64, 256), (129, 72, 264), (300, 4096, 1024), (1000, 520, 776), (2048, 1024, 2304)])
+@pytest.mark.parametrize("m,k,n", [(1, 64, 8), (128, 64, 256), (129, 72, 264), (300, 4096, 1024), (1000, 520, 776), (2048, 1024, 2304),
+                                   # 256-wide tiles, several tiles per persistent thread block: statistics pre-pass ...
+                                   (4096, 512, 2560),
+                                   # ... and statistics inside the kernel (fewer than 2048 rows, but more tiles than SMs)
+                                   (1920, 320, 2568)])
 def test_kernel_matches_oracle_ragged(m, k, n):
     """Ragged M / N / K (rows past M, columns past N and a partial last K step are zero-filled by TMA and never stored),
     several K rounds of the four-stage ring, strided input rows; status word stays clean."""
@@ -80,6 +84,22 @@ def test_kernel_matches_oracle_ragged(m, k, n):
     # linearity in the weight: doubling W doubles y exactly (a power of two commutes with every rounding)
     got2 = ops.fused_rms_norm_matmul(xs, ops.fold_norm_weight(rw.to(dev), (w * 2).to(dev)), eps=eps)
     assert torch.equal(got2, got * 2)
+
+
+@pytest.mark.gpu
+def test_fp16_and_empty_shapes():
+    from llm_compileforge_b200 import ops
+
+    dev = torch.device("cuda:0")
+    x, rw, w, eps = wl.make_norm_matmul_inputs(333, 1032, 520, torch.float16, seed=9)
+    got = ops.fused_rms_norm_matmul(x.to(dev), ops.fold_norm_weight(rw.to(dev), w.to(dev)), eps=eps)
+    want = ref.fused_rms_norm_matmul(x, rw, w, eps)
+    assert got.dtype == torch.float16
+    assert_half_close(got.cpu(), want, what="fp16 333x1032x520")
+    empty = ops.fused_rms_norm_matmul(x.to(dev)[:0], ops.fold_norm_weight(rw.to(dev), w.to(dev)), eps=eps)
+    assert tuple(empty.shape) == (0, 520)
+    batched = ops.fused_rms_norm_matmul(x.to(dev)[:330].view(3, 110, 1032), ops.fold_norm_weight(rw.to(dev), w.to(dev)), eps=eps)
+    assert tuple(batched.shape) == (3, 110, 520) and torch.equal(batched.view(330, 520), got[:330])
 
 
 @pytest.mark.gpu
