@@ -354,6 +354,19 @@ SFB_API int64_t sfb_bm_get_blocks(const SFBBlockManager* bm, const char* request
 SFB_API int64_t sfb_bm_row(const SFBBlockManager* bm, const char* request_id);
 SFB_API int64_t sfb_bm_sync(SFBBlockManager* bm, void* stream);
 
+/* ── Chunked prefill over an e4m3 pool ────────────────────────────────────────
+ * sfb_prefill_paged for a pool of FP8 codes with per-(block, kv head) scales (the layout
+ * sfb_cache_write produces).  The blocks the batch attends to are expanded once into a
+ * 16-bit scratch pool inside `workspace` (value = code * scale in q's type) and the
+ * ordinary prefill runs over it; workspace size from sfb_prefill_fp8_workspace_bytes
+ * (max_blocks = columns of block_tables).  Status word as for sfb_prefill_paged. */
+SFB_API int64_t sfb_prefill_fp8_workspace_bytes(int64_t total_q_tokens, int64_t n_requests, int64_t max_blocks, int64_t n_kv_heads,
+                                                int64_t head_dim);
+SFB_API int sfb_prefill_paged_fp8(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache, const SFBTensor* k_scale,
+                                  const SFBTensor* v_scale, const SFBTensor* block_tables, const SFBTensor* cu_q,
+                                  const SFBTensor* ctx_lens, SFBTensor* out, int q_dtype, float scale, int causal,
+                                  int64_t max_q_tokens, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* ── RMSNorm fused into the following matmul ───────────────────────────────────
  * Replaces fused_rms_norm_matmul (python_runtime/hal/pytorch_backend/_ops_norm.py:47-65):
  *   y = (x * rsqrt(mean(x^2, -1) + eps) * rms_weight) @ mat_weight,  x [M, K], mat_weight [K, N].

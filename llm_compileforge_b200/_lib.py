@@ -118,6 +118,10 @@ def load() -> ctypes.CDLL:
     lib.sfb_paged_attention_decode_gather.restype = c_int
     lib.sfb_paged_attention_decode_gather.argtypes = [_T] * 9 + [POINTER(c_void_p), c_int, c_int, c_int, c_int, c_float, c_int64,
                                                                 c_void_p, c_int64, c_void_p]
+    lib.sfb_prefill_fp8_workspace_bytes.restype = c_int64
+    lib.sfb_prefill_fp8_workspace_bytes.argtypes = [c_int64] * 5
+    lib.sfb_prefill_paged_fp8.restype = c_int
+    lib.sfb_prefill_paged_fp8.argtypes = [_T] * 9 + [c_int, c_float, c_int, c_int64, c_void_p, c_int64, c_void_p]
     lib.sfb_fold_norm_weight.restype = c_int
     lib.sfb_fold_norm_weight.argtypes = [_T, _T, _T, c_int, c_void_p]
     lib.sfb_fused_rms_norm_matmul.restype = c_int

@@ -96,15 +96,14 @@ class PagedKVCache:
 
     def prefill(self, layer: int, q: torch.Tensor, n_tokens: Sequence[int], ctx_lens: Sequence[int], scale: float | None = None) -> torch.Tensor:
         """Causal attention of each request's newest ``n_tokens[i]`` tokens (``q [T, H, D]`` packed) over its
-        ``ctx_lens[i]`` cached tokens; bf16 / fp16 pools (an FP8 pool has no prefill kernel)."""
-        if self.fp8:
-            raise ValueError("prefill over an e4m3 pool is not supported; attend the chunk before quantising, or keep a bf16 pool")
+        ``ctx_lens[i]`` cached tokens.  An e4m3 pool is expanded to 16 bits for the attended blocks first."""
         cu = torch.zeros(len(n_tokens) + 1, dtype=torch.int32)
         cu[1:] = torch.tensor(list(n_tokens), dtype=torch.int32).cumsum(0)
         ctx = torch.tensor(list(ctx_lens), dtype=torch.int32)
         k_cache, v_cache = self._layer(layer)
+        fp8kw = dict(k_scale=self.k_scale[:, layer], v_scale=self.v_scale[:, layer]) if self.fp8 else {}
         return ops.prefill_paged(q, k_cache, v_cache, self._dense, cu.to(self.device), ctx.to(self.device),
-                                 max_q_tokens=max(n_tokens), scale=scale)
+                                 max_q_tokens=max(n_tokens), scale=scale, **fp8kw)
 
     # ── read_paged (cache_manager.py:173-197), for debugging and parity checks only ─
     def read_dense(self, layer: int, rid: str, length: int) -> tuple[torch.Tensor, torch.Tensor]:

@@ -217,9 +217,9 @@ int64_t sfb_prefill_workspace_bytes(int64_t total_q_tokens) {
     return kWorkspaceHeader + ceil_div(total_q_tokens * 8, 256) * 256;
 }
 
-int sfb_prefill_paged(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache, const SFBTensor* block_tables,
-                      const SFBTensor* cu_q, const SFBTensor* ctx_lens, SFBTensor* out, int dtype, float scale,
-                      int causal, int64_t max_q_tokens, void* workspace, int64_t workspace_bytes, void* stream) {
+static int prefill_impl(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache, const SFBTensor* block_tables,
+                        const SFBTensor* cu_q, const SFBTensor* ctx_lens, SFBTensor* out, int dtype, float scale, int causal,
+                        int64_t max_q_tokens, void* workspace, int64_t workspace_bytes, void* stream, bool clear_status) {
     const int e = dtype_size(dtype);
     if (!e || dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "prefill: dtype %d", dtype);
     View vq, vk, vv, vt, vc, vl, vo;
@@ -243,7 +243,7 @@ int sfb_prefill_paged(const SFBTensor* q, const SFBTensor* k_cache, const SFBTen
     if (T == 0 || R == 0 || max_q_tokens <= 0) return SFB_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (workspace && workspace_bytes < kWorkspaceHeader) workspace = nullptr;
-    if (workspace) SFB_CUDA_CHECK(cudaMemsetAsync(workspace, 0, 4, st));
+    if (workspace && clear_status) SFB_CUDA_CHECK(cudaMemsetAsync(workspace, 0, 4, st));
     const float sc = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
 
     PrefillLaunch p{};
@@ -480,6 +480,79 @@ int sfb_fold_norm_weight(const SFBTensor* rms_weight, const SFBTensor* mat_weigh
         return fail(SFB_ERR_UNSUPPORTED, "fold_norm_weight: N a multiple of 8, rows contiguous and 16-byte aligned");
     if (K == 0 || N == 0) return SFB_OK;
     return launch_fold_norm_weight(vg.base, vw.base, vf.base, K, N, vw.stride[2], vf.stride[2], dtype, static_cast<cudaStream_t>(stream));
+}
+
+int sfb_prefill_paged(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache, const SFBTensor* block_tables,
+                      const SFBTensor* cu_q, const SFBTensor* ctx_lens, SFBTensor* out, int dtype, float scale,
+                      int causal, int64_t max_q_tokens, void* workspace, int64_t workspace_bytes, void* stream) {
+    return prefill_impl(q, k_cache, v_cache, block_tables, cu_q, ctx_lens, out, dtype, scale, causal, max_q_tokens, workspace, workspace_bytes,
+                        stream, true);
+}
+
+static SFBTensor device_tensor(void* base, int elem, int rank, const int64_t* sizes) {
+    SFBTensor t{};
+    t.device = SFB_DEVICE_CUDA; t.rank = rank; t.elem_size = elem;
+    int64_t stride = 1;
+    SFBMemRef4* m = &t.r4;  // the four layouts share their first fields; sizes / strides are written per rank below
+    m->allocated = m->aligned = base; m->offset = 0;
+    int64_t* sz = rank == 1 ? t.r1.sizes : rank == 2 ? t.r2.sizes : rank == 3 ? t.r3.sizes : t.r4.sizes;
+    int64_t* st = rank == 1 ? t.r1.strides : rank == 2 ? t.r2.strides : rank == 3 ? t.r3.strides : t.r4.strides;
+    for (int i = rank - 1; i >= 0; --i) { sz[i] = sizes[i]; st[i] = stride; stride *= sizes[i]; }
+    return t;
+}
+
+int64_t sfb_prefill_fp8_workspace_bytes(int64_t total_q_tokens, int64_t n_requests, int64_t max_blocks, int64_t n_kv_heads, int64_t head_dim) {
+    if (total_q_tokens < 0 || n_requests < 0 || max_blocks < 0 || n_kv_heads <= 0 || head_dim <= 0) return SFB_ERR_INVALID_ARG;
+    const int64_t slots = n_requests * max_blocks;
+    return sfb_prefill_workspace_bytes(total_q_tokens) + ceil_div(slots * 4, 256) * 256 + 2 * ceil_div(slots * 16 * n_kv_heads * head_dim * 2, 256) * 256;
+}
+
+int sfb_prefill_paged_fp8(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache, const SFBTensor* k_scale,
+                          const SFBTensor* v_scale, const SFBTensor* block_tables, const SFBTensor* cu_q, const SFBTensor* ctx_lens,
+                          SFBTensor* out, int q_dtype, float scale, int causal, int64_t max_q_tokens, void* workspace,
+                          int64_t workspace_bytes, void* stream) {
+    if (q_dtype != SFB_BF16 && q_dtype != SFB_F16) return fail(SFB_ERR_UNSUPPORTED, "prefill_fp8: bf16 or fp16 queries");
+    View vq, vk, vv, vks, vvs, vt, vl;
+    int rc;
+    if ((rc = make_view(q, "q", 3, 3, 2, &vq))) return rc;
+    if ((rc = make_view(k_cache, "k_cache", 4, 4, 1, &vk))) return rc;
+    if ((rc = make_view(v_cache, "v_cache", 4, 4, 1, &vv))) return rc;
+    if ((rc = make_view(k_scale, "k_scale", 2, 2, 4, &vks))) return rc;
+    if ((rc = make_view(v_scale, "v_scale", 2, 2, 4, &vvs))) return rc;
+    if ((rc = make_view(block_tables, "block_tables", 2, 2, 4, &vt))) return rc;
+    if ((rc = make_view(ctx_lens, "ctx_lens", 1, 1, 4, &vl))) return rc;
+    const int64_t T = vq.size[1], D = vq.size[3], R = vl.size[3];
+    const int64_t NB = vk.size[0], bs = vk.size[1], Hkv = vk.size[2], max_blocks = vt.size[3];
+    if (bs != 16 || vk.size[3] != D || D % 16) return fail(SFB_ERR_UNSUPPORTED, "prefill_fp8: block size 16, head_dim a multiple of 16 equal to q's");
+    for (int i = 0; i < 4; ++i)
+        if (vk.size[i] != vv.size[i] || (i < 3 && vk.stride[i] != vv.stride[i])) return fail(SFB_ERR_INVALID_ARG, "prefill_fp8: k_cache and v_cache layouts differ");
+    if (vk.stride[3] != 1 || !aligned16(vk, 0) || !aligned16(vv, 0)) return fail(SFB_ERR_UNSUPPORTED, "prefill_fp8: pool rows must be contiguous and 16-byte aligned");
+    if (vt.size[2] != R) return fail(SFB_ERR_INVALID_ARG, "prefill_fp8: block_tables rows != requests");
+    if (vks.size[2] != NB || vks.size[3] != Hkv || vvs.size[2] != NB || vvs.size[3] != Hkv || vks.stride[2] != vvs.stride[2] || vks.stride[3] != vvs.stride[3])
+        return fail(SFB_ERR_INVALID_ARG, "prefill_fp8: scales must be [NB, Hkv] with one layout for K and V");
+    if (vl.size[3] > 1 && vl.stride[3] != 1) return fail(SFB_ERR_INVALID_ARG, "prefill_fp8: ctx_lens must be contiguous");
+    if (T == 0 || R == 0 || max_q_tokens <= 0 || max_blocks == 0) return SFB_OK;
+    const int64_t need = sfb_prefill_fp8_workspace_bytes(T, R, max_blocks, Hkv, D);
+    if (!workspace || workspace_bytes < need)
+        return fail(SFB_ERR_WORKSPACE, "prefill_fp8: workspace of %lld B needed, %lld given", (long long)need, (long long)(workspace ? workspace_bytes : 0));
+    if (R * max_blocks > 0x7fffffffLL) return fail(SFB_ERR_UNSUPPORTED, "prefill_fp8: too many table entries");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    char* ws = static_cast<char*>(workspace);
+    const int64_t inner = sfb_prefill_workspace_bytes(T), slots = R * max_blocks;
+    int32_t* tables2 = reinterpret_cast<int32_t*>(ws + inner);
+    char* k_scratch = ws + inner + ceil_div(slots * 4, 256) * 256;
+    char* v_scratch = k_scratch + ceil_div(slots * 16 * Hkv * D * 2, 256) * 256;
+    SFB_CUDA_CHECK(cudaMemsetAsync(ws, 0, 4, st));
+    const int64_t ps[3] = {vk.stride[0], vk.stride[1], vk.stride[2]}, ss[2] = {vks.stride[2], vks.stride[3]};
+    if ((rc = launch_expand_fp8_blocks(vk.base, vv.base, reinterpret_cast<const float*>(vks.base), reinterpret_cast<const float*>(vvs.base), k_scratch,
+                                       v_scratch, reinterpret_cast<const int32_t*>(vt.base), vt.stride[2], reinterpret_cast<const int32_t*>(vl.base),
+                                       tables2, ps, ss, (int)R, (int)max_blocks, (int)Hkv, (int)D, NB, q_dtype,
+                                       reinterpret_cast<int*>(ws), st)))
+        return rc;
+    const int64_t pool_sizes[4] = {slots, 16, Hkv, D}, table_sizes[2] = {R, max_blocks};
+    SFBTensor kt = device_tensor(k_scratch, 2, 4, pool_sizes), vt2 = device_tensor(v_scratch, 2, 4, pool_sizes);
+    SFBTensor tt = device_tensor(tables2, 4, 2, table_sizes);
+    return prefill_impl(q, &kt, &vt2, &tt, cu_q, ctx_lens, out, q_dtype, scale, causal, max_q_tokens, ws, inner, stream, false);
 }
 
 int64_t sfb_fused_rms_norm_matmul_workspace_bytes(int64_t rows) {

@@ -279,6 +279,12 @@ struct NormArgs {
 };
 int launch_rms_norm(const NormArgs& a, cudaStream_t stream);
 
+// prefill_fp8.cu: e4m3 blocks of a batch's contexts -> compact 16-bit scratch pool with identity tables
+int launch_expand_fp8_blocks(const void* k_codes, const void* v_codes, const float* k_scale, const float* v_scale, void* k_scratch,
+                             void* v_scratch, const int32_t* tables, int64_t table_stride, const int32_t* ctx_lens, int32_t* tables_out,
+                             const int64_t* pool_stride, const int64_t* scale_stride, int n_requests, int max_blocks, int n_kv_heads,
+                             int head_dim, int64_t n_pool_blocks, int dtype, int* status, cudaStream_t stream);
+
 // norm_matmul_tcgen05.cu: Wg = diag(g) W, and y = rstd(x) * (x @ Wg) on the tensor cores (strides in elements)
 int launch_fold_norm_weight(const void* g, const void* w, void* out, int64_t K, int64_t N, int64_t w_stride, int64_t out_stride,
                             int dtype, cudaStream_t stream);

@@ -113,12 +113,14 @@ def chunked_prefill(
     n_tokens: Mapping[str, int],
     block_size: int = 16,
     scale: float | None = None,
+    k_scale: torch.Tensor | None = None,
+    v_scale: torch.Tensor | None = None,
 ) -> dict[str, torch.Tensor]:
     """Causal attention of each request's newest ``n_tokens[rid]`` tokens over all
     of its ``ctx_lens[rid]`` cached tokens (prefix + chunk), K/V through the block
     tables.  ``q [T,H,D]`` packs the chunks in dict order (the scheduler's
     ``ScheduledRequest.n_tokens`` / ``block_table``, runtime/src/engine/types.rs:85-94).
-    Returns ``{rid: [n_tokens, H, D]}``."""
+    ``k_scale`` / ``v_scale`` ``[NB,Hkv]``: the pool holds e4m3 codes.  Returns ``{rid: [n_tokens, H, D]}``."""
     if k_cache.shape[1] != block_size:
         raise ValueError(f"k_cache block dimension {k_cache.shape[1]} != block_size {block_size}")
     rids = list(block_tables)
@@ -134,7 +136,7 @@ def chunked_prefill(
         raise ValueError(f"q has {q.shape[0]} rows, the chunks add up to {int(cu[-1])}")
     dev = q.device
     out = ops.prefill_paged(q, k_cache, v_cache, dense.to(dev, non_blocking=True), cu.to(dev), ll.to(dev, non_blocking=True),
-                            max_q_tokens=max(counts), scale=scale, causal=True)
+                            max_q_tokens=max(counts), scale=scale, causal=True, k_scale=k_scale, v_scale=v_scale)
     return {r: out[int(cu[i]) : int(cu[i + 1])] for i, r in enumerate(rids)}
 
 

@@ -267,13 +267,29 @@ def prefill_paged(
     causal: bool = True,
     workspace: torch.Tensor | None = None,
     out: torch.Tensor | None = None,
+    k_scale: torch.Tensor | None = None,
+    v_scale: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """Attention of packed query chunks ``q [T,H,D]`` over prefix + chunk read from
     the paged pool.  Request ``r`` owns rows ``cu_q[r]:cu_q[r+1]``; its chunk ends
-    at cached position ``ctx_lens[r] - 1`` (the chunk's K/V are already in the pool)."""
+    at cached position ``ctx_lens[r] - 1`` (the chunk's K/V are already in the pool).
+    With ``k_scale`` / ``v_scale`` (float32 ``[NB,Hkv]``) the pool holds e4m3 codes; the attended blocks are expanded
+    into a 16-bit scratch inside the workspace first (:func:`prefill_fp8_workspace_bytes`)."""
     lib = _lib.load()
     if out is None:
         out = torch.empty_like(q)
+    if k_scale is not None:
+        kc, vc = _as_codes(k_cache), _as_codes(v_cache)
+        need = prefill_fp8_workspace_bytes(q.shape[0], block_tables.shape[0], block_tables.shape[1], kc.shape[2], kc.shape[3])
+        if workspace is None:
+            workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+        check(lib.sfb_prefill_paged_fp8(
+            desc(q, "q"), desc(kc, "k_cache"), desc(vc, "v_cache"), desc(k_scale, "k_scale"), desc(v_scale, "v_scale"),
+            desc(block_tables, "block_tables"), desc(cu_q, "cu_q"), desc(ctx_lens, "ctx_lens"), desc(out, "out"), dtype_code(q.dtype),
+            float(scale) if scale is not None else 0.0, 1 if causal else 0, int(max_q_tokens), workspace.data_ptr(),
+            workspace.numel() * workspace.element_size(), current_stream(q.device),
+        ))
+        return out
     need = prefill_workspace_bytes(q.shape[0])
     if workspace is None:
         workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
@@ -284,6 +300,10 @@ def prefill_paged(
         workspace.numel() * workspace.element_size(), current_stream(q.device),
     ))
     return out
+
+
+def prefill_fp8_workspace_bytes(total_q_tokens: int, n_requests: int, max_blocks: int, n_kv_heads: int, head_dim: int) -> int:
+    return int(_lib.load().sfb_prefill_fp8_workspace_bytes(int(total_q_tokens), int(n_requests), int(max_blocks), int(n_kv_heads), int(head_dim)))
 
 
 def paged_attention_decode_shared_prefix(

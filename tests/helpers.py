@@ -59,6 +59,16 @@ def assert_half_close(got: torch.Tensor, ref: torch.Tensor, what: str = ""):
     assert cd <= COS_DEFICIT, f"{what}: cosine deficit {cd:.3e} > {COS_DEFICIT}"
 
 
+def assert_half_close_ulp(got: torch.Tensor, ref: torch.Tensor, what: str = ""):
+    """HALF_ABS plus one bf16 unit in the last place of the reference value (2^-7 relative covers it): a result on a
+    rounding boundary may land on either neighbour, and from |y| >= 4 one bf16 step alone is 3.1e-2."""
+    g, w = got.double(), ref.double()
+    excess = ((g - w).abs() - 2.0 ** -7 * w.abs()).max().item()
+    assert excess <= HALF_ABS, f"{what}: |diff| exceeds {HALF_ABS} + 1 ulp by {excess - HALF_ABS:.3e}"
+    cd = cos_deficit(got, ref)
+    assert cd <= COS_DEFICIT, f"{what}: cosine deficit {cd:.3e} > {COS_DEFICIT}"
+
+
 def stack_outputs(out: dict, rids) -> torch.Tensor:
     return torch.stack([out[r] for r in rids])
 

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import llm_compileforge_b200 as pkg
-from helpers import assert_half_close, from_bits, golden, stack_outputs
+from helpers import assert_half_close_ulp, assert_half_close, from_bits, golden, stack_outputs
 from llm_compileforge_b200 import ops
 from llm_compileforge_b200 import workloads as wl
 from llm_compileforge_b200.tables import dense_block_tables
@@ -298,3 +298,37 @@ def test_append_division_is_exact_over_many_scales(cuda, dtype):
     assert torch.equal(kc.cpu(), want_c)
     want_c, want_s = ref.fp8_quantize_pool_fast(x.reshape(nb * bs, hkv, d).flip(0).reshape(nb, bs, hkv, d))
     assert torch.equal(vc.cpu(), want_c) and torch.equal(vs.cpu(), want_s)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_chunked_prefill_over_fp8_pool(cuda, dtype):
+    """Chunks that attend to an e4m3 pool (earlier chunks of the prompt are already quantised): against the oracle's
+    attention over the dequantised pool; three requests share a prefix, ragged chunk and context sizes, a strided
+    (layer-sliced) pool and scale layout; the tcgen05 route (D 128) and the decode route (D 64)."""
+    for d, h, hkv in ((128, 8, 2), (64, 4, 4)):
+        g = torch.Generator().manual_seed(31 + d)
+        nb, bs, layers = 40, 16, 2
+        shared = [3, 17, 9]
+        tables = {"a": shared + [1, 2, 30], "b": shared + [7, 8], "c": shared + [11]}
+        ctx = {"a": 90, "b": 70, "c": 50}
+        chunk = {"a": 40, "b": 70 - 48, "c": 1}
+        src_k = (torch.randn((nb, bs, hkv, d), generator=g) * 2).to(dtype)
+        src_v = (torch.randn((nb, bs, hkv, d), generator=g) * 2).to(dtype)
+        kc, ks = ref.fp8_quantize_pool_fast(src_k)
+        vc, vs = ref.fp8_quantize_pool_fast(src_v)
+        k_deq, v_deq = ref.fp8_dequantize_pool(kc, ks), ref.fp8_dequantize_pool(vc, vs)
+        # layer-sliced device layout: [NB, layers, bs, Hkv, D] codes and [NB, layers, Hkv] scales, layer 1 is ours
+        slab_k = torch.zeros((nb, layers, bs, hkv, d), dtype=torch.uint8, device=cuda)
+        slab_v = torch.zeros_like(slab_k)
+        sc_k = torch.ones((nb, layers, hkv), dtype=torch.float32, device=cuda)
+        sc_v = torch.ones_like(sc_k)
+        slab_k[:, 1], slab_v[:, 1] = kc.to(cuda), vc.to(cuda)
+        sc_k[:, 1], sc_v[:, 1] = ks.to(cuda), vs.to(cuda)
+        q = torch.randn((sum(chunk.values()), h, d), generator=g).to(dtype)
+        out = pkg.chunked_prefill(q.to(cuda), slab_k[:, 1], slab_v[:, 1], tables, ctx, chunk, k_scale=sc_k[:, 1], v_scale=sc_v[:, 1])
+        at = 0
+        for rid in tables:
+            n = chunk[rid]
+            want = ref.chunked_prefill(q[at : at + n].float(), k_deq, v_deq, tables[rid], ctx[rid])
+            assert_half_close_ulp(out[rid].cpu(), want.to(dtype), what=f"fp8 prefill {rid} D {d} {dtype}")
+            at += n

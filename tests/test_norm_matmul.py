@@ -14,15 +14,7 @@ from oracle import reference_port as ref
 CASES = {"bf16_a": torch.bfloat16, "bf16_b": torch.bfloat16, "f16_a": torch.float16}
 
 
-def assert_close_one_ulp(got: torch.Tensor, want: torch.Tensor, what: str) -> None:
-    """2e-2 absolute plus one bf16 unit in the last place of the reference value (2^-7 relative covers it): a result that
-    sits on a rounding boundary may land on either neighbour, and at |y| >= 4 one bf16 step is already 3.1e-2."""
-    from helpers import COS_DEFICIT, cos_deficit
-
-    g, w = got.double(), want.double()
-    excess = ((g - w).abs() - 2.0 ** -7 * w.abs()).max().item()
-    assert excess <= 2e-2, f"{what}: |diff| exceeds 2e-2 + 1 ulp by {excess - 2e-2:.3e}"
-    assert cos_deficit(got, want) <= COS_DEFICIT, what
+from helpers import assert_half_close_ulp as assert_close_one_ulp  # noqa: E402
 
 
 def _want(g, name, dtype):
