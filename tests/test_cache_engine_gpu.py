@@ -60,15 +60,23 @@ def test_serving_loop_matches_reference_protocol(cuda, fp8):
             for (r, n), k_new, v_new in zip(step_reqs, ks, vs):
                 cpu.write(layer, tables[r], k_new, v_new, length[r])
             cache.write(layer, torch.cat(ks).to(cuda), torch.cat(vs).to(cuda), [n for _, n in step_reqs], [length[r] for r in rids])
-            if not fp8:  # chunk attention over prefix + chunk, straight off the pool
-                q = torch.randn((sum(n for _, n in step_reqs), h, d), generator=g).to(torch.bfloat16)
-                out = cache.prefill(layer, q.to(cuda), [n for _, n in step_reqs], [length[r] + n for r, n in step_reqs]).cpu()
-                kp, vp = cpu.pools(layer)
-                at = 0
-                for r, n in step_reqs:
+            # chunk attention over prefix + chunk, straight off the pool (an FP8 pool: over the quantised earlier chunk too)
+            q = torch.randn((sum(n for _, n in step_reqs), h, d), generator=g).to(torch.bfloat16)
+            out = cache.prefill(layer, q.to(cuda), [n for _, n in step_reqs], [length[r] + n for r, n in step_reqs]).cpu()
+            kp, vp = cpu.pools(layer)
+            at = 0
+            for r, n in step_reqs:
+                if fp8:
+                    want = ref.chunked_prefill(q[at : at + n].float(), kp, vp, tables[r], length[r] + n).to(torch.bfloat16)
+                    # V (code * scale) and P are each rounded to bf16 before the tensor-core product and the result once
+                    # more: three roundings of 2^-9 on values as large as the context's largest V entry
+                    tol = 2e-2 + 3 * 2.0 ** -9 * vp.abs().max().item()
+                    err = (out[at : at + n].float() - want.float()).abs().max().item()
+                    assert err <= tol, f"prefill {r} layer {layer}: {err:.3e} > {tol:.3e}"
+                else:
                     want = ref.chunked_prefill(q[at : at + n], kp, vp, tables[r], length[r] + n)
                     assert_half_close(out[at : at + n], want, what=f"prefill {r} layer {layer}")
-                    at += n
+                at += n
         for r, n in step_reqs:
             length[r] += n
     assert length == prompt
