@@ -177,7 +177,14 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     using C = Cfg<KV, NSUB, HB, BPS, STAGES>;
     constexpr bool FP8 = C::kFp8, BF = C::kBf16;
     extern __shared__ uint8_t smem_raw[];
-    const int chunk = blockIdx.x, hg = blockIdx.y, req = blockIdx.z;
+    int chunk = blockIdx.x, req = blockIdx.z;
+    const int hg = blockIdx.y;
+    if (a.work) {  // work list: largest items first, so the last wave is made of the small ones
+        if ((int)blockIdx.x >= *a.n_work) return;
+        const uint32_t item = a.work[blockIdx.x];
+        req = (int)(item >> 16);
+        chunk = (int)(item & 0xffffu);
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = a.n_heads / a.n_kv_heads;
     const int n_chunks = (int)a.split.n_chunks;
@@ -626,6 +633,45 @@ bool make_pool_map(CUtensorMap* map, const void* base, const int64_t* stride_ele
     return r == CUDA_SUCCESS;
 }
 
+// Work list of a split decode: one item per (request, chunk) that has tokens, ordered by size - full chunks first, then
+// the partial last chunks from long to short (33 size classes, counting sort in one thread block).  Thread blocks are
+// dispatched in list order, so the wave that finishes the launch consists of the smallest items instead of whatever
+// request happens to come last; an item is (request << 16 | chunk).
+constexpr int kWorkClasses = 33;
+constexpr int64_t kWorkListMinItems = 600;  // fewer (request, chunk) slots than about two waves: plain grid order
+constexpr int64_t kWorkListMinBytes = 1ll << 30;  // ... or a pool too small for the extra launch (a few microseconds) to pay
+
+__global__ void __launch_bounds__(1024) decode_worklist_kernel(const int32_t* __restrict__ seq_lens, int batch, int max_tokens, int prefix_tokens,
+                                                               int chunk_tokens, uint32_t* __restrict__ work, int* __restrict__ n_work) {
+    __shared__ int count[kWorkClasses], cursor[kWorkClasses];
+    if (threadIdx.x < kWorkClasses) count[threadIdx.x] = 0;
+    __syncthreads();
+    auto size_class = [&](int tokens) { return tokens >= chunk_tokens ? 0 : 32 - (int)(((int64_t)tokens * 32 - 1) / chunk_tokens); };
+    auto request_len = [&](int r) {
+        int len = seq_lens[r];
+        if (len > max_tokens) len = max_tokens;
+        return len - prefix_tokens;
+    };
+    for (int r = threadIdx.x; r < batch; r += blockDim.x) {
+        const int len = request_len(r);
+        if (len <= 0) { atomicAdd(&count[32], 1); continue; }  // the kernel's chunk-0 block zero-fills and flags it
+        for (int c = 0; c * chunk_tokens < len; ++c) atomicAdd(&count[size_class(min(chunk_tokens, len - c * chunk_tokens))], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int i = 0; i < kWorkClasses; ++i) { cursor[i] = at; at += count[i]; }
+        *n_work = at;
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < batch; r += blockDim.x) {
+        const int len = request_len(r);
+        if (len <= 0) { work[atomicAdd(&cursor[32], 1)] = (uint32_t)r << 16; continue; }
+        for (int c = 0; c * chunk_tokens < len; ++c)
+            work[atomicAdd(&cursor[size_class(min(chunk_tokens, len - c * chunk_tokens))], 1)] = ((uint32_t)r << 16) | (uint32_t)c;
+    }
+}
+
 template <int KV, int NSUB, int HB, int BPS, bool QBF16>
 int launch_cfg(const DecodeArgs& a, cudaStream_t stream) {
     constexpr int STAGES = (HB * BPS * NSUB >= 8) ? 3 : 4;
@@ -642,7 +688,20 @@ int launch_cfg(const DecodeArgs& a, cudaStream_t stream) {
         attr_set = true;
     }
     dim3 grid((unsigned)a.split.n_chunks, (unsigned)(a.n_kv_heads / HB), (unsigned)a.batch);
-    kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(kmap, vmap, a);
+    DecodeArgs args = a;
+    const int64_t slots = (int64_t)a.batch * a.split.n_chunks;
+    const int64_t bytes_bound = (int64_t)a.batch * a.max_blocks * 16 * a.n_kv_heads * a.head_dim * elem * 2;  // every table full
+    if (a.split.n_chunks > 1 && a.split.n_chunks <= 65536 && slots >= kWorkListMinItems && slots <= 0x7fffffffLL && bytes_bound >= kWorkListMinBytes &&
+        a.workspace) {
+        int* n_work = reinterpret_cast<int*>(a.workspace + a.split.work_offset);
+        uint32_t* work = reinterpret_cast<uint32_t*>(a.workspace + a.split.work_offset + 256);
+        decode_worklist_kernel<<<1, 1024, 0, stream>>>(a.seq_lens, a.batch, a.max_blocks * 16, a.prefix_tokens, (int)a.split.chunk_tokens, work, n_work);
+        SFB_CUDA_CHECK(cudaGetLastError());
+        args.work = work;
+        args.n_work = n_work;
+        grid = dim3((unsigned)slots, (unsigned)(a.n_kv_heads / HB), 1);
+    }
+    kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(kmap, vmap, args);
     SFB_CUDA_CHECK(cudaGetLastError());
     return SFB_OK;
 }

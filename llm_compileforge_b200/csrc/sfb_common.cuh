@@ -69,6 +69,7 @@ struct DecodeSplit {
     int64_t cnt_offset;
     int64_t ml_offset;
     int64_t o_offset;
+    int64_t work_offset;  // [0]: number of work items, [64..): (request << 16 | chunk) sorted largest first (split decode only)
     int64_t total_bytes;
 };
 
@@ -85,7 +86,8 @@ inline DecodeSplit decode_split(int64_t batch, int64_t n_heads, int64_t head_dim
     s.ml_offset = s.cnt_offset + ceil_div(batch * n_heads * 4, 256) * 256;  // n_heads >= kv-head groups
     int64_t ml_bytes = batch * s.n_chunks * n_heads * 2 * 4;
     s.o_offset = s.ml_offset + ceil_div(ml_bytes, 256) * 256;
-    s.total_bytes = s.o_offset + batch * s.n_chunks * n_heads * head_dim * 4;
+    s.work_offset = s.o_offset + ceil_div(batch * s.n_chunks * n_heads * head_dim * 4, 256) * 256;
+    s.total_bytes = s.work_offset + 256 + batch * s.n_chunks * 4;
     if (s.n_chunks == 1) s.total_bytes = kWorkspaceHeader;
     return s;
 }
@@ -156,6 +158,8 @@ struct DecodeArgs {
     const float* v_scale;
     const int32_t* tables;
     const int32_t* table_rows;  // optional: query row r uses table row table_rows[r] (prefill tokens share a row)
+    const uint32_t* work;       // split decode with many items: thread block x takes item work[x] = request << 16 | chunk ...
+    const int* n_work;          // ... of *n_work items, largest first; nullptr: blockIdx (x, z) = (chunk, request)
     void* peer_out[8];          // n_peers > 0: every output store goes to the same offset in each of these buffers
     int n_peers;                // (head-partitioned multi-GPU decode: each GPU writes its heads into every GPU's copy)
     int64_t n_table_rows;       // rows of `tables`; a table_rows entry outside [0, n) is flagged and row 0 is read
