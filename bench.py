@@ -461,6 +461,9 @@ def main() -> None:
     chunk = pick_chunk_tokens(st.lengths, args.chunk_tokens)
     ws_bytes = ops.decode_workspace_bytes(st.batch, shape.n_heads, shape.head_dim, st.tables.shape[1], shape.block_size, chunk)
     workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)
+    n_chunks = -(-st.tables.shape[1] * shape.block_size // chunk)
+    pool_bound = st.batch * st.tables.shape[1] * shape.block_size * shape.n_kv_heads * shape.head_dim * (1 if st.fp8 else 2) * 2
+    worklist = n_chunks > 1 and st.batch * n_chunks >= 600 and pool_bound >= (1 << 30)
     out = torch.empty_like(st.q)
     gathered = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device=dev) if (args.gather == "nccl" and world > 1) else None
     peer = None
@@ -594,8 +597,9 @@ def main() -> None:
                     "d2h_bytes_per_step": d2h, "steps_in_flight": 2,
                     "one_step_at_a_time": total_requests / (serial_ms / args.steps / 1e3),
                     "table_upload": "device-resident tables; only ids of added blocks are sent"},
-            # per step: cache_write_kernel + decode_tma_kernel (split merge is in-kernel) (+ the peer signal kernel)
-            "gpu_launches": args.steps * (3 if peer is not None else 2),
+            # per step: cache_write_kernel + decode_tma_kernel (split merge is in-kernel), + decode_worklist_kernel when the
+            # split has >= 600 (request, chunk) slots over a pool bound of >= 1 GiB (the launcher's rule), + the peer signal kernel
+            "gpu_launches": args.steps * (2 + int(worklist) + int(peer is not None)),
             "clocks": clocks.summary(),
             "device_status": status | (4 if (peer is not None and peer.timed_out()) else 0),
         }
