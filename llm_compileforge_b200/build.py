@@ -42,6 +42,13 @@ def _headers_mtime() -> float:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile and link.  ``SFB_NVCC_FLAGS`` adds compiler flags (e.g. ``-DSFB_PREFILL_TRACE`` for the prefill kernel's stage
+    stamps) and ``SFB_LIB_OUT`` writes such a variant to another path (objects beside it), leaving the regular library alone."""
+    global OBJ, LIB
+    extra = os.environ.get("SFB_NVCC_FLAGS", "").split()
+    if os.environ.get("SFB_LIB_OUT"):
+        LIB = os.path.abspath(os.environ["SFB_LIB_OUT"])
+        OBJ = LIB + "_obj"
     os.makedirs(OBJ, exist_ok=True)
     nvcc = _nvcc()
     sources = sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
@@ -51,7 +58,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         s = os.path.join(CSRC, src)
         o = os.path.join(OBJ, src[:-3] + ".o")
         if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr):
-            cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-c", s, "-o", o]
+            cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", INCLUDE, "-c", s, "-o", o]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)

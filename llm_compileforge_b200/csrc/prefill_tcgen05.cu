@@ -35,6 +35,20 @@
 
 #include "sfb_common.cuh"
 
+// Optional stage stamps (-DSFB_PREFILL_TRACE): thread block (0,0,0) records clock64 at its barrier waits - the first softmax
+// warp of each query tile (rows 0 / 1 of the table) and the MMA warp (row 2) - into a device array that
+// sfb_debug_prefill_trace copies out: per KV tile {wait begin, S ready, first pass done, maxima exchanged, second pass done,
+// P handed over}, and for the MMA warp {tile 0 before / after issue, tile 1 before / after issue}.
+#ifdef SFB_PREFILL_TRACE
+__device__ long long g_prefill_trace[3][64][6];
+extern "C" __attribute__((visibility("default"))) int sfb_debug_prefill_trace(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_prefill_trace, sizeof(g_prefill_trace));
+}
+#define SFB_TR(w, j, k) do { if (trace_on && (j) < 64) g_prefill_trace[w][j][k] = clock64(); } while (0)
+#else
+#define SFB_TR(w, j, k) do { } while (0)
+#endif
+
 namespace sfb {
 namespace {
 
@@ -244,6 +258,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         return;
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef SFB_PREFILL_TRACE
+    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 8 || warp == kMmaWarp);
+#endif
     const int q0 = qb * 2 * kTileQ;                       // first query row of the block
     int rows_t[2], tiles_t[2];
 #pragma unroll
@@ -368,8 +385,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                 if (ok && more) ok = mbar_wait(bar(B_K_FULL + (s ^ 1)), ((j + 1) >> 1) & 1);
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
+                    SFB_TR(2, j, 2 * t);
                     if (ok && j < tiles_t[t]) ok = issue_pv(t, j);
                     if (ok && j + 1 < tiles_t[t]) issue_qk(t, j + 1);
+                    SFB_TR(2, j, 2 * t + 1);
                 }
                 if (ok) {
                     tc_commit(bar(B_V_EMPTY + s));
@@ -403,8 +422,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
 
         auto softmax_tile = [&](int t, int j) -> bool {
             const uint32_t s_addr = lane_addr + t * kColTile + hf * 64;  // this thread's 64 score columns
+            SFB_TR(t, j, 0);
             if (!mbar_wait(bar(B_S_FULL + t), j & 1)) return false;
             tc_fence_after();
+            SFB_TR(t, j, 1);
             const int kv0 = j * kTileKV + hf * 64;
             // tcgen05.ld / st are warp-collective: the masked / unmasked choice must be uniform across the warp
             const bool full = __all_sync(0xffffffffu, kv0 + 63 <= pos);
@@ -430,9 +451,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                         if (kv0 + ch * 32 + i <= pos) mx0 = fmaxf(mx0, v[i]);
                 }
             }
+            SFB_TR(t, j, 2);
             float mx = fmaxf(mx0, mx1), other;
             if (!exchange(t, j & 1, mx, other)) return false;
             mx = fmaxf(mx, other);
+            SFB_TR(t, j, 3);
             const float m_new = fmaxf(m_used, mx * sl2);
             if (j == 0) {
                 m_used = m_new;
@@ -499,10 +522,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                 }
             }
             l += l0 + l1;
+            SFB_TR(t, j, 4);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_P_FULL + t));
+            SFB_TR(t, j, 5);
             return true;
         };
 
