@@ -101,7 +101,6 @@ class AttentionStepPipeline:
         s = self.slots[ticket % len(self.slots)]
         if s.busy:
             s.copied_out.synchronize()  # its result buffer is about to be reused
-        # host: grow the tables to cover the new token (runtime/src/engine/scheduler.rs:239-246), queue the delta
         key = tuple(request_ids)
         if key != self._rows_key:
             self._rows_key = key
@@ -109,9 +108,8 @@ class AttentionStepPipeline:
         s.meta_host[0, :n] = positions
         torch.add(positions, 1, out=s.meta_host[1, :n])
         s.meta_host[2, :n] = self._rows
-        self.bm.ensure_blocks_batch(request_ids, s.meta_host[1, :n])
-        self.table_entries_sent = self.bm.sync(self.compute)
-        # copy-in: the slot's staging buffers are free once the step that last used them has computed
+        # copy-in first (the slot's staging buffers are free once the step that last used them has computed), so that the
+        # host's table work below runs while the copies are already moving
         self.copy_in.wait_event(s.computed)
         with torch.cuda.stream(self.copy_in):
             s.q[:n].copy_(q, non_blocking=True)
@@ -119,6 +117,9 @@ class AttentionStepPipeline:
             s.v[:n].copy_(v_new, non_blocking=True)
             s.meta.copy_(s.meta_host, non_blocking=True)
             s.copied_in.record()
+        # host: grow the tables to cover the new token (runtime/src/engine/scheduler.rs:239-246), queue the delta
+        self.bm.ensure_blocks_batch(request_ids, s.meta_host[1, :n])
+        self.table_entries_sent = self.bm.sync(self.compute)
         self.compute.wait_event(s.copied_in)
         self.compute.wait_event(s.copied_out)  # the previous result has left s.out
         with torch.cuda.stream(self.compute):
