@@ -277,3 +277,50 @@ def _lib_ws(b, h, d, max_blocks, chunk, prefix_blocks):
     from llm_compileforge_b200 import _lib
 
     return int(_lib.load().sfb_shared_prefix_workspace_bytes(b, h, d, max_blocks, 16, chunk, prefix_blocks))
+
+
+def test_work_list_with_shared_prefix_and_ragged_lengths(cuda):
+    """A batch large enough for the size-ordered work list (>= 600 (request, chunk) slots over >= 1 GiB of addressable pool):
+    plain decode and the shared-prefix route both take their items from the list; lengths from 1 token to several chunks,
+    an empty request in the middle.  The oracle checks a sample; the two routes must agree everywhere."""
+    g = torch.Generator().manual_seed(77)
+    n_req, heads, kv_heads, d, prefix_blocks = 384, 32, 8, 128, 16
+    own = torch.randint(1, 1100, (n_req,), generator=g).tolist()
+    own[5], own[6] = 1, 1024
+    own_blocks = [-(-n // 16) for n in own]
+    nb = prefix_blocks + sum(own_blocks) + 7
+    perm = torch.randperm(nb, generator=g).tolist()
+    shared = perm[:prefix_blocks]
+    tables, lens, at = {}, {}, prefix_blocks
+    for i in range(n_req):
+        tables[f"r{i}"] = shared + perm[at : at + own_blocks[i]]
+        lens[f"r{i}"] = prefix_blocks * 16 + own[i]
+        at += own_blocks[i]
+    gen = torch.Generator(device=cuda).manual_seed(78)
+    q = torch.randn((n_req, heads, d), generator=gen, device=cuda).to(torch.bfloat16)
+    k = torch.randn((nb, 16, kv_heads, d), generator=gen, device=cuda).to(torch.bfloat16)
+    v = torch.randn((nb, 16, kv_heads, d), generator=gen, device=cuda).to(torch.bfloat16)
+    rids = list(tables)
+    dense, ll, _ = dense_block_tables(tables, lens, 16)
+    assert n_req * -(-dense.shape[1] * 16 // 256) >= 600 and n_req * dense.shape[1] * 16 * kv_heads * d * 2 * 2 >= 1 << 30
+    dt, dl = dense.to(cuda), ll.to(cuda)
+    ws = torch.zeros(ops.decode_workspace_bytes(n_req, heads, d, dense.shape[1], 16, 256), dtype=torch.uint8, device=cuda)
+    plain = ops.paged_attention_decode(q, k, v, dt, dl, chunk_tokens=256, workspace=ws)
+    assert ops.read_status(ws) == 0
+    ws2 = torch.zeros(_lib_ws(n_req, heads, d, dense.shape[1], 256, prefix_blocks), dtype=torch.uint8, device=cuda)
+    casc = ops.paged_attention_decode_shared_prefix(q, k, v, dt, dl, prefix_blocks, chunk_tokens=256, workspace=ws2)
+    assert ops.read_status(ws2) == 0
+    assert (casc.float() - plain.float()).abs().max().item() <= 2e-2
+    pick = [5, 6, 17, 200, 383]
+    kc, vc = k.cpu(), v.cpu()
+    want = ref.paged_attention_f64(q.cpu()[pick], kc, vc, {rids[i]: tables[rids[i]] for i in pick}, {rids[i]: lens[rids[i]] for i in pick})
+    for j, i in enumerate(pick):
+        assert_half_close(plain[i].cpu(), want[rids[i]], what=f"work list, request {i}")
+    # an empty request among the others: flagged, zero row, every other row unchanged
+    dl2 = dl.clone()
+    dl2[100] = 0
+    again = ops.paged_attention_decode(q, k, v, dt, dl2, chunk_tokens=256, workspace=ws)
+    assert ops.read_status(ws) & 2  # SFB_STATUS_EMPTY_REQUEST
+    assert float(again[100].float().abs().max()) == 0.0
+    keep = [i for i in range(n_req) if i != 100]
+    assert torch.equal(again[keep], plain[keep])
