@@ -93,6 +93,27 @@ def peaks() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
+def bind_to_gpu_cpus(index: int) -> str:
+    """Restrict this process to the CPUs that sit next to its GPU (read-only NVML query of the device's CPU affinity, then
+    this process's own scheduler affinity) before any pinned host buffer is allocated: first-touch then places the buffers
+    in that socket's memory and the host<->device copies stay off the socket interconnect.  Changes nothing on the GPU."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(ClockSampler._physical_index(index))
+        n_cpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (n_cpu + 63) // 64)
+        cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return f"{len(cpus)} CPUs next to GPU {index}"
+    except Exception as e:  # noqa: BLE001
+        return f"unbound ({type(e).__name__})"
+    return "unbound"
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons while the timed region runs
     (read-only NVML queries every few milliseconds; nvidia-smi as a fallback)."""
@@ -450,6 +471,7 @@ def main() -> None:
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    host_binding = bind_to_gpu_cpus(local_rank) if world > 1 else "single rank: not bound"
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     shape = shape_of(args.workload)
@@ -601,7 +623,7 @@ def main() -> None:
             "e2e": {"value": total_requests / (e2e_ms / args.steps / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps_in_flight": IN_FLIGHT,
                     "one_step_at_a_time": total_requests / (serial_ms / args.steps / 1e3),
-                    "table_upload": "device-resident tables; only ids of added blocks are sent"},
+                    "table_upload": "device-resident tables; only ids of added blocks are sent", "host_binding": host_binding},
             # per step: cache_write_kernel + decode_tma_kernel (split merge is in-kernel), + decode_worklist_kernel when the
             # split has >= 600 (request, chunk) slots over a pool bound of >= 1 GiB (the launcher's rule), + the peer signal kernel
             "gpu_launches": args.steps * (2 + int(worklist) + int(peer is not None)),
