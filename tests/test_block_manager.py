@@ -270,3 +270,26 @@ def test_table_row_out_of_range_is_flagged():
     ws = torch.zeros(ops.decode_workspace_bytes(2, 8, 128, 4), dtype=torch.uint8, device=dev)
     ops.paged_attention_decode(q, k, k, tables, lens, table_rows=torch.tensor([1, 9], dtype=torch.int32, device=dev), workspace=ws)
     assert ops.read_status(ws) & _lib.SFB_STATUS_BAD_BLOCK_ID
+
+
+@pytest.mark.parametrize("cls", IMPLS)
+def test_replay_of_the_reference_radix_cache_trace(cls):
+    """tests/golden/block_manager_trace.json: every call the reference's RadixCache and a small serving loop made on a block
+    manager (recorded by tests/golden/make_block_trace.py), with results; the C++ manager must answer each one the same."""
+    import json
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "block_manager_trace.json")
+    errors = {"OutOfMemory": OOM, "KeyError": (KeyError,), "ValueError": (ValueError,)}
+    for trace in json.load(open(path)):
+        bm = cls(trace["num_blocks"], trace["block_size"])
+        for i, call in enumerate(trace["calls"]):
+            fn = getattr(bm, call["op"])
+            if "raises" in call:
+                with pytest.raises(errors[call["raises"]]):
+                    fn(*call["args"])
+            else:
+                got = fn(*call["args"])
+                want = call["ok"]
+                assert (got == want) or (isinstance(want, float) and abs(got - want) < 1e-9), (i, call, got)
+            assert bm.num_free_blocks() == call["free"], (i, call)
