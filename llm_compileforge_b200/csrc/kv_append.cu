@@ -137,21 +137,36 @@ struct Divider {
         d.fast = s >= 0x1p-60f && s <= 0x1p60f;
         return d;
     }
-    __device__ __forceinline__ float quick(float x) const {
+    // the quotient without its sign repaired: +0 where the true quotient is -0 (x = -0.0, or a negative x that underflows)
+    __device__ __forceinline__ float quick_unsigned_zero(float x) const {
         const float q = __fmul_rn(x, rcp);
-        const float y = __fmaf_rn(__fmaf_rn(-q, scale, x), rcp, q);
-        return copysignf(y, x);  // scale > 0: the quotient has x's sign, also when it is zero (-0.0 encodes as 0x80)
+        return __fmaf_rn(__fmaf_rn(-q, scale, x), rcp, q);
+    }
+    __device__ __forceinline__ float quick(float x) const {
+        return copysignf(quick_unsigned_zero(x), x);  // scale > 0: the quotient has x's sign, also when it is zero (-0.0 encodes as 0x80)
     }
 };
 
-// N source values -> N codes packed little-endian into 32-bit words
+// N source values -> N codes packed little-endian into 32-bit words.  For 16-bit sources the sign of a zero quotient is
+// put back on the packed codes - the four source sign bytes gathered with one byte permute and OR-ed in (a no-op for
+// non-zero quotients, whose codes already carry it) - instead of one copysign per value.
 template <int N>
-__device__ __forceinline__ void encode_quick(const float* x, const Divider& div, uint32_t* words) {
+__device__ __forceinline__ void encode_quick(const float* x, const uint4& raw, const Divider& div, uint32_t* words) {
+    if constexpr (N == 8) {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int i = 0; i < N / 4; ++i) {
-        uint16_t lo = float2_to_e4m3x2(div.quick(x[4 * i]), div.quick(x[4 * i + 1]));
-        uint16_t hi = float2_to_e4m3x2(div.quick(x[4 * i + 2]), div.quick(x[4 * i + 3]));
-        words[i] = (uint32_t)lo | ((uint32_t)hi << 16);
+        for (int i = 0; i < 2; ++i) {
+            uint16_t lo = float2_to_e4m3x2(div.quick_unsigned_zero(x[4 * i]), div.quick_unsigned_zero(x[4 * i + 1]));
+            uint16_t hi = float2_to_e4m3x2(div.quick_unsigned_zero(x[4 * i + 2]), div.quick_unsigned_zero(x[4 * i + 3]));
+            words[i] = ((uint32_t)lo | ((uint32_t)hi << 16)) | (__byte_perm(w[2 * i], w[2 * i + 1], 0x7531) & 0x80808080u);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < N / 4; ++i) {
+            uint16_t lo = float2_to_e4m3x2(div.quick(x[4 * i]), div.quick(x[4 * i + 1]));
+            uint16_t hi = float2_to_e4m3x2(div.quick(x[4 * i + 2]), div.quick(x[4 * i + 3]));
+            words[i] = (uint32_t)lo | ((uint32_t)hi << 16);
+        }
     }
 }
 // the rare out-of-range scale: IEEE division instruction, kept out of line and register-to-register
@@ -271,24 +286,27 @@ __global__ void __launch_bounds__(kThreads) cache_write_kernel(AppendArgs a) {
                 // lane-constant parts of the destination addresses (row_of(j) = r0 + j*rpp when EVEN)
                 uint8_t* const dst_h = pool + h * ps[2];
                 ST* const tail_h = tail + h * ts[2];
+                auto emit = [&](int j, uint2 words) {
+                    uint8_t* dst = dst_h + row_of(j) * ps[1] + col_of(j);
+                    if constexpr (N == 8) *reinterpret_cast<uint2*>(dst) = words;
+                    else *reinterpret_cast<uint32_t*>(dst) = words.x;
+                    if (still_open) *reinterpret_cast<uint4*>(tail_h + row_of(j) * ts[1] + col_of(j)) = raw[j];
+                };
+                if (div.fast) {  // one branch per slice, not per chunk
 #pragma unroll
-                for (int j = 0; j < CPL; ++j) {
-                    if (row_of(j) < bs) {
-                        uint2 words;
-                        if (div.fast) {
+                    for (int j = 0; j < CPL; ++j) {
+                        if (row_of(j) < bs) {
                             float x[N];
                             Src<ST>::unpack(raw[j], x);
                             uint32_t w[N / 4];
-                            encode_quick<N>(x, div, w);
-                            words = make_uint2(w[0], N == 8 ? w[N / 4 - 1] : 0u);
-                        } else {
-                            words = encode_exact_chunk<ST>(raw[j], scale);
+                            encode_quick<N>(x, raw[j], div, w);
+                            emit(j, make_uint2(w[0], N == 8 ? w[N / 4 - 1] : 0u));
                         }
-                        uint8_t* dst = dst_h + row_of(j) * ps[1] + col_of(j);
-                        if constexpr (N == 8) *reinterpret_cast<uint2*>(dst) = words;
-                        else *reinterpret_cast<uint32_t*>(dst) = words.x;
-                        if (still_open) *reinterpret_cast<uint4*>(tail_h + row_of(j) * ts[1] + col_of(j)) = raw[j];
                     }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < CPL; ++j)  // unrolled: a run-time index would put the chunk registers on the stack
+                        if (row_of(j) < bs) emit(j, encode_exact_chunk<ST>(raw[j], scale));
                 }
             }
             if (!more) break;
