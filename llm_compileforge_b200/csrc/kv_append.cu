@@ -253,8 +253,15 @@ __global__ void __launch_bounds__(kThreads) cache_write_kernel(AppendArgs a) {
 
         // The warp walks its (block, head) slices with the next slice's rows already in flight
         // while the current one is reduced and encoded.
+        const bool full_lanes = n_chunks == 32 * CPL;  // every lane owns CPL chunks of a slice: no row check needed
         auto fetch = [&](int fb, int fh, uint4 (&raw)[CPL]) {
             const int lo = fb * bs;
+            if (full_lanes && lo >= start && lo + bs <= end) {  // a block that lies wholly inside the appended range: plain loads
+                const ST* base = src + (int64_t)(lo - start) * src_tok + fh * src_head;
+#pragma unroll
+                for (int j = 0; j < CPL; ++j) raw[j] = ldg_stream(base + (int64_t)row_of(j) * src_tok + col_of(j));
+                return;
+            }
 #pragma unroll
             for (int j = 0; j < CPL; ++j) {
                 raw[j] = make_uint4(0, 0, 0, 0);
@@ -293,16 +300,20 @@ __global__ void __launch_bounds__(kThreads) cache_write_kernel(AppendArgs a) {
                     if (still_open) *reinterpret_cast<uint4*>(tail_h + row_of(j) * ts[1] + col_of(j)) = raw[j];
                 };
                 if (div.fast) {  // one branch per slice, not per chunk
+                    auto fast_loop = [&](auto full_c) {
 #pragma unroll
-                    for (int j = 0; j < CPL; ++j) {
-                        if (row_of(j) < bs) {
-                            float x[N];
-                            Src<ST>::unpack(raw[j], x);
-                            uint32_t w[N / 4];
-                            encode_quick<N>(x, raw[j], div, w);
-                            emit(j, make_uint2(w[0], N == 8 ? w[N / 4 - 1] : 0u));
+                        for (int j = 0; j < CPL; ++j) {
+                            if (decltype(full_c)::value || row_of(j) < bs) {
+                                float x[N];
+                                Src<ST>::unpack(raw[j], x);
+                                uint32_t w[N / 4];
+                                encode_quick<N>(x, raw[j], div, w);
+                                emit(j, make_uint2(w[0], N == 8 ? w[N / 4 - 1] : 0u));
+                            }
                         }
-                    }
+                    };
+                    if (full_lanes) fast_loop(std::true_type{});
+                    else fast_loop(std::false_type{});
                 } else {
 #pragma unroll
                     for (int j = 0; j < CPL; ++j)  // unrolled: a run-time index would put the chunk registers on the stack
