@@ -1,6 +1,10 @@
 """Per-kernel measurements for the hot path's other kernels (one JSON line each).
 
-    python -m llm_compileforge_b200.kernel_bench [--only prefill,append,norm,decode_c2,decode_c3] [--iters 20]
+    python -m llm_compileforge_b200.kernel_bench [--iters 20] [--chunk-tokens 0] \
+        [--only prefill,norm_matmul,append,norm,decode_c2,decode_c3,shared_prefix]
+
+``--only prefill_trace`` prints the prefill kernel's per-stage time stamps; it needs a library built with
+``-DSFB_PREFILL_TRACE`` and is not part of the default list.
 
 ``bench.py`` at the repository root reports the headline decode metric; this
 module times the remaining kernels on their configurations with CUDA events
