@@ -12,8 +12,9 @@
 // the MMAs run, so the operator stays one launch; those shared-memory reads cost the MMAs about a tenth of their
 // operand bandwidth, so for many rows (prefill) a pre-pass (row_rstd_kernel, x read once) supplies rstd instead.
 //
-// Persistent thread blocks (one per SM) walk the 128 x 256 tiles of y; the accumulator is double-buffered in tensor
-// memory (2 x 256 columns), so tile i drains through the epilogue warps while tile i+1's MMAs run:
+// Persistent thread blocks (one per SM) walk the 128 x 256 tiles of y (128 x 128 or 128 x 64 for few rows, see the
+// launcher); the accumulator is double-buffered in tensor memory (2 x 256 columns), so tile i drains through the
+// epilogue warps while tile i+1's MMAs run:
 //   warp 4    TMA producer: per 64-wide K step a [128 rows x 128 B] box of x (K-major, 128B swizzle) and four
 //             [64 k x 128 B] boxes of Wg (N-major), four stages
 //   warp 5    issues tcgen05.mma.cta_group::1.kind::f16, M 128, N 256, K 16, four per stage, accumulator =
@@ -31,22 +32,26 @@
 
 #include <algorithm>
 #include <mutex>
+#include <type_traits>
 
 #include "sfb_common.cuh"
 
 namespace sfb {
 namespace {
 
-constexpr int kTileM = 128, kTileN = 256, kStepK = 64, kStages = 4;
+constexpr int kTileM = 128, kTileN = 256, kStepK = 64, kMaxStages = 6;
 constexpr int kABytes = kTileM * kStepK * 2;       // 16 KB
 constexpr int kBBlockBytes = kStepK * 128;         // one [64 k][64 n] block: 8 KB
 constexpr int kThreads = 192;
 constexpr uint32_t kSpin = 1u << 21;
 constexpr int64_t kPrepassRows = 2048;  // from this many rows on, row statistics come from a pre-pass instead of the A tiles
 
-enum { B_FULL = 0, B_EMPTY = kStages, B_ACC_FULL = 2 * kStages, B_ACC_EMPTY = 2 * kStages + 2, B_COUNT = 2 * kStages + 4 };
-constexpr int smem_bytes(int tn) { return kStages * (kABytes + (tn / 64) * kBBlockBytes) + B_COUNT * 8 + 16 + 1024; }
-constexpr int kNarrowN = 64;  // column width of the tiles used when 256-wide tiles would leave most SMs without one
+enum { B_FULL = 0, B_EMPTY = kMaxStages, B_ACC_FULL = 2 * kMaxStages, B_ACC_EMPTY = 2 * kMaxStages + 2, B_COUNT = 2 * kMaxStages + 4 };
+// Tile widths: 256 columns for large problems; 128 and 64 when 256-wide tiles would leave SMs without one (few rows).
+// Pipeline depth per width: 192 KB of operands in flight per SM - four 48 KB stages (256), six 32 KB stages (128),
+// or two resident thread blocks of four 24 KB stages each (64).
+constexpr int stages_for(int tn) { return tn == 128 ? 6 : 4; }
+constexpr int smem_bytes(int tn) { return stages_for(tn) * (kABytes + (tn / 64) * kBBlockBytes) + B_COUNT * 8 + 16 + 1024; }
 
 struct GemmArgs {
     void* out;
@@ -166,6 +171,7 @@ norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int kStage = kABytes + (TN / 64) * kBBlockBytes;  // bytes per pipeline stage
+    constexpr int kStages = stages_for(TN);
     const int n_k = (a.K + kStepK - 1) / kStepK;  // a ragged last step reads zeros (TMA fills what lies outside the matrices)
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -303,6 +309,201 @@ norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Two thread blocks on one 256 x 256 tile (a cluster of two, tcgen05 cta_group::2), for many rows.
+//
+// With one thread block per 128 x 256 tile every SM takes in 48 KB per K step (16 KB of x, 32 KB of the weight),
+// and that intake - about 110 GB/s per SM - is what bounds the kernel above, not the tensor pipe.  Here the two
+// thread blocks of a cluster share the weight tile: each loads its own 128 rows of x and HALF of the 256 weight
+// columns (32 KB per step and SM), and the leader's MMA (M 256) reads the B operand out of both blocks' shared
+// memory; each block's tensor memory receives its own 128 rows of the accumulator.
+//   leader and peer, warp 4: wait for the local "stage empty" barrier, TMA into local shared memory, transaction
+//                            bytes reported to the LEADER's "stage full" barrier (the cta_group::2 form of the load)
+//   leader, warp 5:          waits on "stage full" (64 KB), issues the MMAs, tcgen05.commit with a cluster mask
+//                            arrives on "stage empty" / "accumulator full" in both blocks
+//   both, warps 0-3:         drain their 128 accumulator rows; all eight warps arrive on the leader's
+//                            "accumulator empty" barrier
+// Row statistics always come from the pre-pass here (a peer has no "stage full" barrier of its own to read tiles by).
+// Waits are bounded as above; both blocks meet at a cluster barrier before tensor memory is released, so neither
+// leaves while the other can still touch its shared memory.
+constexpr int kPairStages = 6;
+constexpr int kPairStage = kABytes + 2 * kBBlockBytes;  // per thread block and stage: 32 KB
+constexpr int kPairTile = 256;
+constexpr int pair_smem_bytes() { return kPairStages * kPairStage + B_COUNT * 8 + 16 + 1024; }
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t leader_addr(uint32_t local) {  // the same shared-memory offset in the cluster's block 0
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(r) : "r"(local));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(cluster_bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {  // arrives on this barrier in both thread blocks
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3)
+                 : "memory");
+}
+__device__ __forceinline__ void mma_ss_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+template <bool BF16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+norm_matmul_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const GemmArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)cluster_rank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int n_k = (a.K + kStepK - 1) / kStepK;
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + kPairStages * kPairStage);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    auto a_stage = [&](int s) { return base + (uint32_t)s * kPairStage; };
+    auto b_stage = [&](int s) { return base + (uint32_t)s * kPairStage + kABytes; };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPairStages; ++s) {
+            mbar_init(bar(B_FULL + s), 1);   // used in the leader only: its producer's arrive + both blocks' bytes
+            mbar_init(bar(B_EMPTY + s), 1);  // the leader's commit, delivered to both blocks
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(B_ACC_FULL + i), 1);
+            mbar_init(bar(B_ACC_EMPTY + i), 8);  // used in the leader only: the epilogue warps of both blocks
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 5) tmem_alloc_pair(smem_u32(tmem_slot), 2 * kPairTile);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();  // the peer's barriers exist before anything is sent to them
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    bool timed_out = false;
+
+    if (warp == 4) {
+        // ===================== TMA producer (both thread blocks) ====================
+        if (lane == 0) {
+            int g = 0;
+            for (int tile = pair; tile < a.tiles_total && !timed_out; tile += n_pairs) {
+                const int m0 = (tile / a.tiles_n) * kPairTile + rank * kTileM;
+                const int n0 = (tile % a.tiles_n) * kPairTile + rank * (kPairTile / 2);
+                for (int kb = 0; kb < n_k; ++kb, ++g) {
+                    const int s = g % kPairStages;
+                    if (!mbar_wait(bar(B_EMPTY + s), ((g / kPairStages) & 1) ^ 1)) { timed_out = true; break; }
+                    if (rank == 0) mbar_expect_tx(bar(B_FULL + s), 2 * kPairStage);
+                    const uint32_t full = leader_addr(bar(B_FULL + s));
+                    tma_load_2d_pair(a_stage(s), &amap, full, kb * kStepK, m0);
+                    tma_load_2d_pair(b_stage(s), &bmap, full, n0, kb * kStepK);
+                    tma_load_2d_pair(b_stage(s) + kBBlockBytes, &bmap, full, n0 + 64, kb * kStepK);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ========================= MMA issuer (leader only) =========================
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = instr_desc(BF16, 2 * kTileM, kPairTile);
+            bool ok = true;
+            int g = 0, it = 0;
+            for (int tile = pair; tile < a.tiles_total && ok; tile += n_pairs, ++it) {
+                const int buf = it & 1;
+                ok = mbar_wait(bar(B_ACC_EMPTY + buf), ((it >> 1) & 1) ^ 1);  // both blocks have drained this accumulator
+                if (!ok) break;
+                tc_fence_after();
+                for (int kb = 0; kb < n_k && ok; ++kb, ++g) {
+                    const int s = g % kPairStages;
+                    ok = mbar_wait(bar(B_FULL + s), (g / kPairStages) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < kStepK / 16; ++ks)
+                        mma_ss_pair(tmem + buf * kPairTile, smem_desc(a_stage(s) + ks * 32, 16, 1024),
+                                    smem_desc(b_stage(s) + ks * 2048, kBBlockBytes, 1024), idesc, (kb > 0 || ks > 0));
+                    tc_commit_pair(bar(B_EMPTY + s));
+                }
+                if (ok) tc_commit_pair(bar(B_ACC_FULL + buf));
+            }
+            timed_out = !ok;
+        }
+    } else {
+        // ===================== epilogue (both thread blocks) ========================
+        const int row = threadIdx.x;
+        bool ok = true;
+        int it = 0;
+        for (int tile = pair; tile < a.tiles_total && ok; tile += n_pairs, ++it) {
+            const int m0 = (tile / a.tiles_n) * kPairTile + rank * kTileM, n0 = (tile % a.tiles_n) * kPairTile;
+            const int buf = it & 1;
+            ok = mbar_wait(bar(B_ACC_FULL + buf), (it >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const bool row_ok = m0 + row < a.M;
+            const float rstd = row_ok ? a.rstd[m0 + row] : 0.f;
+            const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16) + buf * kPairTile;
+            uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(m0 + row) * a.out_stride + n0;
+#pragma unroll 1
+            for (int ch = 0; ch < kPairTile / 32; ++ch) {
+                float v[32];
+                tmem_ld32(lane_base + ch * 32, v);
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (n0 + ch * 32 + i * 8 < a.N) {
+                            uint4 w;
+                            w.x = pack2<BF16>(v[8 * i] * rstd, v[8 * i + 1] * rstd);
+                            w.y = pack2<BF16>(v[8 * i + 2] * rstd, v[8 * i + 3] * rstd);
+                            w.z = pack2<BF16>(v[8 * i + 4] * rstd, v[8 * i + 5] * rstd);
+                            w.w = pack2<BF16>(v[8 * i + 6] * rstd, v[8 * i + 7] * rstd);
+                            *reinterpret_cast<uint4*>(dst + ch * 32 + i * 8) = w;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_addr(bar(B_ACC_EMPTY + buf)));
+        }
+        timed_out = !ok;
+    }
+    if (timed_out && a.status && lane == 0) atomicOr(a.status, SFB_STATUS_WAIT_TIMEOUT);
+    // ---- teardown: both thread blocks meet before tensor memory goes back
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem, 2 * kPairTile);
+    }
+}
+
 // One warp per row: rstd[m] = rsqrt(mean(x[m, :]^2) + eps), 16-byte loads.
 template <bool BF16>
 __global__ void row_rstd_kernel(const uint16_t* __restrict__ x, int64_t x_stride, int M, int K, float eps, float* __restrict__ rstd) {
@@ -398,30 +599,63 @@ int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t 
     int dev = 0, sms = 0;
     SFB_CUDA_CHECK(cudaGetDevice(&dev));
     SFB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    // Many rows: clusters of two thread blocks on 256 x 256 tiles, when there are enough tiles to occupy every cluster.
+    if (prepass) {
+        const int64_t ptiles_n = ceil_div(N, (int64_t)kPairTile), ptiles = ptiles_n * ceil_div(M, (int64_t)kPairTile);
+        auto launch_pair = [&](auto kernel) -> int {
+            constexpr int smem = pair_smem_bytes();
+            SFB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            cudaLaunchConfig_t cfg{};
+            cudaLaunchAttribute attr{};
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+            cfg.gridDim = dim3((unsigned)sms); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+            cfg.attrs = &attr; cfg.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); clusters = 0; }
+            clusters = std::min(clusters, sms / 2);
+            if (clusters < 1 || ptiles < clusters || ptiles > 0x7fffffffLL) return 1;  // not taken: the single-block kernel runs
+            GemmArgs p = a;
+            p.tiles_n = (int)ptiles_n;
+            p.tiles_total = (int)ptiles;
+            kernel<<<dim3(2u * (unsigned)clusters), kThreads, smem, stream>>>(amap, bmap, p);
+            SFB_CUDA_CHECK(cudaGetLastError());
+            return SFB_OK;
+        };
+        const int rc = bf16 ? launch_pair(norm_matmul_pair_kernel<true>) : launch_pair(norm_matmul_pair_kernel<false>);
+        if (rc != 1) return rc;
+    }
     const int64_t m_tiles = ceil_div(M, (int64_t)kTileM);
-    // few rows (decode): 256-wide tiles would give fewer thread blocks than SMs and each would stream its whole
-    // column block of the weight alone; 64-wide tiles spread the weight over four times as many blocks, two per SM
-    const bool narrow = m_tiles * ceil_div(N, (int64_t)kTileN) < sms;
-    const int tn = narrow ? kNarrowN : kTileN;
+    // Tile width.  With few rows the kernel is bound by what one SM can pull in (each tile streams its K panel of x and
+    // of the weight: kTileM + width bytes-per-k units), so take the width whose busiest SM pulls the least:
+    // rounds of tiles per SM x (kTileM + width).  Ties go to the wider tile (less traffic in total).
+    int tn = kTileN;
+    int64_t best = -1;
+    for (int w : {256, 128, 64}) {
+        const int64_t cost = ceil_div(m_tiles * ceil_div(N, (int64_t)w), (int64_t)sms) * (kTileM + w);
+        if (best < 0 || cost < best) { best = cost; tn = w; }
+    }
     const int64_t tiles_n = ceil_div(N, (int64_t)tn), tiles = tiles_n * m_tiles;
     if (tiles > 0x7fffffffLL) return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: too many tiles");
     a.tiles_n = (int)tiles_n;
     a.tiles_total = (int)tiles;
-    const dim3 grid((unsigned)std::min<int64_t>(tiles, narrow ? 2 * sms : sms));  // persistent thread blocks walk the tiles
+    // persistent thread blocks walk the tiles; the 64-wide kernel's shared memory lets two of them share an SM
+    const dim3 grid((unsigned)std::min<int64_t>(tiles, tn == 64 ? 2 * sms : sms));
     auto launch = [&](auto kernel, int smem) -> int {
         SFB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         kernel<<<grid, kThreads, smem, stream>>>(amap, bmap, a);
         SFB_CUDA_CHECK(cudaGetLastError());
         return SFB_OK;
     };
-    if (narrow) {
-        constexpr int sm = smem_bytes(kNarrowN);
-        if (bf16) return prepass ? launch(norm_matmul_tcgen05_kernel<true, false, kNarrowN>, sm) : launch(norm_matmul_tcgen05_kernel<true, true, kNarrowN>, sm);
-        return prepass ? launch(norm_matmul_tcgen05_kernel<false, false, kNarrowN>, sm) : launch(norm_matmul_tcgen05_kernel<false, true, kNarrowN>, sm);
-    }
-    constexpr int sm = smem_bytes(kTileN);
-    if (bf16) return prepass ? launch(norm_matmul_tcgen05_kernel<true, false, kTileN>, sm) : launch(norm_matmul_tcgen05_kernel<true, true, kTileN>, sm);
-    return prepass ? launch(norm_matmul_tcgen05_kernel<false, false, kTileN>, sm) : launch(norm_matmul_tcgen05_kernel<false, true, kTileN>, sm);
+    auto pick = [&](auto width) -> int {
+        constexpr int W = decltype(width)::value;
+        constexpr int sm = smem_bytes(W);
+        if (bf16) return prepass ? launch(norm_matmul_tcgen05_kernel<true, false, W>, sm) : launch(norm_matmul_tcgen05_kernel<true, true, W>, sm);
+        return prepass ? launch(norm_matmul_tcgen05_kernel<false, false, W>, sm) : launch(norm_matmul_tcgen05_kernel<false, true, W>, sm);
+    };
+    if (tn == 64) return pick(std::integral_constant<int, 64>{});
+    if (tn == 128) return pick(std::integral_constant<int, 128>{});
+    return pick(std::integral_constant<int, 256>{});
 }
 
 }  // namespace sfb

@@ -52,10 +52,15 @@ def test_kernel_matches_reference_fixture(name):
                                    # 256-wide tiles, several tiles per persistent thread block: statistics pre-pass ...
                                    (4096, 512, 2560),
                                    # ... and statistics inside the kernel (fewer than 2048 rows, but more tiles than SMs)
-                                   (1920, 320, 2568)])
+                                   (1920, 320, 2568),
+                                   # 128-wide tiles with the six-stage ring (few rows, wide output): whole and ragged
+                                   (256, 4096, 6144), (200, 1000, 9000),
+                                   # clusters of two thread blocks on 256 x 256 tiles (pre-pass statistics, enough tiles for every
+                                   # cluster): the last row block and the last column block are ragged in the second block's half
+                                   (2300, 1000, 2440)])
 def test_kernel_matches_oracle_ragged(m, k, n):
     """Ragged M / N / K (rows past M, columns past N and a partial last K step are zero-filled by TMA and never stored),
-    several K rounds of the four-stage ring, strided input rows; status word stays clean."""
+    several K rounds of the operand ring, strided input rows; status word stays clean."""
     from llm_compileforge_b200 import ops
 
     dev = torch.device("cuda:0")
