@@ -578,13 +578,63 @@ int launch_fold_norm_weight(const void* g, const void* w, void* out, int64_t K, 
     return SFB_OK;
 }
 
+namespace {
+
+// How many clusters of two the pair kernel can have resident on this device (0: cannot run); asked once per device.
+template <bool BF16>
+int pair_clusters(int dev, int sms) {
+    static std::mutex mu;
+    static int cached[64];
+    static bool known[64];
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && known[dev]) return cached[dev];
+    auto kernel = norm_matmul_pair_kernel<BF16>;
+    int clusters = 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes()) == cudaSuccess) {
+        cudaLaunchConfig_t cfg{};
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.gridDim = dim3((unsigned)(sms & ~1)); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = pair_smem_bytes();
+        cfg.attrs = &attr; cfg.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) clusters = 0;
+    }
+    cudaGetLastError();  // a refusal above only means "not available"
+    clusters = std::max(0, std::min(clusters, sms / 2));
+    if (dev >= 0 && dev < 64) { cached[dev] = clusters; known[dev] = true; }
+    return clusters;
+}
+
+}  // namespace
+
 int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t wg_stride, void* out, int64_t out_stride, int64_t M,
                        int64_t N, int64_t K, float eps, int dtype, int* status, float* rstd_scratch, cudaStream_t stream) {
     CUtensorMap amap, bmap;
     if (!encode_2d(&amap, x, M, K, x_stride, kTileM) || !encode_2d(&bmap, wg, K, N, wg_stride, kStepK))
         return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: tensor map encoding failed (16-byte aligned bases and row strides are required)");
     const bool bf16 = dtype == SFB_BF16;
-    const bool prepass = rstd_scratch != nullptr && M >= kPrepassRows;
+    int dev = 0, sms = 0;
+    SFB_CUDA_CHECK(cudaGetDevice(&dev));
+    SFB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+
+    // Shape of the work.  What bounds this kernel is what one SM can take in per K step (about 110 GB/s: a 128-row
+    // panel of x plus its share of the weight columns, kTileM + width rows of 128 bytes), so every candidate is
+    // priced as  rounds of tiles on the busiest SM x rows taken in per step,  and the cheapest runs:
+    //   one thread block per 128 x {256, 128, 64} tile  (ties go to the wider tile: less traffic in total), or
+    //   a cluster of two on a 256 x 256 tile, each block taking in 128 + 128 rows - needs the statistics pre-pass,
+    //   so only with a workspace for it, and only when strictly cheaper.
+    const int64_t m_tiles = ceil_div(M, (int64_t)kTileM);
+    int tn = kTileN;
+    int64_t best = -1;
+    for (int w : {256, 128, 64}) {
+        const int64_t cost = ceil_div(m_tiles * ceil_div(N, (int64_t)w), (int64_t)sms) * (kTileM + w);
+        if (best < 0 || cost < best) { best = cost; tn = w; }
+    }
+    const int64_t ptiles_n = ceil_div(N, (int64_t)kPairTile), ptiles = ptiles_n * ceil_div(M, (int64_t)kPairTile);
+    int clusters = 0;
+    if (rstd_scratch != nullptr && ptiles <= 0x7fffffffLL) clusters = bf16 ? pair_clusters<true>(dev, sms) : pair_clusters<false>(dev, sms);
+    const bool pair = clusters > 0 && ceil_div(ptiles, (int64_t)clusters) * (kTileM + kPairTile / 2) < best;
+    const bool prepass = rstd_scratch != nullptr && (pair || M >= kPrepassRows);
     if (prepass) {
         const unsigned blocks = (unsigned)ceil_div(M, (int64_t)8);
         if (bf16) row_rstd_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(x), x_stride, (int)M, (int)K, eps, rstd_scratch);
@@ -596,44 +646,14 @@ int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t 
     a.M = (int)M; a.N = (int)N; a.K = (int)K;
     a.eps = eps; a.status = status;
     a.rstd = prepass ? rstd_scratch : nullptr;
-    int dev = 0, sms = 0;
-    SFB_CUDA_CHECK(cudaGetDevice(&dev));
-    SFB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    // Many rows: clusters of two thread blocks on 256 x 256 tiles, when there are enough tiles to occupy every cluster.
-    if (prepass) {
-        const int64_t ptiles_n = ceil_div(N, (int64_t)kPairTile), ptiles = ptiles_n * ceil_div(M, (int64_t)kPairTile);
-        auto launch_pair = [&](auto kernel) -> int {
-            constexpr int smem = pair_smem_bytes();
-            SFB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            cudaLaunchConfig_t cfg{};
-            cudaLaunchAttribute attr{};
-            attr.id = cudaLaunchAttributeClusterDimension;
-            attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-            cfg.gridDim = dim3((unsigned)sms); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
-            cfg.attrs = &attr; cfg.numAttrs = 1;
-            int clusters = 0;
-            if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); clusters = 0; }
-            clusters = std::min(clusters, sms / 2);
-            if (clusters < 1 || ptiles < clusters || ptiles > 0x7fffffffLL) return 1;  // not taken: the single-block kernel runs
-            GemmArgs p = a;
-            p.tiles_n = (int)ptiles_n;
-            p.tiles_total = (int)ptiles;
-            kernel<<<dim3(2u * (unsigned)clusters), kThreads, smem, stream>>>(amap, bmap, p);
-            SFB_CUDA_CHECK(cudaGetLastError());
-            return SFB_OK;
-        };
-        const int rc = bf16 ? launch_pair(norm_matmul_pair_kernel<true>) : launch_pair(norm_matmul_pair_kernel<false>);
-        if (rc != 1) return rc;
-    }
-    const int64_t m_tiles = ceil_div(M, (int64_t)kTileM);
-    // Tile width.  With few rows the kernel is bound by what one SM can pull in (each tile streams its K panel of x and
-    // of the weight: kTileM + width bytes-per-k units), so take the width whose busiest SM pulls the least:
-    // rounds of tiles per SM x (kTileM + width).  Ties go to the wider tile (less traffic in total).
-    int tn = kTileN;
-    int64_t best = -1;
-    for (int w : {256, 128, 64}) {
-        const int64_t cost = ceil_div(m_tiles * ceil_div(N, (int64_t)w), (int64_t)sms) * (kTileM + w);
-        if (best < 0 || cost < best) { best = cost; tn = w; }
+    if (pair) {
+        a.tiles_n = (int)ptiles_n;
+        a.tiles_total = (int)ptiles;
+        const dim3 grid(2u * (unsigned)std::min<int64_t>(ptiles, clusters));
+        if (bf16) norm_matmul_pair_kernel<true><<<grid, kThreads, pair_smem_bytes(), stream>>>(amap, bmap, a);
+        else norm_matmul_pair_kernel<false><<<grid, kThreads, pair_smem_bytes(), stream>>>(amap, bmap, a);
+        SFB_CUDA_CHECK(cudaGetLastError());
+        return SFB_OK;
     }
     const int64_t tiles_n = ceil_div(N, (int64_t)tn), tiles = tiles_n * m_tiles;
     if (tiles > 0x7fffffffLL) return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: too many tiles");
