@@ -378,8 +378,10 @@ SFB_API int sfb_prefill_paged_fp8(const SFBTensor* q, const SFBTensor* k_cache, 
  * rows contiguous and 16-byte aligned.  `workspace` (device, may be NULL) of
  * sfb_fused_rms_norm_matmul_workspace_bytes(M) bytes: its first word is the status word
  * (sfb_read_status; SFB_STATUS_WAIT_TIMEOUT if a bounded wait inside the kernel ran out),
- * the rest holds per-row statistics when M is large enough for a statistics pre-pass to pay
- * (2048 rows up); without it the statistics are always taken inside the GEMM kernel. */
+ * the rest holds per-row statistics when the shape is large enough for a statistics pre-pass
+ * to pay (2048 rows up, or wherever a cluster of two thread blocks per 256 x 256 tile is the
+ * cheaper shape: that kernel needs the pre-pass); without it the statistics are always taken
+ * inside the single-block GEMM kernel. */
 SFB_API int64_t sfb_fused_rms_norm_matmul_workspace_bytes(int64_t rows);
 SFB_API int sfb_fold_norm_weight(const SFBTensor* rms_weight, const SFBTensor* mat_weight, SFBTensor* folded, int dtype, void* stream);
 SFB_API int sfb_fused_rms_norm_matmul(const SFBTensor* x, const SFBTensor* folded_weight, SFBTensor* out, int dtype, float eps,

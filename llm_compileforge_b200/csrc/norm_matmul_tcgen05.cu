@@ -12,21 +12,26 @@
 // the MMAs run, so the operator stays one launch; those shared-memory reads cost the MMAs about a tenth of their
 // operand bandwidth, so for many rows (prefill) a pre-pass (row_rstd_kernel, x read once) supplies rstd instead.
 //
-// Persistent thread blocks (one per SM) walk the 128 x 256 tiles of y (128 x 128 or 128 x 64 for few rows, see the
-// launcher); the accumulator is double-buffered in tensor memory (2 x 256 columns), so tile i drains through the
-// epilogue warps while tile i+1's MMAs run:
-//   warp 4    TMA producer: per 64-wide K step a [128 rows x 128 B] box of x (K-major, 128B swizzle) and four
-//             [64 k x 128 B] boxes of Wg (N-major), four stages
-//   warp 5    issues tcgen05.mma.cta_group::1.kind::f16, M 128, N 256, K 16, four per stage, accumulator =
-//             256 tensor-memory columns of fp32 (two of them, alternating); tcgen05.commit frees the stage /
-//             publishes the accumulator
+// Two kernels: one thread block per 128 x {256, 128, 64} tile (below), and a cluster of two thread blocks per
+// 256 x 256 tile (cta_group::2, further down) for shapes with enough tiles and a workspace for the pre-pass; the
+// launcher at the end of the file prices both by what an SM has to take in and runs the cheaper.
+//
+// Persistent thread blocks (one per SM) walk the tiles of y; the accumulator is double-buffered in tensor memory
+// (2 x 256 columns), so tile i drains through the epilogue warps while tile i+1's MMAs run:
+//   warp 4    TMA producer: per 64-wide K step a [128 rows x 128 B] box of x (K-major, 128B swizzle) and one
+//             [64 k x 128 B] box of Wg (N-major) per 64 columns of the tile; four or six stages
+//   warp 5    issues tcgen05.mma.cta_group::1.kind::f16, M 128, N = tile width, K 16, four per stage, accumulator =
+//             tensor-memory columns of fp32 (two sets, alternating); tcgen05.commit frees the stage / publishes the
+//             accumulator
 //   warps 0-3 one thread per output row: reads its row of every A stage from shared memory (16-byte chunks in
 //             a rotated order, so a quarter-warp never hits one bank twice; the swizzle only permutes chunks
 //             inside the row, the sum does not care), then tcgen05.ld the accumulator row, times rstd, 16-bit
 //             pack, 16-byte stores
 // Every wait is bounded; a stuck pipeline sets SFB_STATUS_WAIT_TIMEOUT in *status and the block leaves
 // through the common teardown, which releases tensor memory.
-// Bound: tensor pipe, 2*M*N*K flops; HBM traffic is x once per N tile (L2 keeps it) and Wg once per M tile.
+// Bound: 2*M*N*K flops on the tensor pipe once operands arrive fast enough - an SM takes in about 110 GB/s, which
+// is what holds the single-block kernel (48 KB per K step) below the pipe's rate and the few-row case far below it.
+// HBM traffic is x once per N tile (L2 keeps it) and Wg once per M tile.
 
 #include <cuda.h>
 

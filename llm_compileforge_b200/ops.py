@@ -356,7 +356,8 @@ def fused_rms_norm_matmul(x: torch.Tensor, folded_weight: torch.Tensor, eps: flo
     """``rms_norm(x) @ W`` with the norm's weight already folded into ``folded_weight`` (:func:`fold_norm_weight`):
     ``x [..., K]`` bf16 / fp16, result ``[..., N]``; one tcgen05 GEMM on the raw activations, the row factor applied to the
     accumulators.  ``workspace`` (uint8, :func:`norm_matmul_workspace_bytes`; allocated when missing) carries the status word
-    (:func:`read_status`) and, from 2048 rows up, the per-row statistics of a pre-pass."""
+    (:func:`read_status`) and the per-row statistics of a pre-pass, which large shapes use (from 2048 rows up, or whenever the
+    two-thread-block kernel is the cheaper shape)."""
     k = x.shape[-1]
     x2 = x.reshape(-1, k)
     n = folded_weight.shape[1]
