@@ -97,6 +97,18 @@ def test_fp16_and_empty_shapes():
     assert tuple(empty.shape) == (0, 520)
     batched = ops.fused_rms_norm_matmul(x.to(dev)[:330].view(3, 110, 1032), ops.fold_norm_weight(rw.to(dev), w.to(dev)), eps=eps)
     assert tuple(batched.shape) == (3, 110, 520) and torch.equal(batched.view(330, 520), got[:330])
+    # fp16 through the two-thread-block kernel (enough 256 x 256 tiles, workspace for the pre-pass); and the two kernels agree:
+    # without a workspace the same call runs one thread block per tile with the statistics taken in the kernel
+    x, rw, w, eps = wl.make_norm_matmul_inputs(2100, 264, 2600, torch.float16, seed=10)
+    folded = ops.fold_norm_weight(rw.to(dev), w.to(dev))
+    ws = torch.empty(ops.norm_matmul_workspace_bytes(2100), dtype=torch.uint8, device=dev)
+    pair = ops.fused_rms_norm_matmul(x.to(dev), folded, eps=eps, workspace=ws)
+    assert ops.read_status(ws) == 0
+    want = ref.fused_rms_norm_matmul(x, rw, w, eps)
+    assert_half_close(pair.cpu(), want, what="fp16 2100x264x2600, clusters of two")
+    single = ops.fused_rms_norm_matmul(x.to(dev), folded, eps=eps, workspace=torch.empty(256, dtype=torch.uint8, device=dev))
+    assert_half_close(single.cpu(), want, what="fp16 2100x264x2600, one block per tile")
+    assert (pair.float() - single.float()).abs().max().item() <= 2.0 ** -9 * want.abs().max().item()  # at most one rounding apart
 
 
 @pytest.mark.gpu
