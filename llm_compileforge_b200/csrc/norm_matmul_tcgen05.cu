@@ -44,7 +44,7 @@
 namespace sfb {
 namespace {
 
-constexpr int kTileM = 128, kTileN = 256, kStepK = 64, kMaxStages = 6;
+constexpr int kTileM = 128, kTileN = 256, kStepK = 64, kMaxStages = 8;
 constexpr int kABytes = kTileM * kStepK * 2;       // 16 KB
 constexpr int kBBlockBytes = kStepK * 128;         // one [64 k][64 n] block: 8 KB
 constexpr int kThreads = 192;
@@ -54,15 +54,17 @@ constexpr int64_t kPrepassRows = 2048;  // from this many rows on, row statistic
 enum { B_FULL = 0, B_EMPTY = kMaxStages, B_ACC_FULL = 2 * kMaxStages, B_ACC_EMPTY = 2 * kMaxStages + 2, B_COUNT = 2 * kMaxStages + 4 };
 // Tile widths: 256 columns for large problems; 128 and 64 when 256-wide tiles would leave SMs without one (few rows).
 // Pipeline depth per width: 192 KB of operands in flight per SM - four 48 KB stages (256), six 32 KB stages (128),
-// or two resident thread blocks of four 24 KB stages each (64).
-constexpr int stages_for(int tn) { return tn == 128 ? 6 : 4; }
-constexpr int smem_bytes(int tn) { return stages_for(tn) * (kABytes + (tn / 64) * kBBlockBytes) + B_COUNT * 8 + 16 + 1024; }
+// eight 24 KB stages (64) when every tile has an SM to itself, or two resident thread blocks of four stages each
+// when there are more 64-wide tiles than SMs.  A load takes about 1900 cycles from issue to "stage full" and the MMA
+// warp's four issues per stage about 330, so with four 64-wide stages a K step costs 630 cycles, with eight about half.
+constexpr int smem_bytes(int tn, int stages) { return stages * (kABytes + (tn / 64) * kBBlockBytes) + B_COUNT * 8 + 16 + 1024; }
 
 struct GemmArgs {
     void* out;
     int64_t out_stride;  // elements between output rows
     int M, N, K;
     int tiles_n, tiles_total;
+    int a_bytes;  // bytes one K step's box of x brings in: 128 per row, kABytes unless there are fewer than 128 rows in all
     float eps;
     int* status;
     const float* rstd;  // per-row rsqrt(mean(x^2) + eps) from the statistics pre-pass; nullptr: taken in this kernel from the A tiles
@@ -170,13 +172,12 @@ __device__ __forceinline__ float sumsq8(uint4 w) {  // sum of squares of eight 1
     return s;
 }
 
-template <bool BF16, bool STATS, int TN>
+template <bool BF16, bool STATS, int TN, int kStages>
 __global__ void __launch_bounds__(kThreads, 1)
 norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const GemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int kStage = kABytes + (TN / 64) * kBBlockBytes;  // bytes per pipeline stage
-    constexpr int kStages = stages_for(TN);
     const int n_k = (a.K + kStepK - 1) / kStepK;  // a ragged last step reads zeros (TMA fills what lies outside the matrices)
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -219,7 +220,7 @@ norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
                 for (int kb = 0; kb < n_k; ++kb, ++g) {
                     const int s = g % kStages;
                     if (!mbar_wait(bar(B_EMPTY + s), ((g / kStages) & 1) ^ 1)) { timed_out = true; break; }
-                    mbar_expect_tx(bar(B_FULL + s), kStage);
+                    mbar_expect_tx(bar(B_FULL + s), a.a_bytes + (TN / 64) * kBBlockBytes);
                     tma_load_2d(a_stage(s), &amap, bar(B_FULL + s), kb * kStepK, m0);
 #pragma unroll
                     for (int nb = 0; nb < TN / 64; ++nb)
@@ -335,6 +336,7 @@ constexpr int kPairStages = 6;
 constexpr int kPairStage = kABytes + 2 * kBBlockBytes;  // per thread block and stage: 32 KB
 constexpr int kPairTile = 256;
 constexpr int pair_smem_bytes() { return kPairStages * kPairStage + B_COUNT * 8 + 16 + 1024; }
+static_assert(kPairStages <= kMaxStages, "barrier slots");
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -614,9 +616,6 @@ int pair_clusters(int dev, int sms) {
 
 int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t wg_stride, void* out, int64_t out_stride, int64_t M,
                        int64_t N, int64_t K, float eps, int dtype, int* status, float* rstd_scratch, cudaStream_t stream) {
-    CUtensorMap amap, bmap;
-    if (!encode_2d(&amap, x, M, K, x_stride, kTileM) || !encode_2d(&bmap, wg, K, N, wg_stride, kStepK))
-        return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: tensor map encoding failed (16-byte aligned bases and row strides are required)");
     const bool bf16 = dtype == SFB_BF16;
     int dev = 0, sms = 0;
     SFB_CUDA_CHECK(cudaGetDevice(&dev));
@@ -628,11 +627,14 @@ int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t 
     //   one thread block per 128 x {256, 128, 64} tile  (ties go to the wider tile: less traffic in total), or
     //   a cluster of two on a 256 x 256 tile, each block taking in 128 + 128 rows - needs the statistics pre-pass,
     //   so only with a workspace for it, and only when strictly cheaper.
+    //   with fewer than 128 rows in all, the box of x is cut to the rows there are (in eights): the MMA still reads 128
+    //   rows of shared memory, but what the rows past M hold only reaches accumulator rows that are never stored.
     const int64_t m_tiles = ceil_div(M, (int64_t)kTileM);
+    const int a_rows = M < kTileM ? (int)std::max<int64_t>(8, ceil_div(M, (int64_t)8) * 8) : kTileM;
     int tn = kTileN;
     int64_t best = -1;
     for (int w : {256, 128, 64}) {
-        const int64_t cost = ceil_div(m_tiles * ceil_div(N, (int64_t)w), (int64_t)sms) * (kTileM + w);
+        const int64_t cost = ceil_div(m_tiles * ceil_div(N, (int64_t)w), (int64_t)sms) * (a_rows + w);
         if (best < 0 || cost < best) { best = cost; tn = w; }
     }
     const int64_t ptiles_n = ceil_div(N, (int64_t)kPairTile), ptiles = ptiles_n * ceil_div(M, (int64_t)kPairTile);
@@ -646,9 +648,13 @@ int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t 
         else row_rstd_kernel<false><<<blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(x), x_stride, (int)M, (int)K, eps, rstd_scratch);
         SFB_CUDA_CHECK(cudaGetLastError());
     }
+    CUtensorMap amap, bmap;
+    if (!encode_2d(&amap, x, M, K, x_stride, pair ? kTileM : a_rows) || !encode_2d(&bmap, wg, K, N, wg_stride, kStepK))
+        return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: tensor map encoding failed (16-byte aligned bases and row strides are required)");
     GemmArgs a{};
     a.out = out; a.out_stride = out_stride;
     a.M = (int)M; a.N = (int)N; a.K = (int)K;
+    a.a_bytes = a_rows * kStepK * 2;
     a.eps = eps; a.status = status;
     a.rstd = prepass ? rstd_scratch : nullptr;
     if (pair) {
@@ -664,23 +670,25 @@ int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t 
     if (tiles > 0x7fffffffLL) return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: too many tiles");
     a.tiles_n = (int)tiles_n;
     a.tiles_total = (int)tiles;
-    // persistent thread blocks walk the tiles; the 64-wide kernel's shared memory lets two of them share an SM
-    const dim3 grid((unsigned)std::min<int64_t>(tiles, tn == 64 ? 2 * sms : sms));
+    // persistent thread blocks walk the tiles; with more 64-wide tiles than SMs two thread blocks of four stages share an SM
+    const bool deep64 = tn == 64 && tiles <= sms;
+    const dim3 grid((unsigned)std::min<int64_t>(tiles, tn == 64 && !deep64 ? 2 * sms : sms));
     auto launch = [&](auto kernel, int smem) -> int {
         SFB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         kernel<<<grid, kThreads, smem, stream>>>(amap, bmap, a);
         SFB_CUDA_CHECK(cudaGetLastError());
         return SFB_OK;
     };
-    auto pick = [&](auto width) -> int {
-        constexpr int W = decltype(width)::value;
-        constexpr int sm = smem_bytes(W);
-        if (bf16) return prepass ? launch(norm_matmul_tcgen05_kernel<true, false, W>, sm) : launch(norm_matmul_tcgen05_kernel<true, true, W>, sm);
-        return prepass ? launch(norm_matmul_tcgen05_kernel<false, false, W>, sm) : launch(norm_matmul_tcgen05_kernel<false, true, W>, sm);
+    auto pick = [&](auto width, auto stages) -> int {
+        constexpr int W = decltype(width)::value, S = decltype(stages)::value;
+        constexpr int sm = smem_bytes(W, S);
+        if (bf16) return prepass ? launch(norm_matmul_tcgen05_kernel<true, false, W, S>, sm) : launch(norm_matmul_tcgen05_kernel<true, true, W, S>, sm);
+        return prepass ? launch(norm_matmul_tcgen05_kernel<false, false, W, S>, sm) : launch(norm_matmul_tcgen05_kernel<false, true, W, S>, sm);
     };
-    if (tn == 64) return pick(std::integral_constant<int, 64>{});
-    if (tn == 128) return pick(std::integral_constant<int, 128>{});
-    return pick(std::integral_constant<int, 256>{});
+    if (deep64) return pick(std::integral_constant<int, 64>{}, std::integral_constant<int, 8>{});
+    if (tn == 64) return pick(std::integral_constant<int, 64>{}, std::integral_constant<int, 4>{});
+    if (tn == 128) return pick(std::integral_constant<int, 128>{}, std::integral_constant<int, 6>{});
+    return pick(std::integral_constant<int, 256>{}, std::integral_constant<int, 4>{});
 }
 
 }  // namespace sfb
