@@ -109,10 +109,16 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+// The MMA-issuing thread is alone in its warp and every instruction it runs between two MMAs is time the tensor pipe
+// idles (an MMA issue returns when the pipe accepts it, i.e. when the one before has finished), so its loop is kept
+// short: descriptors are a per-kernel constant plus the stage offset (low word: start address and leading offset in
+// 16-byte units; high word: stride offset, version, swizzle mode), stage and phase are running counters.
+__device__ __forceinline__ void mma_ss(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                       uint32_t accumulate) {
     asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n mov.b64 da, {%1, %2};\n mov.b64 db, {%3, %4};\n setp.ne.b32 p, %6, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
@@ -139,6 +145,8 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
     d |= (uint64_t)2 << 61;
     return d;
 }
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) { return (uint32_t)smem_desc(addr, lbo_bytes, 0); }
+__device__ __forceinline__ uint32_t desc_hi(uint32_t sbo_bytes) { return (uint32_t)(smem_desc(0, 0, sbo_bytes) >> 32); }
 // Instruction descriptor for kind::f16: fp32 accumulate, 16-bit A/B, A K-major, B MN-major, M x N tile.
 __host__ __device__ constexpr uint32_t instr_desc(bool bf16, int m, int n) {
     return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (1u << 16) | ((uint32_t)(n >> 3) << 17) |
@@ -232,23 +240,28 @@ norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
         // ============================ MMA issuer ==============================
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc(BF16, kTileM, TN);
+            const uint32_t a_lo0 = desc_lo(a_stage(0), 16), b_lo0 = desc_lo(b_stage(0), kBBlockBytes), hi = desc_hi(1024);
             bool ok = true;
-            int g = 0, it = 0;
+            uint32_t s = 0, phase = 0, off = 0;  // stage, its parity, its offset in 16-byte units
+            int it = 0;
             for (int tile = blockIdx.x; tile < a.tiles_total && ok; tile += gridDim.x, ++it) {
                 const int buf = it & 1;
                 ok = mbar_wait(bar(B_ACC_EMPTY + buf), ((it >> 1) & 1) ^ 1);  // the epilogue has drained this accumulator
                 if (!ok) break;
                 tc_fence_after();
-                for (int kb = 0; kb < n_k && ok; ++kb, ++g) {
-                    const int s = g % kStages;
-                    ok = mbar_wait(bar(B_FULL + s), (g / kStages) & 1);
+                const uint32_t d = tmem + buf * TN;
+                for (int kb = 0; kb < n_k; ++kb) {
+                    ok = mbar_wait(bar0 + 8u * (B_FULL + s), phase);
                     if (!ok) break;
                     tc_fence_after();
-#pragma unroll
-                    for (int ks = 0; ks < kStepK / 16; ++ks)
-                        mma_ss(tmem + buf * TN, smem_desc(a_stage(s) + ks * 32, 16, 1024),
-                               smem_desc(b_stage(s) + ks * 2048, kBBlockBytes, 1024), idesc, (kb > 0 || ks > 0));
-                    tc_commit(bar(B_EMPTY + s));
+                    mma_ss(d, a_lo0 + off, hi, b_lo0 + off, hi, idesc, kb > 0);
+                    mma_ss(d, a_lo0 + off + 2, hi, b_lo0 + off + 128, hi, idesc, 1);
+                    mma_ss(d, a_lo0 + off + 4, hi, b_lo0 + off + 256, hi, idesc, 1);
+                    mma_ss(d, a_lo0 + off + 6, hi, b_lo0 + off + 384, hi, idesc, 1);
+                    tc_commit(bar0 + 8u * (B_EMPTY + s));
+                    ++s;
+                    off += kStage >> 4;
+                    if (s == kStages) { s = 0; off = 0; phase ^= 1; }
                 }
                 if (ok) tc_commit(bar(B_ACC_FULL + buf));
             }
@@ -372,10 +385,12 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {  // arrives on th
                  ::"r"(bar), "h"((uint16_t)3)
                  : "memory");
 }
-__device__ __forceinline__ void mma_ss_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void mma_ss_pair(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                            uint32_t accumulate) {
     asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n mov.b64 da, {%1, %2};\n mov.b64 db, {%3, %4};\n setp.ne.b32 p, %6, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
@@ -439,23 +454,28 @@ norm_matmul_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_c
         // ========================= MMA issuer (leader only) =========================
         if (lane == 0 && rank == 0) {
             constexpr uint32_t idesc = instr_desc(BF16, 2 * kTileM, kPairTile);
+            const uint32_t a_lo0 = desc_lo(a_stage(0), 16), b_lo0 = desc_lo(b_stage(0), kBBlockBytes), hi = desc_hi(1024);
             bool ok = true;
-            int g = 0, it = 0;
+            uint32_t s = 0, phase = 0, off = 0;
+            int it = 0;
             for (int tile = pair; tile < a.tiles_total && ok; tile += n_pairs, ++it) {
                 const int buf = it & 1;
                 ok = mbar_wait(bar(B_ACC_EMPTY + buf), ((it >> 1) & 1) ^ 1);  // both blocks have drained this accumulator
                 if (!ok) break;
                 tc_fence_after();
-                for (int kb = 0; kb < n_k && ok; ++kb, ++g) {
-                    const int s = g % kPairStages;
-                    ok = mbar_wait(bar(B_FULL + s), (g / kPairStages) & 1);
+                const uint32_t d = tmem + buf * kPairTile;
+                for (int kb = 0; kb < n_k; ++kb) {
+                    ok = mbar_wait(bar0 + 8u * (B_FULL + s), phase);
                     if (!ok) break;
                     tc_fence_after();
-#pragma unroll
-                    for (int ks = 0; ks < kStepK / 16; ++ks)
-                        mma_ss_pair(tmem + buf * kPairTile, smem_desc(a_stage(s) + ks * 32, 16, 1024),
-                                    smem_desc(b_stage(s) + ks * 2048, kBBlockBytes, 1024), idesc, (kb > 0 || ks > 0));
-                    tc_commit_pair(bar(B_EMPTY + s));
+                    mma_ss_pair(d, a_lo0 + off, hi, b_lo0 + off, hi, idesc, kb > 0);
+                    mma_ss_pair(d, a_lo0 + off + 2, hi, b_lo0 + off + 128, hi, idesc, 1);
+                    mma_ss_pair(d, a_lo0 + off + 4, hi, b_lo0 + off + 256, hi, idesc, 1);
+                    mma_ss_pair(d, a_lo0 + off + 6, hi, b_lo0 + off + 384, hi, idesc, 1);
+                    tc_commit_pair(bar0 + 8u * (B_EMPTY + s));
+                    ++s;
+                    off += kPairStage >> 4;
+                    if (s == kPairStages) { s = 0; off = 0; phase ^= 1; }
                 }
                 if (ok) tc_commit_pair(bar(B_ACC_FULL + buf));
             }
