@@ -57,7 +57,7 @@ enum { B_FULL = 0, B_EMPTY = kMaxStages, B_ACC_FULL = 2 * kMaxStages, B_ACC_EMPT
 // eight 24 KB stages (64) when every tile has an SM to itself, or two resident thread blocks of four stages each
 // when there are more 64-wide tiles than SMs.  A load takes about 1900 cycles from issue to "stage full" and the MMA
 // warp's four issues per stage about 330, so with four 64-wide stages a K step costs 630 cycles, with eight about half.
-constexpr int smem_bytes(int tn, int stages) { return stages * (kABytes + (tn / 64) * kBBlockBytes) + B_COUNT * 8 + 16 + 1024; }
+constexpr int smem_bytes(int tn, int stages, int ksub) { return stages * ksub * (kABytes + (tn / 64) * kBBlockBytes) + B_COUNT * 8 + 16 + 1024; }
 
 struct GemmArgs {
     void* out;
@@ -180,13 +180,14 @@ __device__ __forceinline__ float sumsq8(uint4 w) {  // sum of squares of eight 1
     return s;
 }
 
-template <bool BF16, bool STATS, int TN, int kStages>
+template <bool BF16, bool STATS, int TN, int kStages, int KSUB>
 __global__ void __launch_bounds__(kThreads, 1)
 norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const GemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int kStage = kABytes + (TN / 64) * kBBlockBytes;  // bytes per pipeline stage
-    const int n_k = (a.K + kStepK - 1) / kStepK;  // a ragged last step reads zeros (TMA fills what lies outside the matrices)
+    constexpr int kSub = kABytes + (TN / 64) * kBBlockBytes;  // one 64-wide K step: a box of x and TN / 64 boxes of the weight
+    constexpr int kStage = KSUB * kSub;                       // a pipeline stage = KSUB such steps behind one pair of barriers
+    const int n_k = (a.K + kStepK * KSUB - 1) / (kStepK * KSUB);  // a ragged last step reads zeros (TMA fills what lies outside)
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -221,21 +222,29 @@ norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
     // tiles, g = it * n_k + kb its K steps: stage g % kStages, accumulator it & 1.
     if (warp == 4) {
         // ============================ TMA producer ============================
-        if (lane == 0) {
-            int g = 0;
-            for (int tile = blockIdx.x; tile < a.tiles_total && !timed_out; tile += gridDim.x) {
-                const int m0 = (tile / a.tiles_n) * kTileM, n0 = (tile % a.tiles_n) * TN;
-                for (int kb = 0; kb < n_k; ++kb, ++g) {
-                    const int s = g % kStages;
-                    if (!mbar_wait(bar(B_EMPTY + s), ((g / kStages) & 1) ^ 1)) { timed_out = true; break; }
-                    mbar_expect_tx(bar(B_FULL + s), a.a_bytes + (TN / 64) * kBBlockBytes);
-                    tma_load_2d(a_stage(s), &amap, bar(B_FULL + s), kb * kStepK, m0);
-#pragma unroll
-                    for (int nb = 0; nb < TN / 64; ++nb)
-                        tma_load_2d(b_stage(s) + nb * kBBlockBytes, &bmap, bar(B_FULL + s), n0 + nb * 64, kb * kStepK);
-                }
+        // The whole warp waits for the stage; then lane l issues the l-th box of the stage (per K step one box of x and
+        // TN / 64 boxes of the weight) in ONE warp instruction: the producer's chain per stage is a wait, the expect and a
+        // single issue, whatever the number of boxes - it, too, is a single instruction stream whose length per stage
+        // bounds the pipeline when the tiles are small.
+        constexpr int kBoxesPerSub = 1 + TN / 64, kBoxes = KSUB * kBoxesPerSub;
+        static_assert(kBoxes <= 32, "one lane per box");
+        const int sub = lane / kBoxesPerSub, j = lane % kBoxesPerSub;  // lane's box: j == 0 the x box, else weight box j - 1
+        const bool has_box = lane < kBoxes;
+        const CUtensorMap* map = j == 0 ? &amap : &bmap;
+        const uint32_t dst0 = base + (uint32_t)sub * kSub + (j == 0 ? 0u : (uint32_t)(kABytes + (j - 1) * kBBlockBytes));
+        uint32_t s = 0, ephase = 1;
+        for (int tile = blockIdx.x; tile < a.tiles_total && !timed_out; tile += gridDim.x) {
+            const int m0 = (tile / a.tiles_n) * kTileM, n0 = (tile % a.tiles_n) * TN;
+            for (int kb = 0; kb < n_k; ++kb) {
+                if (!mbar_wait(bar0 + 8u * (B_EMPTY + s), ephase)) { timed_out = true; break; }
+                const uint32_t full = bar0 + 8u * (B_FULL + s);
+                if (lane == 0) mbar_expect_tx(full, KSUB * (a.a_bytes + (TN / 64) * kBBlockBytes));
+                const int k0 = (kb * KSUB + sub) * kStepK;
+                if (has_box) tma_load_2d(dst0 + s * kStage, map, full, j == 0 ? k0 : n0 + (j - 1) * 64, j == 0 ? m0 : k0);
+                if (++s == kStages) { s = 0; ephase ^= 1; }
             }
         }
+        timed_out = __any_sync(0xffffffffu, timed_out);
     } else if (warp == 5) {
         // ============================ MMA issuer ==============================
         if (lane == 0) {
@@ -254,10 +263,14 @@ norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
                     ok = mbar_wait(bar0 + 8u * (B_FULL + s), phase);
                     if (!ok) break;
                     tc_fence_after();
-                    mma_ss(d, a_lo0 + off, hi, b_lo0 + off, hi, idesc, kb > 0);
-                    mma_ss(d, a_lo0 + off + 2, hi, b_lo0 + off + 128, hi, idesc, 1);
-                    mma_ss(d, a_lo0 + off + 4, hi, b_lo0 + off + 256, hi, idesc, 1);
-                    mma_ss(d, a_lo0 + off + 6, hi, b_lo0 + off + 384, hi, idesc, 1);
+#pragma unroll
+                    for (int sub = 0; sub < KSUB; ++sub) {
+                        const uint32_t o = off + sub * (kSub >> 4);
+                        mma_ss(d, a_lo0 + o, hi, b_lo0 + o, hi, idesc, sub > 0 || kb > 0);
+                        mma_ss(d, a_lo0 + o + 2, hi, b_lo0 + o + 128, hi, idesc, 1);
+                        mma_ss(d, a_lo0 + o + 4, hi, b_lo0 + o + 256, hi, idesc, 1);
+                        mma_ss(d, a_lo0 + o + 6, hi, b_lo0 + o + 384, hi, idesc, 1);
+                    }
                     tc_commit(bar0 + 8u * (B_EMPTY + s));
                     ++s;
                     off += kStage >> 4;
@@ -280,9 +293,12 @@ norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
                 const int s = g % kStages;
                 ok = mbar_wait(bar(B_FULL + s), (g / kStages) & 1);
                 if (!ok) break;
-                const uint4* rowp = reinterpret_cast<const uint4*>(base_ptr + (size_t)s * kStage + (size_t)row * 128);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) ss += sumsq8<BF16>(rowp[(c + row) & 7]);
+                for (int sub = 0; sub < KSUB; ++sub) {
+                    const uint4* rowp = reinterpret_cast<const uint4*>(base_ptr + (size_t)s * kStage + (size_t)sub * kSub + (size_t)row * 128);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) ss += sumsq8<BF16>(rowp[(c + row) & 7]);
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_EMPTY + s));
             }
@@ -699,16 +715,18 @@ int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t 
         SFB_CUDA_CHECK(cudaGetLastError());
         return SFB_OK;
     };
-    auto pick = [&](auto width, auto stages) -> int {
-        constexpr int W = decltype(width)::value, S = decltype(stages)::value;
-        constexpr int sm = smem_bytes(W, S);
-        if (bf16) return prepass ? launch(norm_matmul_tcgen05_kernel<true, false, W, S>, sm) : launch(norm_matmul_tcgen05_kernel<true, true, W, S>, sm);
-        return prepass ? launch(norm_matmul_tcgen05_kernel<false, false, W, S>, sm) : launch(norm_matmul_tcgen05_kernel<false, true, W, S>, sm);
+    auto pick = [&](auto width, auto stages, auto ksub) -> int {
+        constexpr int W = decltype(width)::value, S = decltype(stages)::value, KS = decltype(ksub)::value;
+        constexpr int sm = smem_bytes(W, S, KS);
+        if (bf16) return prepass ? launch(norm_matmul_tcgen05_kernel<true, false, W, S, KS>, sm) : launch(norm_matmul_tcgen05_kernel<true, true, W, S, KS>, sm);
+        return prepass ? launch(norm_matmul_tcgen05_kernel<false, false, W, S, KS>, sm) : launch(norm_matmul_tcgen05_kernel<false, true, W, S, KS>, sm);
     };
-    if (deep64) return pick(std::integral_constant<int, 64>{}, std::integral_constant<int, 8>{});
-    if (tn == 64) return pick(std::integral_constant<int, 64>{}, std::integral_constant<int, 4>{});
-    if (tn == 128) return pick(std::integral_constant<int, 128>{}, std::integral_constant<int, 6>{});
-    return pick(std::integral_constant<int, 256>{}, std::integral_constant<int, 4>{});
+    using std::integral_constant;
+    // 64-wide tiles with an SM each: four stages of two K steps (each wait / commit of the MMA warp covers eight MMAs)
+    if (deep64) return pick(integral_constant<int, 64>{}, integral_constant<int, 4>{}, integral_constant<int, 2>{});
+    if (tn == 64) return pick(integral_constant<int, 64>{}, integral_constant<int, 4>{}, integral_constant<int, 1>{});
+    if (tn == 128) return pick(integral_constant<int, 128>{}, integral_constant<int, 6>{}, integral_constant<int, 1>{});
+    return pick(integral_constant<int, 256>{}, integral_constant<int, 4>{}, integral_constant<int, 1>{});
 }
 
 }  // namespace sfb
