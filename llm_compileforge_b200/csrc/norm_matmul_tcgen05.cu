@@ -54,9 +54,11 @@ constexpr int64_t kPrepassRows = 2048;  // from this many rows on, row statistic
 enum { B_FULL = 0, B_EMPTY = kMaxStages, B_ACC_FULL = 2 * kMaxStages, B_ACC_EMPTY = 2 * kMaxStages + 2, B_COUNT = 2 * kMaxStages + 4 };
 // Tile widths: 256 columns for large problems; 128 and 64 when 256-wide tiles would leave SMs without one (few rows).
 // Pipeline depth per width: 192 KB of operands in flight per SM - four 48 KB stages (256), six 32 KB stages (128),
-// eight 24 KB stages (64) when every tile has an SM to itself, or two resident thread blocks of four stages each
-// when there are more 64-wide tiles than SMs.  A load takes about 1900 cycles from issue to "stage full" and the MMA
-// warp's four issues per stage about 330, so with four 64-wide stages a K step costs 630 cycles, with eight about half.
+// four stages of TWO K steps each (64-wide tiles with an SM each: 2 x 24 KB per stage), or two resident thread blocks of
+// four 24 KB stages when there are more 64-wide tiles than SMs.  With narrow tiles the MMAs are short (an N = 64 MMA
+// occupies the pipe for about 50 cycles, four of them 200) and what the MMA warp's one thread executes between them
+// - barrier wait about 80 cycles, commit 65, loop - is time the pipe idles: measured 630 cycles per K step with the
+// first version of that loop, about 400 now (840 per two-step stage with the trace stamps in).
 constexpr int smem_bytes(int tn, int stages, int ksub) { return stages * ksub * (kABytes + (tn / 64) * kBBlockBytes) + B_COUNT * 8 + 16 + 1024; }
 
 struct GemmArgs {
