@@ -29,8 +29,9 @@
 //             pack, 16-byte stores
 // Every wait is bounded; a stuck pipeline sets SFB_STATUS_WAIT_TIMEOUT in *status and the block leaves
 // through the common teardown, which releases tensor memory.
-// Bound: 2*M*N*K flops on the tensor pipe once operands arrive fast enough - an SM takes in about 110 GB/s, which
-// is what holds the single-block kernel (48 KB per K step) below the pipe's rate and the few-row case far below it.
+// Bound: 2*M*N*K flops on the tensor pipe.  What keeps the pipe from being busy all the time: the 48 KB a block takes
+// in per K step (110 GB/s per SM), and the instruction chain of the one MMA-issuing thread between two K steps (see
+// the note at mma_ss); the cluster kernel halves both.
 // HBM traffic is x once per N tile (L2 keeps it) and Wg once per M tile.
 
 #include <cuda.h>
@@ -349,9 +350,10 @@ norm_matmul_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
 // ---------------------------------------------------------------------------------------------------------------
 // Two thread blocks on one 256 x 256 tile (a cluster of two, tcgen05 cta_group::2), for many rows.
 //
-// With one thread block per 128 x 256 tile every SM takes in 48 KB per K step (16 KB of x, 32 KB of the weight),
-// and that intake - about 110 GB/s per SM - is what bounds the kernel above, not the tensor pipe.  Here the two
-// thread blocks of a cluster share the weight tile: each loads its own 128 rows of x and HALF of the 256 weight
+// With one thread block per 128 x 256 tile every SM takes in 48 KB per K step (16 KB of x, 32 KB of the weight,
+// about 110 GB/s per SM) and the issuing thread pays its wait / commit / loop chain once per four M 128 MMAs; the
+// tensor pipe is 86 % busy.  Here the two thread blocks of a cluster share the weight tile, and an M 256 MMA is twice
+// the work per issue (94 % busy): each loads its own 128 rows of x and HALF of the 256 weight
 // columns (32 KB per step and SM), and the leader's MMA (M 256) reads the B operand out of both blocks' shared
 // memory; each block's tensor memory receives its own 128 rows of the accumulator.
 //   leader and peer, warp 4: wait for the local "stage empty" barrier, TMA into local shared memory, transaction
@@ -659,9 +661,9 @@ int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t 
     SFB_CUDA_CHECK(cudaGetDevice(&dev));
     SFB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
 
-    // Shape of the work.  What bounds this kernel is what one SM can take in per K step (about 110 GB/s: a 128-row
-    // panel of x plus its share of the weight columns, kTileM + width rows of 128 bytes), so every candidate is
-    // priced as  rounds of tiles on the busiest SM x rows taken in per step,  and the cheapest runs:
+    // Shape of the work.  Every candidate is priced by what the busiest SM has to take in: a 128-row panel of x plus
+    // its share of the weight columns per K step (kTileM + width rows of 128 bytes) x its rounds of tiles - a proxy
+    // that also orders the shapes by tensor work per SM - and the cheapest runs:
     //   one thread block per 128 x {256, 128, 64} tile  (ties go to the wider tile: less traffic in total), or
     //   a cluster of two on a 256 x 256 tile, each block taking in 128 + 128 rows - needs the statistics pre-pass,
     //   so only with a workspace for it, and only when strictly cheaper.
