@@ -383,6 +383,11 @@ SFB_API int sfb_prefill_paged_fp8(const SFBTensor* q, const SFBTensor* k_cache, 
  * cheaper shape: that kernel needs the pre-pass); without it the statistics are always taken
  * inside the single-block GEMM kernel. */
 SFB_API int64_t sfb_fused_rms_norm_matmul_workspace_bytes(int64_t rows);
+/* Host arithmetic only (no device call): the tile shape sfb_fused_rms_norm_matmul runs for an [rows, K] x [K, cols]
+ * problem on a device with `sms` SMs that can hold `clusters` clusters of two thread blocks, with or without a full
+ * workspace.  plan6 = {clusters of two (0/1), tile width, pipeline stages, K steps per stage, statistics pre-pass (0/1),
+ * rows of x per TMA box}. */
+SFB_API int sfb_fused_rms_norm_matmul_plan(int64_t rows, int64_t cols, int sms, int clusters, int has_workspace, int32_t* plan6);
 SFB_API int sfb_fold_norm_weight(const SFBTensor* rms_weight, const SFBTensor* mat_weight, SFBTensor* folded, int dtype, void* stream);
 SFB_API int sfb_fused_rms_norm_matmul(const SFBTensor* x, const SFBTensor* folded_weight, SFBTensor* out, int dtype, float eps,
                                       void* workspace, int64_t workspace_bytes, void* stream);

@@ -128,6 +128,8 @@ def load() -> ctypes.CDLL:
     lib.sfb_fused_rms_norm_matmul.argtypes = [_T, _T, _T, c_int, c_float, c_void_p, c_int64, c_void_p]
     lib.sfb_fused_rms_norm_matmul_workspace_bytes.restype = c_int64
     lib.sfb_fused_rms_norm_matmul_workspace_bytes.argtypes = [c_int64]
+    lib.sfb_fused_rms_norm_matmul_plan.restype = ctypes.c_int
+    lib.sfb_fused_rms_norm_matmul_plan.argtypes = [c_int64, c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int32)]
     lib.sfb_peer_signal_wait.restype = c_int
     lib.sfb_peer_signal_wait.argtypes = [POINTER(c_void_p), c_int, c_int, ctypes.c_uint32, c_int, c_void_p, c_void_p]
     _lib = lib

@@ -560,6 +560,13 @@ int64_t sfb_fused_rms_norm_matmul_workspace_bytes(int64_t rows) {
     return kWorkspaceHeader + ceil_div(rows * 4, 256) * 256;
 }
 
+int sfb_fused_rms_norm_matmul_plan(int64_t rows, int64_t cols, int sms, int clusters, int has_workspace, int32_t* plan6) {
+    if (rows < 0 || cols < 0 || sms <= 0 || clusters < 0 || !plan6) return fail(SFB_ERR_INVALID_ARG, "fused_rms_norm_matmul_plan: bad argument");
+    const NormMatmulPlan p = plan_norm_matmul(rows, cols, sms, clusters, has_workspace != 0);
+    plan6[0] = p.pair; plan6[1] = p.tile_n; plan6[2] = p.stages; plan6[3] = p.k_steps_per_stage; plan6[4] = p.prepass; plan6[5] = p.x_box_rows;
+    return SFB_OK;
+}
+
 int sfb_fused_rms_norm_matmul(const SFBTensor* x, const SFBTensor* folded_weight, SFBTensor* out, int dtype, float eps, void* workspace,
                               int64_t workspace_bytes, void* stream) {
     if (dtype != SFB_BF16 && dtype != SFB_F16) return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: bf16 or fp16 (other types go to the fallback executor)");

@@ -654,6 +654,40 @@ int pair_clusters(int dev, int sms) {
 
 }  // namespace
 
+// Shape of the work (host arithmetic only).  Every candidate is priced by what the busiest SM has to take in: a
+// 128-row panel of x plus its share of the weight columns per K step (kTileM + width rows of 128 bytes) x its rounds
+// of tiles - a proxy that also orders the shapes by tensor work per SM - and the cheapest runs:
+//   one thread block per 128 x {256, 128, 64} tile  (ties go to the wider tile: less traffic in total), or
+//   a cluster of two on a 256 x 256 tile, each block taking in 128 + 128 rows - needs the statistics pre-pass,
+//   so only with a workspace for it, and only when strictly cheaper.
+//   With fewer than 128 rows in all, the box of x is cut to the rows there are (in eights): the MMA still reads 128
+//   rows of shared memory, but what the rows past M hold only reaches accumulator rows that are never stored.
+NormMatmulPlan plan_norm_matmul(int64_t M, int64_t N, int sms, int clusters, bool has_scratch) {
+    NormMatmulPlan p{};
+    sms = std::max(sms, 1);
+    const int64_t m_tiles = ceil_div(M, (int64_t)kTileM);
+    p.x_box_rows = M < kTileM ? (int)std::max<int64_t>(8, ceil_div(M, (int64_t)8) * 8) : kTileM;
+    p.tile_n = kTileN;
+    int64_t best = -1;
+    for (int w : {256, 128, 64}) {
+        const int64_t cost = ceil_div(m_tiles * ceil_div(N, (int64_t)w), (int64_t)sms) * (p.x_box_rows + w);
+        if (best < 0 || cost < best) { best = cost; p.tile_n = w; }
+    }
+    const int64_t ptiles = ceil_div(N, (int64_t)kPairTile) * ceil_div(M, (int64_t)kPairTile);
+    p.pair = has_scratch && clusters > 0 && ptiles <= 0x7fffffffLL &&
+             ceil_div(ptiles, (int64_t)clusters) * (kTileM + kPairTile / 2) < best;
+    p.prepass = has_scratch && (p.pair || M >= kPrepassRows);
+    if (p.pair) {
+        p.tile_n = kPairTile; p.x_box_rows = kTileM; p.stages = kPairStages; p.k_steps_per_stage = 1;
+    } else {
+        const int64_t tiles = m_tiles * ceil_div(N, (int64_t)p.tile_n);
+        const bool deep64 = p.tile_n == 64 && tiles <= sms;  // every 64-wide tile has an SM to itself
+        p.stages = p.tile_n == 128 ? 6 : 4;
+        p.k_steps_per_stage = deep64 ? 2 : 1;
+    }
+    return p;
+}
+
 int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t wg_stride, void* out, int64_t out_stride, int64_t M,
                        int64_t N, int64_t K, float eps, int dtype, int* status, float* rstd_scratch, cudaStream_t stream) {
     const bool bf16 = dtype == SFB_BF16;
@@ -661,27 +695,14 @@ int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t 
     SFB_CUDA_CHECK(cudaGetDevice(&dev));
     SFB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
 
-    // Shape of the work.  Every candidate is priced by what the busiest SM has to take in: a 128-row panel of x plus
-    // its share of the weight columns per K step (kTileM + width rows of 128 bytes) x its rounds of tiles - a proxy
-    // that also orders the shapes by tensor work per SM - and the cheapest runs:
-    //   one thread block per 128 x {256, 128, 64} tile  (ties go to the wider tile: less traffic in total), or
-    //   a cluster of two on a 256 x 256 tile, each block taking in 128 + 128 rows - needs the statistics pre-pass,
-    //   so only with a workspace for it, and only when strictly cheaper.
-    //   with fewer than 128 rows in all, the box of x is cut to the rows there are (in eights): the MMA still reads 128
-    //   rows of shared memory, but what the rows past M hold only reaches accumulator rows that are never stored.
-    const int64_t m_tiles = ceil_div(M, (int64_t)kTileM);
-    const int a_rows = M < kTileM ? (int)std::max<int64_t>(8, ceil_div(M, (int64_t)8) * 8) : kTileM;
-    int tn = kTileN;
-    int64_t best = -1;
-    for (int w : {256, 128, 64}) {
-        const int64_t cost = ceil_div(m_tiles * ceil_div(N, (int64_t)w), (int64_t)sms) * (a_rows + w);
-        if (best < 0 || cost < best) { best = cost; tn = w; }
-    }
     const int64_t ptiles_n = ceil_div(N, (int64_t)kPairTile), ptiles = ptiles_n * ceil_div(M, (int64_t)kPairTile);
     int clusters = 0;
     if (rstd_scratch != nullptr && ptiles <= 0x7fffffffLL) clusters = bf16 ? pair_clusters<true>(dev, sms) : pair_clusters<false>(dev, sms);
-    const bool pair = clusters > 0 && ceil_div(ptiles, (int64_t)clusters) * (kTileM + kPairTile / 2) < best;
-    const bool prepass = rstd_scratch != nullptr && (pair || M >= kPrepassRows);
+    const NormMatmulPlan plan = plan_norm_matmul(M, N, sms, clusters, rstd_scratch != nullptr);
+    const bool pair = plan.pair != 0;
+    const int tn = plan.tile_n, a_rows = plan.x_box_rows;
+    const int64_t m_tiles = ceil_div(M, (int64_t)kTileM);
+    const bool prepass = plan.prepass != 0;
     if (prepass) {
         const unsigned blocks = (unsigned)ceil_div(M, (int64_t)8);
         if (bf16) row_rstd_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(x), x_stride, (int)M, (int)K, eps, rstd_scratch);
@@ -711,7 +732,7 @@ int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t 
     a.tiles_n = (int)tiles_n;
     a.tiles_total = (int)tiles;
     // persistent thread blocks walk the tiles; with more 64-wide tiles than SMs two thread blocks of four stages share an SM
-    const bool deep64 = tn == 64 && tiles <= sms;
+    const bool deep64 = plan.k_steps_per_stage == 2;
     const dim3 grid((unsigned)std::min<int64_t>(tiles, tn == 64 && !deep64 ? 2 * sms : sms));
     auto launch = [&](auto kernel, int smem) -> int {
         SFB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));

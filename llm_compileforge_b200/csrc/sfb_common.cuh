@@ -292,6 +292,16 @@ int launch_expand_fp8_blocks(const void* k_codes, const void* v_codes, const flo
 // norm_matmul_tcgen05.cu: Wg = diag(g) W, and y = rstd(x) * (x @ Wg) on the tensor cores (strides in elements)
 int launch_fold_norm_weight(const void* g, const void* w, void* out, int64_t K, int64_t N, int64_t w_stride, int64_t out_stride,
                             int dtype, cudaStream_t stream);
+// Tile shape the fused norm-matmul launcher picks for a problem (see plan_norm_matmul in norm_matmul_tcgen05.cu).
+struct NormMatmulPlan {
+    int pair;               // 1: clusters of two thread blocks on 256 x 256 tiles; 0: one thread block per 128 x tile_n tile
+    int tile_n;             // tile width
+    int stages;             // pipeline stages
+    int k_steps_per_stage;  // 64-wide K steps behind one pair of barriers
+    int prepass;            // 1: row statistics from the pre-pass kernel
+    int x_box_rows;         // rows of x one TMA box brings in
+};
+NormMatmulPlan plan_norm_matmul(int64_t M, int64_t N, int sms, int clusters, bool has_scratch);
 int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t wg_stride, void* out, int64_t out_stride, int64_t M,
                        int64_t N, int64_t K, float eps, int dtype, int* status, float* rstd_scratch, cudaStream_t stream);
 

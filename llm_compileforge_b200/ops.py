@@ -373,3 +373,13 @@ def fused_rms_norm_matmul(x: torch.Tensor, folded_weight: torch.Tensor, eps: flo
 
 def norm_matmul_workspace_bytes(rows: int) -> int:
     return int(_lib.load().sfb_fused_rms_norm_matmul_workspace_bytes(int(rows)))
+
+
+def norm_matmul_plan(rows: int, cols: int, *, sms: int = 148, clusters: int = 74, has_workspace: bool = True) -> dict:
+    """The tile shape :func:`fused_rms_norm_matmul` runs for ``[rows, K] x [K, cols]`` (host arithmetic, no device needed)."""
+    import ctypes
+
+    out = (ctypes.c_int32 * 6)()
+    check(_lib.load().sfb_fused_rms_norm_matmul_plan(int(rows), int(cols), int(sms), int(clusters), int(bool(has_workspace)), out))
+    keys = ("pair", "tile_n", "stages", "k_steps_per_stage", "prepass", "x_box_rows")
+    return dict(zip(keys, (int(v) for v in out)))

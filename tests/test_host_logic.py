@@ -91,3 +91,32 @@ def test_b200_hardware_spec_has_the_loader_schema():
         hbm = [m for m in spec["memory_levels"] if m["name"].startswith("HBM")][0]
         tensor = [c for c in spec["compute_units"] if "Tensor" in c["name"]][0]
         assert abs(hbm["bandwidth_gbs"] - peaks["hbm_gbs"]) < 1 and abs(tensor["bf16_tflops"] - peaks["bf16_tflops_sustained"]) < 1
+
+
+def test_norm_matmul_plan_follows_the_intake_cost_model():
+    """The fused norm-matmul launcher's tile shape (host arithmetic behind ``sfb_fused_rms_norm_matmul_plan``): every
+    candidate costs rounds-of-tiles-on-the-busiest-SM x rows taken in per K step; the cluster of two only with a
+    workspace for its statistics pre-pass and only when strictly cheaper."""
+    from llm_compileforge_b200 import ops
+
+    plan = ops.norm_matmul_plan
+    # decode-sized: 64-wide tiles, an SM each (96 tiles on 148 SMs) -> two K steps per stage; the x box holds the rows there are
+    assert plan(1, 6144) == dict(pair=0, tile_n=64, stages=4, k_steps_per_stage=2, prepass=0, x_box_rows=8)
+    assert plan(100, 6144)["x_box_rows"] == 104 and plan(128, 6144)["x_box_rows"] == 128
+    # 256 rows: 64-wide would need two rounds (192 tiles), 256-wide leaves 100 SMs idle: 128-wide, six stages, one launch
+    assert plan(256, 6144) == dict(pair=0, tile_n=128, stages=6, k_steps_per_stage=1, prepass=0, x_box_rows=128)
+    # more 64-wide tiles than SMs (300 of them, three rounds of 8 + 64 rows against two of 8 + 128 or one of 8 + 256):
+    # two thread blocks per SM, one K step per stage
+    assert plan(8, 19200) == dict(pair=0, tile_n=64, stages=4, k_steps_per_stage=1, prepass=0, x_box_rows=8)
+    # from 512 rows on the cluster of two is cheaper (48 pair tiles: 1 x 256 against 1 x 384) - if there is a workspace
+    assert plan(512, 6144) == dict(pair=1, tile_n=256, stages=6, k_steps_per_stage=1, prepass=1, x_box_rows=128)
+    assert plan(512, 6144, has_workspace=False) == dict(pair=0, tile_n=256, stages=4, k_steps_per_stage=1, prepass=0, x_box_rows=128)
+    assert plan(512, 6144, clusters=0)["pair"] == 0  # a device that cannot co-schedule the pair
+    # prefill-sized: pair + pre-pass; without a workspace the single-block kernel with in-kernel statistics
+    assert plan(16384, 6144)["pair"] == 1 and plan(16384, 6144)["prepass"] == 1
+    big = plan(16384, 6144, has_workspace=False)
+    assert (big["pair"], big["tile_n"], big["prepass"]) == (0, 256, 0)
+    # ties between widths go to the wider tile: 2 x 384 (256-wide, 165 tiles) = 3 x 256 (128-wide, 315 tiles)
+    assert plan(1920, 2568, has_workspace=False)["tile_n"] == 256
+    with pytest.raises(ValueError):
+        plan(-1, 8)

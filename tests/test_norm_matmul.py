@@ -59,7 +59,9 @@ def test_kernel_matches_reference_fixture(name):
                                    # cluster): the last row block and the last column block are ragged in the second block's half
                                    (2300, 1000, 2440),
                                    # fewer than 128 rows: the box of x is cut to the rows present (16, 64, 104 of them)
-                                   (16, 1024, 3072), (64, 4096, 6144), (100, 520, 776)])
+                                   (16, 1024, 3072), (64, 4096, 6144), (100, 520, 776),
+                                   # more 64-wide tiles than SMs: two thread blocks share an SM, one K step per stage
+                                   (8, 264, 19200)])
 def test_kernel_matches_oracle_ragged(m, k, n):
     """Ragged M / N / K (rows past M, columns past N and a partial last K step are zero-filled by TMA and never stored),
     several K rounds of the operand ring, strided input rows; status word stays clean."""
