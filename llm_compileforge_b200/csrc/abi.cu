@@ -2,6 +2,9 @@
 // The kernels live in the sibling .cu files; nothing here touches device data.
 
 #include <cstring>
+#include <mutex>
+#include <utility>
+#include <vector>
 
 #include "sfb_common.cuh"
 
@@ -22,6 +25,19 @@ int fail(int status, const char* fmt, ...) {
     vsnprintf(g_error, sizeof(g_error), fmt, ap);
     va_end(ap);
     return status;
+}
+
+int allow_shared_memory_once(const void* kernel, int smem_bytes) {
+    static std::mutex mu;
+    static std::vector<std::pair<const void*, int>> done;
+    int dev = 0;
+    SFB_CUDA_CHECK(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    for (const auto& e : done)
+        if (e.first == kernel && e.second == dev) return SFB_OK;
+    SFB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    done.emplace_back(kernel, dev);
+    return SFB_OK;
 }
 
 int make_view(const SFBTensor* t, const char* what, int min_rank, int max_rank, int elem_size, View* v) {

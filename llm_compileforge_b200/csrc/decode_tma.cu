@@ -682,11 +682,7 @@ int launch_cfg(const DecodeArgs& a, cudaStream_t stream) {
         !make_pool_map(&vmap, a.v, a.v_stride, elem, NSUB, HB, a.n_kv_heads, a.n_pool_blocks))
         return SFB_ERR_UNSUPPORTED;
     auto kern = decode_tma_kernel<KV, NSUB, HB, BPS, STAGES, QBF16>;
-    static bool attr_set = false;  // per instantiation
-    if (!attr_set) {
-        SFB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-        attr_set = true;
-    }
+    if (const int rc = allow_shared_memory_once(reinterpret_cast<const void*>(kern), C::SMEM_BYTES)) return rc;
     dim3 grid((unsigned)a.split.n_chunks, (unsigned)(a.n_kv_heads / HB), (unsigned)a.batch);
     DecodeArgs args = a;
     const int64_t slots = (int64_t)a.batch * a.split.n_chunks;

@@ -39,8 +39,6 @@
 #include <algorithm>
 #include <mutex>
 #include <type_traits>
-#include <utility>
-#include <vector>
 
 #include "sfb_common.cuh"
 
@@ -629,19 +627,6 @@ int launch_fold_norm_weight(const void* g, const void* w, void* out, int64_t K, 
 
 namespace {
 
-// The opt-in to more than 48 KB of dynamic shared memory is per kernel and device: made on a kernel's first launch there,
-// not on every call (the operator is called once per layer and step).
-int allow_shared_memory_once(const void* kernel, int smem, int dev) {
-    static std::mutex mu;
-    static std::vector<std::pair<const void*, int>> done;
-    std::lock_guard<std::mutex> lock(mu);
-    for (const auto& e : done)
-        if (e.first == kernel && e.second == dev) return SFB_OK;
-    SFB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    done.emplace_back(kernel, dev);
-    return SFB_OK;
-}
-
 // How many clusters of two the pair kernel can have resident on this device (0: cannot run); asked once per device.
 template <bool BF16>
 int pair_clusters(int dev, int sms) {
@@ -750,7 +735,7 @@ int launch_norm_matmul(const void* x, int64_t x_stride, const void* wg, int64_t 
     const bool deep64 = plan.k_steps_per_stage == 2;
     const dim3 grid((unsigned)std::min<int64_t>(tiles, tn == 64 && !deep64 ? 2 * sms : sms));
     auto launch = [&](auto kernel, int smem) -> int {
-        const int rc = allow_shared_memory_once(reinterpret_cast<const void*>(kernel), smem, dev);
+        const int rc = allow_shared_memory_once(reinterpret_cast<const void*>(kernel), smem);
         if (rc != SFB_OK) return rc;
         kernel<<<grid, kThreads, smem, stream>>>(amap, bmap, a);
         SFB_CUDA_CHECK(cudaGetLastError());

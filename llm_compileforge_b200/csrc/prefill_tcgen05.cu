@@ -663,12 +663,11 @@ int launch_prefill_tcgen05(const PrefillLaunch& p, cudaStream_t stream) {
     a.part_seq_lens = p.part_seq_lens; a.part_n_chunks = p.part_n_chunks; a.part_chunk_tokens = p.part_chunk_tokens;
     a.part_max_tokens = p.part_max_tokens;
     dim3 grid((unsigned)ceil_div(p.max_q_tokens, 2 * kTileQ), (unsigned)p.n_heads, (unsigned)p.n_requests);
-    static bool attr_set[2] = {false, false};
     if (a.bf16) {
-        if (!attr_set[1]) { SFB_CUDA_CHECK(cudaFuncSetAttribute(prefill_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)); attr_set[1] = true; }
+        if (const int rc = allow_shared_memory_once(reinterpret_cast<const void*>(prefill_tcgen05_kernel<true>), kSmemBytes)) return rc;
         prefill_tcgen05_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(qmap, kmap, vmap, a);
     } else {
-        if (!attr_set[0]) { SFB_CUDA_CHECK(cudaFuncSetAttribute(prefill_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)); attr_set[0] = true; }
+        if (const int rc = allow_shared_memory_once(reinterpret_cast<const void*>(prefill_tcgen05_kernel<false>), kSmemBytes)) return rc;
         prefill_tcgen05_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(qmap, kmap, vmap, a);
     }
     SFB_CUDA_CHECK(cudaGetLastError());

@@ -27,6 +27,11 @@ int fail(int status, const char* fmt, ...);
             return ::sfb::fail(SFB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__)); \
     } while (0)
 
+// Opt-in to more than 48 KB of dynamic shared memory for `kernel` on the calling thread's current device.  The
+// attribute is per kernel AND device, so it is made on a kernel's first launch on each device (not once per
+// process, which breaks the second device of a multi-device host; not on every call either).
+int allow_shared_memory_once(const void* kernel, int smem_bytes);
+
 // A descriptor flattened to rank 4 (leading dimensions of size 1, stride 0).
 struct View {
     char* base = nullptr;  // element 0
