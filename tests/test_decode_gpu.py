@@ -324,3 +324,24 @@ def test_work_list_with_shared_prefix_and_ragged_lengths(cuda):
     assert float(again[100].float().abs().max()) == 0.0
     keep = [i for i in range(n_req) if i != 100]
     assert torch.equal(again[keep], plain[keep])
+
+
+@pytest.mark.gpu
+def test_second_device_of_one_process(cuda):
+    """One process driving two GPUs: per-kernel settings (the shared-memory opt-in, the cluster occupancy query) are made
+    per device, so the kernels launch on cuda:1 after they have run on cuda:0."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from llm_compileforge_b200 import ops, workloads as wl
+    q, k, v, tables, lens = _random_case(77, 5, 32, 8, 128, 200, torch.bfloat16)
+    want = ref.paged_attention_f64(q, k, v, tables, lens)
+    rids = list(tables)
+    x, rw, w, eps = wl.make_norm_matmul_inputs(2100, 264, 2600, torch.bfloat16, seed=3)
+    want_nm = ref.fused_rms_norm_matmul(x, rw, w, eps)
+    for dev in (torch.device("cuda:0"), torch.device("cuda:1")):
+        with torch.cuda.device(dev):
+            out = pkg.paged_attention(q.to(dev), k.to(dev), v.to(dev), tables, lens, chunk_tokens=48)
+            assert_half_close(stack_outputs(out, rids).cpu(), stack_outputs(want, rids), what=f"decode on {dev}")
+            got = ops.fused_rms_norm_matmul(x.to(dev), ops.fold_norm_weight(rw.to(dev), w.to(dev)), eps=eps)
+            from helpers import assert_half_close_ulp
+            assert_half_close_ulp(got.cpu(), want_nm, what=f"norm-matmul on {dev}")
