@@ -9,7 +9,18 @@
 // physical blocks at the head of several tables.  GQA: query head h reads kv
 // head h / (H / Hkv).
 //
-// One thread block = 256 query tokens (two 128-row tiles) of one (request, query head):
+// One thread block = 256 query tokens (two 128-row tiles) of one (request, query head), five warpgroups:
+//   warps 0-15 softmax, eight warps per query tile, two threads per query row (64 key columns each; a warp
+//             can only reach its own 32 tensor-memory lanes, so warps w and w+4 share lanes and split the
+//             columns).  With two warps per SM sub-partition on a tile, one warp's FMA / pack instructions
+//             issue while the other's ex2 occupy the XU pipe.  A thread reads its 64 scores ONCE
+//             (tcgen05.ld into registers; the softmax warpgroups raise their register allowance with
+//             setmaxnreg, the fifth warpgroup lowers its own), swaps half-row maxima with its partner
+//             through shared memory under a 64-thread named barrier, keeps running max / sum in log2
+//             units, writes P as bf16/fp16 over its own S columns in two halves so that the P.V product
+//             starts on the first half while the second is still being computed, rescales O in tensor
+//             memory only when the max grew by more than 2^8 (the stale max stays exact in fp32), adds the
+//             partial sums in the epilogue and writes O / l.
 //   warp 16   TMA producer: both Q tiles once, then per 128-token KV tile sixteen
 //             [16 tokens x 128 B] boxes for K and sixteen for V, two stages each
 //   warp 17   issues tcgen05.mma: S_t = Q_t K^T (128x128x128, both operands K-major
@@ -17,15 +28,8 @@
 //             tensor memory and V as an MN-major shared-memory operand, alternating
 //             between the two query tiles so that one tile's MMAs run while the
 //             other tile's rows are in the softmax warps
-//   warps 0-15 softmax: eight warps per query tile, two threads per query row (64 key
-//             columns each; a warp can only reach its own 32 tensor-memory lanes, so
-//             warps w and w+4 share lanes and split the columns).  With two warps per SM
-//             sub-partition on a tile, one warp's FFMA / pack instructions issue while the
-//             other's ex2 occupy the XU pipe.  tcgen05.ld the S half row, half-row maxima
-//             exchanged through shared memory (mbarrier, bounded wait), running max / sum
-//             in log2 units, P written as bf16/fp16 over the thread's own S columns,
-//             O rescaled in tensor memory only when the max grew by more than 2^8 (the
-//             stale max stays exact in fp32), partial sums added in the epilogue, O / l out
+//   warp 18   clears the V rows past the context in the last KV tile (a pool that was never
+//             zero-filled may hold NaN patterns there, and 0 * NaN would reach O)
 // Tensor memory: per query tile S|P (128 columns) and O (128) = 512 columns in all.
 // Bound: tensor pipe (4*D*Sq*Skv flops per head against ~1.4 PFLOP/s dense).
 
@@ -40,7 +44,7 @@
 // sfb_debug_prefill_trace copies out: per KV tile {wait begin, S ready, first pass done, maxima exchanged, second pass done,
 // P handed over}, and for the MMA warp {tile 0 before / after issue, tile 1 before / after issue}.
 #ifdef SFB_PREFILL_TRACE
-__device__ long long g_prefill_trace[3][64][6];
+__device__ long long g_prefill_trace[6][64][6];
 extern "C" __attribute__((visibility("default"))) int sfb_debug_prefill_trace(long long* out) {
     return (int)cudaMemcpyFromSymbol(out, g_prefill_trace, sizeof(g_prefill_trace));
 }
@@ -57,8 +61,9 @@ constexpr int kTileKV = 128;
 constexpr int kHeadDim = 128;
 constexpr int kSubBytes = kTileKV * 128;     // one [128 rows][128 B] swizzled sub-tile
 constexpr int kTileBytes = 2 * kSubBytes;    // D = 128 16-bit values = two sub-tiles
-constexpr int kThreads = 576;  // 2 x 8 softmax warps (one group per query tile), TMA warp, MMA warp
-constexpr int kTmaWarp = 16, kMmaWarp = 17;
+constexpr int kThreads = 640;  // 2 x 8 softmax warps (one group per query tile) + a warpgroup with the TMA, MMA and fix-up warps
+constexpr int kMmaWarp = 0, kTmaWarp = 1, kTmaWarpV = 2, kFirstSoftmaxWarp = 4;
+constexpr int kPParts = 2;  // P is handed to the MMA thread in this many parts per KV tile (1 or 2)
 constexpr uint32_t kSpin = 1u << 21;  // bounded waits: a stuck pipeline gives up (status bit) within about a second
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;    // log2 units
@@ -119,7 +124,6 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(0), "r"(0), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
         : "memory");
 }
-
 // ---- tensor memory and tcgen05 ------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
@@ -133,18 +137,21 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-// D[tmem] (+)= A[smem desc] . B[smem desc]
-__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[smem desc] . B[smem desc]; descriptors as (low, high) words
+__device__ __forceinline__ void mma_ss(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                       uint32_t accumulate) {
     asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n mov.b64 da, {%1, %2};\n mov.b64 db, {%3, %4};\n setp.ne.b32 p, %6, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // D[tmem] (+)= A[tmem] . B[smem desc]
-__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-        ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        "{\n .reg .pred p;\n .reg .b64 db;\n mov.b64 db, {%2, %3};\n setp.ne.b32 p, %5, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n}\n"
+        ::"r"(d), "r"(a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, float (&v)[32]) {
@@ -162,6 +169,16 @@ __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, float (&v)[32]) 
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     tmem_ld32_issue(taddr, v);
+    tmem_wait_ld();
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
     tmem_wait_ld();
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
@@ -219,26 +236,31 @@ __host__ __device__ constexpr uint32_t instr_desc(bool bf16, bool b_mn_major, in
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// barrier slots
+// barrier slots.  Ring slot j&1 of K holds K(j), of V holds V(j); the MMA step j needs V(j) and K(j+1), so one
+// "full" / "empty" pair per step parity covers V slot j&1 together with K slot (j+1)&1.
 enum {
-    B_Q_FULL = 0,
-    B_K_FULL = 1,    // +stage
-    B_K_EMPTY = 3,   // +stage
-    B_V_FULL = 5,    // +stage
-    B_V_EMPTY = 7,   // +stage
-    B_S_FULL = 9,    // +query tile
-    B_P_FULL = 11,   // +query tile
-    B_PV_DONE = 13,  // +query tile
-    B_X_FULL = 15,   // +query tile: half-row maxima / sums exchanged between the two threads of a row
-    B_COUNT = 17
+    B_Q_FULL = 0,    // both Q tiles and K(0)
+    B_KV_FULL = 1,   // +step parity: V(j) and K(j+1) have landed (one arrival per producer warp)
+    B_KV_EMPTY = 3,  // +step parity: every MMA that read them is complete
+    B_S_FULL = 5,    // +query tile
+    B_P_FULL = 7,    // +2 * query tile + half: keys 0-31 of both column halves, then keys 32-63
+    B_PV_DONE = 11,  // +query tile: the tile's last P.V product is complete
+    B_V_FIXED = 13,  // the last KV tile's V rows past the context are cleared
+    B_COUNT = 14
 };
-constexpr int kXchFloats = 2 * 2 * kTileQ;  // [query tile][column half][row]
+constexpr int kXchFloats = 2 * 2 * 2 * kTileQ;  // [step parity][query tile][column half][row]
 constexpr int kSmemBytes = 6 * kTileBytes + B_COUNT * 8 + 16 + kXchFloats * 4 + 1024;  // 2 Q tiles, 2 K stages, 2 V stages
 
 // Tensor-memory columns of query tile t: S (fp32, 128 columns) at t*256, with P (16-bit pairs,
 // 64 columns) written over its first half once the row has been read; O (fp32) at t*256 + 128.
 constexpr uint32_t kColTile = 256;
 constexpr uint32_t kColO = 128;
+
+// Register allowances after the role split (five warpgroups of 128 threads; the kernel is compiled for
+// 65536 / 640 -> 96 registers per thread): 4 * 128 * kSoftmaxRegs + 128 * kOtherRegs must not exceed the 640 * 96
+// registers the block owns from launch, so that the raise never waits for registers from outside the block.
+constexpr int kSoftmaxRegs = 104;
+constexpr int kOtherRegs = 64;
 
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -259,7 +281,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef SFB_PREFILL_TRACE
-    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 8 || warp == kMmaWarp);
+    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == kFirstSoftmaxWarp || warp == kFirstSoftmaxWarp + 8 || warp < kFirstSoftmaxWarp);
 #endif
     const int q0 = qb * 2 * kTileQ;                       // first query row of the block
     int rows_t[2], tiles_t[2];
@@ -273,6 +295,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     const int used_blocks = (ctx + 15) >> 4;
     const int group = a.n_heads / a.n_kv_heads;
     const int kvh = head / group;
+    // the KV tile that holds the last cached token may end inside a 16-token block: its V rows past the context are cleared
+    const int fix_tile = (ctx - 1) / kTileKV;
+    const bool fix_v = (ctx & 15) != 0 && fix_tile < n_tiles;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -286,15 +311,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     if (threadIdx.x == 0) {
         mbar_init(bar(B_Q_FULL), 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(bar(B_K_FULL + s), 1);
-            mbar_init(bar(B_K_EMPTY + s), 1);
-            mbar_init(bar(B_V_FULL + s), 1);
-            mbar_init(bar(B_V_EMPTY + s), 1);
+            mbar_init(bar(B_KV_FULL + s), 2);
+            mbar_init(bar(B_KV_EMPTY + s), 1);
             mbar_init(bar(B_S_FULL + s), 1);
-            mbar_init(bar(B_P_FULL + s), 8);
-            mbar_init(bar(B_X_FULL + s), 8);
+            mbar_init(bar(B_P_FULL + 2 * s), 8);
+            mbar_init(bar(B_P_FULL + 2 * s + 1), 8);
             mbar_init(bar(B_PV_DONE + s), 1);
         }
+        mbar_init(bar(B_V_FIXED), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -305,249 +329,267 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     const uint32_t tmem = *tmem_slot;
     bool timed_out = false;
 
-    if (warp == kTmaWarp) {
-        // ============================ TMA producer ============================
-        if (lane == 0) {
-            mbar_expect_tx(bar(B_Q_FULL), 2 * kTileBytes);
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {  // rows past the packed batch read as zeros
-                tma_load_4d(q_s + t * kTileBytes, &qmap, bar(B_Q_FULL), q_begin + q0 + t * kTileQ, 0, head);
-                tma_load_4d(q_s + t * kTileBytes + kSubBytes, &qmap, bar(B_Q_FULL), q_begin + q0 + t * kTileQ, 1, head);
-            }
-        }
-        const int blk = (lane & 15) >> 1, sub = lane & 1;
-        const int32_t* table = a.tables + (int64_t)req * a.table_stride;
-        auto lookup = [&](int tile) -> int {
-            const int e = tile * 8 + blk;
-            if (tile >= n_tiles || e >= used_blocks) return (int)a.n_pool_blocks;  // out of range -> zero fill
-            const int64_t p = table[e];
-            if (p < 0 || p >= a.n_pool_blocks) {
-                if (a.status) atomicOr(a.status, SFB_STATUS_BAD_BLOCK_ID);
-                return (int)a.n_pool_blocks;
-            }
-            return (int)p;
-        };
-        int phys = lookup(0);
-        for (int j = 0; j < n_tiles; ++j) {
-            const int s = j & 1;
-            const uint32_t par = ((j >> 1) & 1) ^ 1;
-            const int next_phys = lookup(j + 1);  // in flight while this tile's copies are issued
-            const uint32_t dst_off = sub * kSubBytes + blk * 2048;
-            if (!mbar_wait(bar(B_K_EMPTY + s), par)) { timed_out = true; break; }
-            if (lane == 0) mbar_expect_tx(bar(B_K_FULL + s), kTileBytes);
-            __syncwarp();
-            if (lane < 16) tma_load_5d(k_s + s * kTileBytes + dst_off, &kmap, bar(B_K_FULL + s), sub, kvh, phys);
-            if (!mbar_wait(bar(B_V_EMPTY + s), par)) { timed_out = true; break; }
-            if (lane == 16) mbar_expect_tx(bar(B_V_FULL + s), kTileBytes);
-            __syncwarp();
-            if (lane >= 16) tma_load_5d(v_s + s * kTileBytes + dst_off, &vmap, bar(B_V_FULL + s), sub, kvh, phys);
-            phys = next_phys;
-        }
-    } else if (warp == kMmaWarp) {
-        // ============================ MMA issuer ==============================
-        // Issue order PV0(j), QK0(j+1), PV1(j), QK1(j+1): while one query tile's rows are in the
-        // softmax warps, the tensor pipe works on the other tile.
-        if (lane == 0) {
-            constexpr uint32_t idesc_qk = instr_desc(BF16, false, kTileQ, kTileKV);
-            constexpr uint32_t idesc_pv = instr_desc(BF16, true, kTileQ, kHeadDim);
-            auto issue_qk = [&](int t, int j) {  // K stage j&1 is known to be full
-                const int s = j & 1;
-                tc_fence_after();
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {  // 16 head-dim values per instruction
-                    const uint32_t off = (ks >> 2) * kSubBytes + (ks & 3) * 32;
-                    mma_ss(tmem + t * kColTile, smem_desc(q_s + t * kTileBytes + off, 16, 1024),
-                           smem_desc(k_s + s * kTileBytes + off, 16, 1024), idesc_qk, ks > 0);
+    if (warp < kFirstSoftmaxWarp) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
+        if (warp == kTmaWarp || warp == kTmaWarpV) {
+            // ============================ TMA producers ===========================
+            // Warp 1 feeds Q and K, warp 2 feeds V: the issue of one step's boxes (a few tens of clocks per box) is
+            // shared between two warps.  For MMA step j the K warp loads K(j+1), the V warp V(j), both behind the
+            // step's "empty" barrier and onto its "full" barrier.
+            const bool is_v = warp == kTmaWarpV;
+            // K: lane = (block of the tile, 64-value half), a [16 tokens x 128 B] box each, laid out [half][128 tokens][128 B].
+            // V: lane = block of the tile, one [2 halves x 16 tokens x 128 B] box each, laid out [block][half][16 tokens][128 B].
+            const int blk = is_v ? (lane & 7) : ((lane & 15) >> 1), sub = lane & 1;
+            const bool active = is_v ? lane < 8 : lane < 16;
+            const uint32_t dst_off = is_v ? blk * 4096 : sub * kSubBytes + blk * 2048;
+            const int32_t* table = a.tables + (int64_t)req * a.table_stride;
+            auto lookup = [&](int tile) -> int {
+                const int e = tile * 8 + blk;
+                if (tile >= n_tiles || e >= used_blocks) return (int)a.n_pool_blocks;  // out of range -> zero fill
+                const int64_t p = table[e];
+                if (p < 0 || p >= a.n_pool_blocks) {
+                    if (a.status && !is_v) atomicOr(a.status, SFB_STATUS_BAD_BLOCK_ID);
+                    return (int)a.n_pool_blocks;
                 }
-                tc_commit(bar(B_S_FULL + t));
+                return (int)p;
             };
-            auto issue_pv = [&](int t, int j) -> bool {  // V stage j&1 is known to be full
-                const int s = j & 1;
-                if (!mbar_wait(bar(B_P_FULL + t), j & 1)) return false;
-                tc_fence_after();
+            const int first = is_v ? 0 : 1;  // KV tile of step 0
+            int phys = lookup(first), phys1 = lookup(first + 1);
+            if (!is_v) {
+                const int phys0 = lookup(0);
+                if (lane == 0) {
+                    mbar_expect_tx(bar(B_Q_FULL), 3 * kTileBytes);
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks)  // 16 KV tokens per instruction
-                    mma_ts(tmem + t * kColTile + kColO, tmem + t * kColTile + (ks >> 2) * 64 + (ks & 3) * 8,
-                           smem_desc(v_s + s * kTileBytes + ks * 2048, kSubBytes, 1024), idesc_pv, (j > 0 || ks > 0));
-                tc_commit(bar(B_PV_DONE + t));
-                return true;
-            };
-            bool ok = mbar_wait(bar(B_Q_FULL), 0) && mbar_wait(bar(B_K_FULL), 0);
-            if (ok) {
-                if (tiles_t[0] > 0) issue_qk(0, 0);
-                if (tiles_t[1] > 0) issue_qk(1, 0);
-                tc_commit(bar(B_K_EMPTY));
-            }
-            for (int j = 0; ok && j < n_tiles; ++j) {
-                const int s = j & 1;
-                const bool more = j + 1 < n_tiles;
-                ok = mbar_wait(bar(B_V_FULL + s), (j >> 1) & 1);
-                if (ok && more) ok = mbar_wait(bar(B_K_FULL + (s ^ 1)), ((j + 1) >> 1) & 1);
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    SFB_TR(2, j, 2 * t);
-                    if (ok && j < tiles_t[t]) ok = issue_pv(t, j);
-                    if (ok && j + 1 < tiles_t[t]) issue_qk(t, j + 1);
-                    SFB_TR(2, j, 2 * t + 1);
+                    for (int t = 0; t < 2; ++t) {  // rows past the packed batch read as zeros
+                        tma_load_4d(q_s + t * kTileBytes, &qmap, bar(B_Q_FULL), q_begin + q0 + t * kTileQ, 0, head);
+                        tma_load_4d(q_s + t * kTileBytes + kSubBytes, &qmap, bar(B_Q_FULL), q_begin + q0 + t * kTileQ, 1, head);
+                    }
                 }
+                __syncwarp();
+                if (active) tma_load_5d(k_s + dst_off, &kmap, bar(B_Q_FULL), sub, kvh, phys0);  // K(0) into slot 0
+            }
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j & 1;
+                // "empty" phases: parity 0 completes at the end of step 0 (pair 0) resp. once Q.K(0)^T is done (pair 1)
+                const uint32_t par = s ? ((j >> 1) & 1) : (((j >> 1) & 1) ^ 1);
+                const int phys2 = lookup(first + j + 2);  // table entries are fetched two tiles ahead of their use
+                SFB_TR(4 + (int)is_v, j, 0);
+                if (!mbar_wait(bar(B_KV_EMPTY + s), par)) { timed_out = true; break; }
+                SFB_TR(4 + (int)is_v, j, 1);
+                if (is_v) {
+                    if (lane == 0) mbar_expect_tx(bar(B_KV_FULL + s), kTileBytes);
+                    __syncwarp();
+                    if (active) tma_load_5d(v_s + s * kTileBytes + dst_off, &vmap, bar(B_KV_FULL + s), 0, kvh, phys);
+                } else if (j + 1 < n_tiles) {
+                    if (lane == 0) mbar_expect_tx(bar(B_KV_FULL + s), kTileBytes);
+                    __syncwarp();
+                    if (active) tma_load_5d(k_s + (s ^ 1) * kTileBytes + dst_off, &kmap, bar(B_KV_FULL + s), sub, kvh, phys);
+                } else if (lane == 0) {
+                    mbar_arrive(bar(B_KV_FULL + s));  // no further K tile: the step's barrier still counts two arrivals
+                }
+                SFB_TR(4 + (int)is_v, j, 2);
+                phys = phys1;
+                phys1 = phys2;
+            }
+            if (is_v && fix_v && !timed_out) {
+                // Clear the V rows past the context in the last KV tile.  A 128-byte row of a swizzled sub-tile is permuted
+                // only inside itself, so whole rows can be cleared in place.
+                const int s = fix_tile & 1;
+                if (mbar_wait(bar(B_KV_FULL + s), (fix_tile >> 1) & 1)) {
+                    const int fblk = ((ctx - 1) >> 4) & 7, first = ctx & 15;
+                    uint8_t* v_tile = base_ptr + 4 * kTileBytes + s * kTileBytes + fblk * 4096;
+                    for (int i = lane; i < (16 - first) * 16; i += 32) {  // (row, 64-value half, 16-byte piece)
+                        const int r = first + (i >> 4), h = (i >> 3) & 1, piece = i & 7;
+                        *reinterpret_cast<uint4*>(v_tile + h * 2048 + r * 128 + piece * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(B_V_FIXED));
+                } else {
+                    timed_out = true;
+                }
+            }
+        } else if (warp == kMmaWarp) {
+            // ============================ MMA issuer ==============================
+            // One thread issues every MMA, in the order PV0(j), QK0(j+1), PV1(j), QK1(j+1): while one query tile's rows
+            // are in the softmax warps, the tensor pipe works on the other tile (two issuing threads, one per tile, were
+            // measured: the tiles then fall into step and the pipe idles while both are in their softmax).  An issue
+            // returns when the pipe accepts the MMA, so whatever else this thread runs is time with nothing queued: per
+            // step it waits once for the operands and once or twice per tile for P, and commits the S tiles and the
+            // operand slots; descriptors are a constant plus a slot / K-step offset in the low word.
+            if (lane == 0) {
+                constexpr uint32_t idesc_qk = instr_desc(BF16, false, kTileQ, kTileKV);
+                constexpr uint32_t idesc_pv = instr_desc(BF16, true, kTileQ, kHeadDim);
+                const uint32_t hi = (uint32_t)(smem_desc(0, 0, 1024) >> 32);
+                const uint32_t q_lo = (uint32_t)smem_desc(q_s, 16, 0);
+                const uint32_t k_lo = (uint32_t)smem_desc(k_s, 16, 0), v_lo = (uint32_t)smem_desc(v_s, 2048, 0);
+                auto issue_qk = [&](int t, int slot) {  // 16 head-dim values per instruction
+                    const uint32_t qb_lo = q_lo + t * (kTileBytes >> 4), kb = k_lo + slot * (kTileBytes >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint32_t off = ((ks >> 2) * kSubBytes + (ks & 3) * 32) >> 4;
+                        mma_ss(tmem + t * kColTile, qb_lo + off, hi, kb + off, hi, idesc_qk, ks > 0);
+                    }
+                    tc_commit(bar(B_S_FULL + t));
+                };
+                auto issue_pv = [&](int t, int j) -> bool {
+                    const uint32_t vb = v_lo + (j & 1) * (kTileBytes >> 4), s_tm = tmem + t * kColTile;
+#pragma unroll
+                    for (int part = 0; part < kPParts; ++part) {  // with two parts: keys {0-31, 64-95}, then {32-63, 96-127}
+                        if (!mbar_wait(bar(B_P_FULL + 2 * t + part), j & 1)) return false;
+                        SFB_TR(2 + t, j, 1 + part);
+                        tc_fence_after();
+#pragma unroll
+                        for (int i = 0; i < 8 / kPParts; ++i) {  // 16 KV tokens per instruction
+                            const int ks = kPParts == 2 ? (i >> 1) * 4 + part * 2 + (i & 1) : i;
+                            mma_ts(s_tm + kColO, s_tm + (ks >> 2) * 64 + (ks & 3) * 8, vb + ks * (4096 >> 4), hi, idesc_pv,
+                                   (j > 0 || part > 0 || i > 0));
+                        }
+                    }
+                    if (j + 1 == tiles_t[t]) tc_commit(bar(B_PV_DONE + t));  // the tile's last product: the epilogue waits for it
+                    return true;
+                };
+                bool ok = mbar_wait(bar(B_Q_FULL), 0);
                 if (ok) {
-                    tc_commit(bar(B_V_EMPTY + s));
-                    if (more) tc_commit(bar(B_K_EMPTY + (s ^ 1)));
+                    tc_fence_after();
+                    if (tiles_t[0] > 0) issue_qk(0, 0);
+                    if (tiles_t[1] > 0) issue_qk(1, 0);
+                    tc_commit(bar(B_KV_EMPTY + 1));  // K slot 0 may take K(2) once these are done
                 }
+                for (int j = 0; ok && j < n_tiles; ++j) {
+                    SFB_TR(2, j, 0);
+                    ok = mbar_wait(bar(B_KV_FULL + (j & 1)), (j >> 1) & 1);
+                    if (ok && fix_v && j == fix_tile) ok = mbar_wait(bar(B_V_FIXED), 0);
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        if (ok && j < tiles_t[t]) ok = issue_pv(t, j);
+                        SFB_TR(2 + t, j, 3);
+                        if (ok && j + 1 < tiles_t[t]) issue_qk(t, (j + 1) & 1);
+                        SFB_TR(2 + t, j, 4);
+                    }
+                    if (ok && j + 2 < n_tiles) tc_commit(bar(B_KV_EMPTY + (j & 1)));  // the producers wait for it before step j + 2
+                }
+                timed_out = !ok;
             }
-            timed_out = !ok;
         }
-    } else if (warp < 16) {
+    } else {
         // ======================= softmax / correction / epilogue ==============
         // Eight warps per query tile.  Warp w owns tensor-memory lanes 32*(w&3).. (its hardware window) and key
-        // columns 64*((w>>2)&1).. of its tile: two threads share a query row, exchange their half-row maxima
-        // through shared memory (an mbarrier with bounded waits orders it) and keep partial sums that are only
+        // columns 64*((w>>2)&1).. of its tile: two threads share a query row, swap their half-row maxima through
+        // shared memory (64-thread named barrier, slots alternate by step) and keep partial sums that are only
         // added up in the epilogue.
-        const int my_t = warp >> 3;          // query tile of this 8-warp group
-        const int hf = (warp >> 2) & 1;
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
+        const int my_t = (warp - kFirstSoftmaxWarp) >> 3;  // query tile of this 8-warp group
+        const int hf = ((warp - kFirstSoftmaxWarp) >> 2) & 1;
         const int row = threadIdx.x & 127;
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t pair_bar = 1 + my_t * 4 + (warp & 3);  // named barrier of the two warps that share a lane window
         const float sl2 = a.scale * kLog2e;
         float m_used = -INFINITY, l = 0.f;
-        const int pos = (row < rows_t[my_t] && a.causal) ? ctx - n_q + q0 + my_t * kTileQ + row : ctx - 1;  // padding rows see everything
+        const int my_rows = my_t ? rows_t[1] : rows_t[0], my_tiles = my_t ? tiles_t[1] : tiles_t[0];
+        const int pos = (row < my_rows && a.causal) ? ctx - n_q + q0 + my_t * kTileQ + row : ctx - 1;  // padding rows see everything
+        const uint32_t s_addr = lane_addr + my_t * kColTile + hf * 64;  // this thread's 64 score columns
+        const uint32_t o_addr = lane_addr + my_t * kColTile + kColO + hf * 64;
 
-        auto exchange = [&](int t, uint32_t parity, float mine, float& other) -> bool {
-            xch[(t * 2 + hf) * kTileQ + row] = mine;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(B_X_FULL + t));
-            if (!mbar_wait(bar(B_X_FULL + t), parity)) return false;
-            other = xch[(t * 2 + (hf ^ 1)) * kTileQ + row];
-            return true;
+        // both warps of a pair run the same waits in the same order, so they reach this barrier together or not at all
+        auto exchange = [&](int step, float mine) -> float {
+            float* slot = xch + ((step & 1) * 2 + my_t) * 2 * kTileQ;
+            slot[hf * kTileQ + row] = mine;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            return slot[(hf ^ 1) * kTileQ + row];
         };
 
-        auto softmax_tile = [&](int t, int j) -> bool {
-            const uint32_t s_addr = lane_addr + t * kColTile + hf * 64;  // this thread's 64 score columns
-            SFB_TR(t, j, 0);
-            if (!mbar_wait(bar(B_S_FULL + t), j & 1)) return false;
+        auto softmax_tile = [&](int j) -> bool {
+            SFB_TR(my_t, j, 0);
+            if (!mbar_wait(bar(B_S_FULL + my_t), j & 1)) return false;
             tc_fence_after();
-            SFB_TR(t, j, 1);
+            SFB_TR(my_t, j, 1);
             const int kv0 = j * kTileKV + hf * 64;
             // tcgen05.ld / st are warp-collective: the masked / unmasked choice must be uniform across the warp
             const bool full = __all_sync(0xffffffffu, kv0 + 63 <= pos);
+            float s[64];
+            tmem_ld32_issue(s_addr, *reinterpret_cast<float(*)[32]>(s));
+            tmem_ld32_issue(s_addr + 32, *reinterpret_cast<float(*)[32]>(s + 32));
+            tmem_wait_ld();
             float mx0 = -INFINITY, mx1 = -INFINITY;
             if (full) {
-#pragma unroll 1
-                for (int ch = 0; ch < 2; ++ch) {
-                    float v[32];
-                    tmem_ld32(s_addr + ch * 32, v);
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        mx0 = max3(mx0, v[i], v[i + 1]);
-                        mx1 = max3(mx1, v[i + 2], v[i + 3]);
-                    }
+                for (int i = 0; i < 64; i += 4) {
+                    mx0 = max3(mx0, s[i], s[i + 1]);
+                    mx1 = max3(mx1, s[i + 2], s[i + 3]);
                 }
             } else {
-#pragma unroll 1
-                for (int ch = 0; ch < 2; ++ch) {
-                    float v[32];
-                    tmem_ld32(s_addr + ch * 32, v);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (kv0 + ch * 32 + i <= pos) mx0 = fmaxf(mx0, v[i]);
+                for (int i = 0; i < 64; ++i) {
+                    if (kv0 + i > pos) s[i] = -INFINITY;  // exp2(-inf) = 0 below
+                    mx0 = fmaxf(mx0, s[i]);
                 }
             }
-            SFB_TR(t, j, 2);
-            float mx = fmaxf(mx0, mx1), other;
-            if (!exchange(t, j & 1, mx, other)) return false;
-            mx = fmaxf(mx, other);
-            SFB_TR(t, j, 3);
+            SFB_TR(my_t, j, 2);
+            const float mx = fmaxf(fmaxf(mx0, mx1), exchange(j, fmaxf(mx0, mx1)));
+            SFB_TR(my_t, j, 3);
             const float m_new = fmaxf(m_used, mx * sl2);
             if (j == 0) {
                 m_used = m_new;
             } else {
                 const bool need = m_new > m_used + kRescaleThreshold;  // the same for both threads of a row
                 if (__any_sync(0xffffffffu, need)) {
-                    // O is only touched between PV products: wait for the previous one
-                    if (!mbar_wait(bar(B_PV_DONE + t), (j - 1) & 1)) return false;
-                    tc_fence_after();
+                    // O is only touched between P.V products.  The previous one is complete: this tile's S was committed by
+                    // the same thread after it, and a commit covers everything that thread issued before.
                     const float f = need ? fast_exp2(m_used - m_new) : 1.f;
                     l *= f;
                     if (need) m_used = m_new;
 #pragma unroll 1
-                    for (int ch = 0; ch < 2; ++ch) {
-                        float o[32];
-                        tmem_ld32(lane_addr + t * kColTile + kColO + hf * 64 + ch * 32, o);
+                    for (int ch = 0; ch < 4; ++ch) {
+                        float o[16];
+                        tmem_ld16(o_addr + ch * 16, o);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] *= f;
-                        tmem_st32(lane_addr + t * kColTile + kColO + hf * 64 + ch * 32, o);
+                        for (int i = 0; i < 16; ++i) o[i] *= f;
+                        tmem_st16(o_addr + ch * 16, *reinterpret_cast<uint32_t(*)[16]>(o));
                     }
                     tmem_wait_st();
                 }
             }
-            // P (16-bit pairs, 32 columns) goes over the first half of this thread's own score columns
-            const float neg_m = -m_used;
-            float l0 = 0.f, l1 = 0.f;
-            if (full) {
-                // packed fp32 pairs: one FFMA2 scales and shifts two scores, one FADD2 adds two probabilities
-                const float2 sl2v = make_float2(sl2, sl2), nmv = make_float2(neg_m, neg_m);
-                float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-#pragma unroll 1
-                for (int ch = 0; ch < 2; ++ch) {
-                    float v[32];
-                    tmem_ld32(s_addr + ch * 32, v);
-                    uint32_t pk[16];
+            // P (16-bit pairs, 32 columns) goes over the first half of this thread's own score columns, in two halves
+            // packed fp32 pairs: one FFMA2 scales and shifts two scores, one FADD2 adds two probabilities
+            const float2 sl2v = make_float2(sl2, sl2), nmv = make_float2(-m_used, -m_used);
+            float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float2 x = __ffma2_rn(make_float2(v[2 * i], v[2 * i + 1]), sl2v, nmv);
-                        const float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-                        if (i & 1) acc1 = __fadd2_rn(acc1, pr);
-                        else acc0 = __fadd2_rn(acc0, pr);
-                        pk[i] = pack2<BF16>(pr.x, pr.y);
-                    }
-                    tmem_st16(s_addr + ch * 16, pk);  // P chunk ch lands on score columns that chunk <= ch has already read
-                }
-                l0 = acc0.x + acc1.x;
-                l1 = acc0.y + acc1.y;
-            } else {
-#pragma unroll 1
-                for (int ch = 0; ch < 2; ++ch) {
-                    float v[32];
-                    tmem_ld32(s_addr + ch * 32, v);
-                    uint32_t pk[16];
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t pk[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int c = kv0 + ch * 32 + 2 * i;
-                        const float p0 = c <= pos ? fast_exp2(fmaf(v[2 * i], sl2, neg_m)) : 0.f;
-                        const float p1 = c + 1 <= pos ? fast_exp2(fmaf(v[2 * i + 1], sl2, neg_m)) : 0.f;
-                        l0 += p0;
-                        l1 += p1;
-                        pk[i] = pack2<BF16>(p0, p1);
-                    }
-                    tmem_st16(s_addr + ch * 16, pk);
+                for (int i = 0; i < 16; ++i) {
+                    const float2 x = __ffma2_rn(make_float2(s[32 * ch + 2 * i], s[32 * ch + 2 * i + 1]), sl2v, nmv);
+                    const float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                    if (i & 1) acc1 = __fadd2_rn(acc1, pr);
+                    else acc0 = __fadd2_rn(acc0, pr);
+                    pk[i] = pack2<BF16>(pr.x, pr.y);
                 }
+                tmem_st16(s_addr + ch * 16, pk);
+                if (kPParts == 2 || ch == 1) {
+                    tmem_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(B_P_FULL + 2 * my_t + (kPParts == 2 ? ch : 0)));
+                }
+                SFB_TR(my_t, j, 4 + ch);
             }
-            l += l0 + l1;
-            SFB_TR(t, j, 4);
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(B_P_FULL + t));
-            SFB_TR(t, j, 5);
+            l += (acc0.x + acc1.x) + (acc0.y + acc1.y);
             return true;
         };
 
         bool ok = true;
-        for (int j = 0; j < tiles_t[my_t] && ok; ++j) ok = softmax_tile(my_t, j);
+        for (int j = 0; j < my_tiles && ok; ++j) ok = softmax_tile(j);
         // ---- epilogue: O / l, each thread its 64 output columns
-        for (int t = my_t; t == my_t; ++t) {
-            const int my_tiles = tiles_t[t];
-            if (!ok || my_tiles <= 0) continue;
-            if (!mbar_wait(bar(B_PV_DONE + t), (my_tiles - 1) & 1)) { ok = false; continue; }
+        if (ok && my_tiles > 0) ok = mbar_wait(bar(B_PV_DONE + my_t), 0);
+        if (ok && my_tiles > 0) {
             tc_fence_after();
-            float l_other;
-            if (!exchange(t, my_tiles & 1, l, l_other)) { ok = false; continue; }
-            const float l_row = l + l_other;
-            const bool row_valid = row < rows_t[t];
-            const uint32_t o_addr = lane_addr + t * kColTile + kColO + hf * 64;
+            const float l_row = l + exchange(my_tiles, l);
+            const bool row_valid = row < my_rows;
             if (a.part_o) {
                 // shared-prefix mode: this row is decode request `qrow`; its partial goes to the chunk slot right after
                 // the request's own chunks, in the decode kernel's format (unnormalised O, max in log2 units, sum)
-                const int qrow = q0 + t * kTileQ + row;
+                const int qrow = q0 + my_t * kTileQ + row;
                 int64_t pslot = 0;
                 if (row_valid) {
                     int len = a.part_seq_lens[qrow];
@@ -572,7 +614,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                 }
             } else {
                 const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-                uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(q_begin + q0 + t * kTileQ + row) * a.out_stride[0] +
+                uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(q_begin + q0 + my_t * kTileQ + row) * a.out_stride[0] +
                                 (int64_t)head * a.out_stride[1] + hf * 64;
 #pragma unroll 1
                 for (int ch = 0; ch < 2; ++ch) {
@@ -650,7 +692,7 @@ int launch_prefill_tcgen05(const PrefillLaunch& p, cudaStream_t stream) {
         const int64_t* st = which ? p.v_stride : p.k_stride;
         cuuint64_t dims[5] = {128, 16, 2, (cuuint64_t)p.n_kv_heads, (cuuint64_t)p.n_pool_blocks};
         cuuint64_t strides[4] = {(cuuint64_t)st[1] * 2, 128, (cuuint64_t)st[2] * 2, (cuuint64_t)st[0] * 2};
-        cuuint32_t box[5] = {128, 16, 1, 1, 1};
+        cuuint32_t box[5] = {128, 16, which ? 2u : 1u, 1, 1};  // V: both 64-value halves of a block in one box
         if (!encode(which ? &vmap : &kmap, which ? p.v : p.k, 5, dims, strides, box)) return SFB_ERR_UNSUPPORTED;
     }
     PrefillArgs a{};
