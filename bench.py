@@ -48,7 +48,7 @@ METRIC = "paged_fp8_decode_tokens_per_s"
 UNIT = "tokens/s"
 NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes of the decode kernel, from the ncu capture of a
-# 128-request case of the same shape (profiles/decode_tma_fp8_c5.md: 1.259 GB + 0.077 GB for 1.253 GB algorithmic);
+# 128-request case of the same shape (1.259 GB read + 0.077 GB written for 1.253 GB algorithmic);
 # the full launch is beyond the capture size rule, and its traffic grows with the KV tokens read.
 TRAFFIC_PER_ALGORITHMIC_BYTE = 1.066
 

@@ -99,7 +99,8 @@ typedef enum {
 enum {
     SFB_STATUS_BAD_BLOCK_ID = 1, /* block-table entry outside [0, NB): block skipped */
     SFB_STATUS_EMPTY_REQUEST = 2, /* seq_len <= 0: output row zero-filled */
-    SFB_STATUS_WAIT_TIMEOUT = 4  /* a bounded device-side wait gave up */
+    SFB_STATUS_WAIT_TIMEOUT = 4, /* a bounded device-side wait gave up */
+    SFB_STATUS_UNSORTED_POSITIONS = 8 /* sfb_attention_dense: a positional mask whose positions decrease somewhere */
 };
 
 SFB_API int sfb_abi_version(void);
@@ -240,6 +241,61 @@ SFB_API int sfb_prefill_paged(const SFBTensor* q, const SFBTensor* k_cache, cons
                               SFBTensor* out, int dtype, float scale, int causal, int64_t max_q_tokens,
                               void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Same, with the visible length of every query row given explicitly instead of the
+ * causal rule: row t of the packed batch attends to positions 0 .. row_limits[t]-1 of
+ * its request (clamped to ctx_len; a row whose limit is <= 0 gets a zero output).
+ * This is how the reference backend's positional attention mask is served
+ * (python_runtime/hal/pytorch_backend/_ops_attention.py:33-43: key j is visible to
+ * query i iff pos[i] >= pos[j], which for non-decreasing positions is a prefix of
+ * keys) and the top-left aligned causal mask of the Rust runtime's dense attention
+ * (runtime/src/engine/kernels.rs:246-252: row i sees keys 0..i).
+ *   row_limits  [T] int32, contiguous */
+SFB_API int sfb_prefill_paged_rows(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
+                                   const SFBTensor* block_tables, const SFBTensor* cu_q, const SFBTensor* ctx_lens,
+                                   const SFBTensor* row_limits, SFBTensor* out, int dtype, float scale,
+                                   int64_t max_q_tokens, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* ── Dense attention ──────────────────────────────────────────────────────────
+ * softmax(q k^T scale + mask) v over dense [B, H, S, D] operands (k, v: [B, Hkv, Skv, D],
+ * H a multiple of Hkv); any batch / head / token strides that are multiples of 16 bytes,
+ * D contiguous, so a position-major [B, S, H, D] buffer is passed as a permuted view.
+ * Replaces the reference backend's scaled_dot_product_attention
+ * (python_runtime/hal/pytorch_backend/_ops_attention.py:13-53) and the Rust runtime's
+ * dense attention (runtime/src/engine/kernels.rs:97-302: fp32, head-major operands,
+ * q pre-scaled -> pass scale = 1; decode = SFB_MASK_NONE, prefill = SFB_MASK_CAUSAL_TOP_LEFT).
+ * Masks are prefixes of keys per query row:
+ *   SFB_MASK_NONE                 every key
+ *   SFB_MASK_CAUSAL_TOP_LEFT      row i sees keys 0..i (torch's is_causal, kernels.rs:246-252)
+ *   SFB_MASK_CAUSAL_BOTTOM_RIGHT  row i sees keys 0..Skv-Sq+i (a chunk at the end of its context)
+ *   SFB_MASK_POSITIONS            `positions` [B or 1, S] f32, Sq = Skv = S: key j is visible to
+ *                                 query i iff positions[i] >= positions[j], the reference's
+ *                                 positional mask (_ops_attention.py:33-43).  The positions must
+ *                                 not decrease along S; otherwise SFB_STATUS_UNSORTED_POSITIONS is
+ *                                 set in the status word and the output is unspecified.
+ * scale <= 0 means 1/sqrt(D).  `workspace` (sfb_attention_dense_workspace_bytes) holds the
+ * status word (first 4 bytes, sfb_read_status) and the repacked operands: the attention
+ * itself runs on the chunked-prefill kernels over a private pool of 16-token blocks. */
+enum { SFB_MASK_NONE = 0, SFB_MASK_CAUSAL_TOP_LEFT = 1, SFB_MASK_CAUSAL_BOTTOM_RIGHT = 2, SFB_MASK_POSITIONS = 3 };
+SFB_API int64_t sfb_attention_dense_workspace_bytes(int64_t batch, int64_t n_heads, int64_t n_kv_heads, int64_t q_len, int64_t kv_len,
+                                                    int64_t head_dim, int dtype);
+SFB_API int sfb_attention_dense(const SFBTensor* q, const SFBTensor* k, const SFBTensor* v, const SFBTensor* positions, SFBTensor* out,
+                                int dtype, float scale, int mask_mode, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* ── Dense read of the paged pool ─────────────────────────────────────────────
+ * The `cache_read` operator the dialect reserves beside paged_attention / cache_write
+ * (sf-dialect/include/Sf/HALOps.td:190-194) and CacheManager.read_paged
+ * (python_runtime/engine/cache_manager.py:173-197): out[r, t] = the pool row of token t of
+ * request r through its block table, zero for t >= seq_lens[r] (with seq_lens[r] = the table's
+ * capacity this is read_paged exactly).  Call once for K and once for V.
+ *   cache        [NB, bs, Hkv, D] cache_dtype;  scale [NB, Hkv] f32 with an e4m3 pool, else NULL
+ *   block_tables [R, max_blocks] int32;  seq_lens [R] int32
+ *   out          [R, max_seq_len, Hkv, D] out_dtype, contiguous (f32 / bf16 / f16; for an e4m3
+ *                pool value = code * scale, the reference's dequantize_block,
+ *                compiler/quantize/fp8_kv_cache.py:95-105)
+ * `status` (may be NULL): device int32 that receives SFB_STATUS_BAD_BLOCK_ID. */
+SFB_API int sfb_cache_read(const SFBTensor* cache, const SFBTensor* scale, const SFBTensor* block_tables, const SFBTensor* seq_lens,
+                           SFBTensor* out, int cache_dtype, int out_dtype, void* status, void* stream);
+
 /* ── Decode with a shared (radix) prefix ────────────────────────────────────
  * Same result as sfb_paged_attention_decode for requests whose first
  * `shared_prefix_blocks` table entries are the same physical blocks in EVERY
@@ -302,7 +358,12 @@ SFB_API int sfb_rms_norm(const SFBTensor* x, const SFBTensor* residual, const SF
  * of GPU p's copy (peer_out[rank] the local one; all copies have out_all's layout).
  * The buffers must be mapped for peer access by the caller (CUDA IPC / symmetric
  * memory).  Follow it on the same stream with sfb_peer_signal_wait: after that the
- * local copy is complete.  Only the shapes of the TMA decode kernel are supported. */
+ * local copy is complete.  The signal says "arrived", nothing says "consumed": a
+ * GPU that has passed its wait may start the next step's stores while a slower peer
+ * still reads this one.  Alternate between TWO output sets by step parity and queue
+ * the reader of a step on the same stream before the next decode; the stores of step
+ * n + 2 then cannot start before every peer has signalled step n + 1, i.e. after
+ * its reader of step n.  Only the shapes of the TMA decode kernel are supported. */
 SFB_API int sfb_paged_attention_decode_gather(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
                                               const SFBTensor* k_scale, const SFBTensor* v_scale,
                                               const SFBTensor* block_tables, const SFBTensor* seq_lens,
@@ -404,6 +465,43 @@ SFB_API int sfb_fused_rms_norm_matmul(const SFBTensor* x, const SFBTensor* folde
  * `allocated` is NULL (the convention has no error channel). */
 SFB_API void _mlir_ciface_sfb_rms_norm_f32(void* sret, const SFBMemRef2* x, const SFBMemRef1* w);
 SFB_API void serveforge_free(void* ptr);
+
+/* The attention operators in the same convention, under the operator names the dialect
+ * reserves (sf-dialect/include/Sf/HALOps.td:184-211: paged_attention, cache_read,
+ * cache_write, quantize, dequantize) plus the dense attention of
+ * python_runtime/hal/pytorch_backend/_ops_attention.py:13-53 and
+ * runtime/src/engine/kernels.rs:97-302; one symbol per element type (_f32, _bf16).
+ * Operands beyond the dialect's own lists (sequence lengths, the pools, the per-request
+ * token ranges) are what the engine holds as state around those operators.  Outputs are
+ * contiguous, consecutive descriptors in `sret`; int32 index operands.
+ *   paged_attention(q [B,H,D], key_cache, value_cache [NB,bs,Hkv,D], block_table [B,max_blocks],
+ *                   seq_lens [B]) -> [B,H,D]
+ *   cache_write(key, value [T,Hkv,D], cu_tokens [B+1], start_pos [B], block_table, key_cache,
+ *               value_cache): writes the pools, no result (`sret` untouched)
+ *   cache_read(block_table [R,max_blocks], seq_lens [R], key_cache, value_cache)
+ *                   -> key, value [R, max_blocks*bs, Hkv, D]
+ *   quantize(x [NB,bs,Hkv,D]) -> codes [NB,bs,Hkv,D] u8 (e4m3), scales [NB,Hkv] f32
+ *   dequantize(codes, scales) -> [NB,bs,Hkv,D]
+ *   scaled_dot_product_attention / causal_attention(q [B,H,Sq,D], k, v [B,Hkv,Skv,D]) -> [B,H,Sq,D]
+ *                   (scale 1/sqrt(D); causal = row i sees keys 0..i) */
+#define SFB_DECLARE_CIFACE(sfx)                                                                                                    \
+    SFB_API void _mlir_ciface_sfb_paged_attention_##sfx(void* sret, const SFBMemRef3* q, const SFBMemRef4* key_cache,              \
+                                                        const SFBMemRef4* value_cache, const SFBMemRef2* block_table,             \
+                                                        const SFBMemRef1* seq_lens);                                              \
+    SFB_API void _mlir_ciface_sfb_cache_write_##sfx(void* sret, const SFBMemRef3* key, const SFBMemRef3* value,                    \
+                                                    const SFBMemRef1* cu_tokens, const SFBMemRef1* start_pos,                     \
+                                                    const SFBMemRef2* block_table, const SFBMemRef4* key_cache,                   \
+                                                    const SFBMemRef4* value_cache);                                               \
+    SFB_API void _mlir_ciface_sfb_cache_read_##sfx(void* sret, const SFBMemRef2* block_table, const SFBMemRef1* seq_lens,          \
+                                                   const SFBMemRef4* key_cache, const SFBMemRef4* value_cache);                   \
+    SFB_API void _mlir_ciface_sfb_quantize_##sfx(void* sret, const SFBMemRef4* x);                                                 \
+    SFB_API void _mlir_ciface_sfb_dequantize_##sfx(void* sret, const SFBMemRef4* codes, const SFBMemRef2* scales);                 \
+    SFB_API void _mlir_ciface_sfb_scaled_dot_product_attention_##sfx(void* sret, const SFBMemRef4* q, const SFBMemRef4* k,         \
+                                                                     const SFBMemRef4* v);                                        \
+    SFB_API void _mlir_ciface_sfb_causal_attention_##sfx(void* sret, const SFBMemRef4* q, const SFBMemRef4* k, const SFBMemRef4* v);
+SFB_DECLARE_CIFACE(f32)
+SFB_DECLARE_CIFACE(bf16)
+#undef SFB_DECLARE_CIFACE
 
 #ifdef __cplusplus
 }

@@ -34,7 +34,8 @@ SFB_F32, SFB_BF16, SFB_F16, SFB_F8E4M3 = 0, 1, 2, 3
 
 SFB_QUANT_PER_TENSOR, SFB_QUANT_PER_BLOCK_HEAD = 0, 1
 
-SFB_STATUS_BAD_BLOCK_ID, SFB_STATUS_EMPTY_REQUEST, SFB_STATUS_WAIT_TIMEOUT = 1, 2, 4
+SFB_STATUS_BAD_BLOCK_ID, SFB_STATUS_EMPTY_REQUEST, SFB_STATUS_WAIT_TIMEOUT, SFB_STATUS_UNSORTED_POSITIONS = 1, 2, 4, 8
+SFB_MASK_NONE, SFB_MASK_CAUSAL_TOP_LEFT, SFB_MASK_CAUSAL_BOTTOM_RIGHT, SFB_MASK_POSITIONS = 0, 1, 2, 3
 
 _DTYPES = {
     torch.float32: SFB_F32,
@@ -143,6 +144,14 @@ def _optional(lib: ctypes.CDLL) -> None:
         lib.sfb_prefill_paged.argtypes = [_T] * 7 + [c_int, c_float, c_int, c_int64, c_void_p, c_int64, c_void_p]
         lib.sfb_prefill_workspace_bytes.restype = c_int64
         lib.sfb_prefill_workspace_bytes.argtypes = [c_int64]
+    lib.sfb_prefill_paged_rows.restype = c_int
+    lib.sfb_prefill_paged_rows.argtypes = [_T] * 8 + [c_int, c_float, c_int64, c_void_p, c_int64, c_void_p]
+    lib.sfb_attention_dense_workspace_bytes.restype = c_int64
+    lib.sfb_attention_dense_workspace_bytes.argtypes = [c_int64] * 6 + [c_int]
+    lib.sfb_attention_dense.restype = c_int
+    lib.sfb_attention_dense.argtypes = [_T] * 5 + [c_int, c_float, c_int, c_void_p, c_int64, c_void_p]
+    lib.sfb_cache_read.restype = c_int
+    lib.sfb_cache_read.argtypes = [_T] * 5 + [c_int, c_int, c_void_p, c_void_p]
 
 
 def _block_manager_protos(lib: ctypes.CDLL) -> None:

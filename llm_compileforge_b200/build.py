@@ -42,8 +42,8 @@ def _headers_mtime() -> float:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile and link.  ``SFB_NVCC_FLAGS`` adds compiler flags (e.g. ``-DSFB_PREFILL_TRACE`` for the prefill kernel's stage
-    stamps) and ``SFB_LIB_OUT`` writes such a variant to another path (objects beside it), leaving the regular library alone."""
+    """Compile and link.  ``SFB_NVCC_FLAGS`` adds compiler flags and ``SFB_LIB_OUT`` writes such a variant to another path
+    (objects beside it), leaving the regular library alone."""
     global OBJ, LIB
     extra = os.environ.get("SFB_NVCC_FLAGS", "").split()
     if os.environ.get("SFB_LIB_OUT"):

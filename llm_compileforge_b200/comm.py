@@ -117,10 +117,17 @@ def kv_head_shard(t: torch.Tensor, rank: int, world_size: int, dim: int) -> torc
 class PeerGather:
     """Output buffers for head-partitioned decode whose all-gather happens inside the decode kernel.
 
-    Every rank allocates the whole ``[batch, heads_per_rank * world, head_dim]`` output plus a ``uint32 [world]`` flag
-    array in peer-mapped (symmetric) memory; rank g's decode stores its heads into every rank's copy
-    (:func:`ops.paged_attention_decode_gather`) and :meth:`signal_wait` closes the step.  One node, at most 8 ranks.
+    Every rank allocates TWO copies of the whole ``[batch, heads_per_rank * world, head_dim]`` output plus a
+    ``uint32 [world]`` flag array in peer-mapped (symmetric) memory; rank g's decode stores its heads into every rank's
+    copy (:func:`ops.paged_attention_decode_gather`) and :meth:`signal_wait` closes the step.  One node, at most 8 ranks.
     The NCCL path (:meth:`TorchDistCommunicator.gather_heads`) stays the portable fallback for callers that cannot map peers.
+
+    Why two copies: there is a "data has arrived" flag per step and no "data has been consumed" flag.  Once rank g has
+    passed its wait for step n, its decode of step n + 1 starts storing into the peers' buffers while a slower peer p may
+    still be reading step n.  Steps therefore alternate between the two copies (step parity): g's stores of step n + 2
+    reuse step n's copy, and g only gets there after p's flag for step n + 1, which p's stream sets after everything it
+    queued for step n.  The rule this leaves to the caller: whatever reads the tensor :meth:`decode` returns must be
+    queued on the same stream before the next :meth:`decode`, and the tensor is only valid until the decode after next.
     """
 
     def __init__(self, batch: int, heads_per_rank: int, head_dim: int, dtype: torch.dtype, device: torch.device,
@@ -132,24 +139,35 @@ class PeerGather:
         if self.world > 8:
             raise ValueError("PeerGather covers one node: at most 8 ranks")
         self.device = device
-        self.out = symm_mem.empty((batch, heads_per_rank * self.world, head_dim), dtype=dtype, device=device)
-        self._out_hdl = symm_mem.rendezvous(self.out, grp)
+        self.outs, self._out_hdls, self.out_ptrs_by_parity = [], [], []
+        for _ in range(2):
+            buf = symm_mem.empty((batch, heads_per_rank * self.world, head_dim), dtype=dtype, device=device)
+            hdl = symm_mem.rendezvous(buf, grp)
+            self.outs.append(buf)
+            self._out_hdls.append(hdl)
+            self.out_ptrs_by_parity.append([int(p) for p in hdl.buffer_ptrs])
         self.flags = symm_mem.empty((self.world,), dtype=torch.int32, device=device)
         self.flags.zero_()
         self._flag_hdl = symm_mem.rendezvous(self.flags, grp)
-        self.out_ptrs = [int(p) for p in self._out_hdl.buffer_ptrs]
         self.flag_ptrs = [int(p) for p in self._flag_hdl.buffer_ptrs]
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.step = 0
         torch.cuda.synchronize(device)
         dist.barrier(grp)  # every rank's flags are zero before anybody signals
 
+    @property
+    def out(self) -> torch.Tensor:
+        """The copy the last completed :meth:`decode` filled."""
+        return self.outs[step_buffer(self.step)]
+
     def decode(self, q, k_cache, v_cache, block_tables, seq_lens, **kw) -> torch.Tensor:
         from . import ops
 
-        ops.paged_attention_decode_gather(q, k_cache, v_cache, block_tables, seq_lens, self.out, self.out_ptrs, self.rank, **kw)
+        which = step_buffer(self.step + 1)
+        ops.paged_attention_decode_gather(q, k_cache, v_cache, block_tables, seq_lens, self.outs[which],
+                                          self.out_ptrs_by_parity[which], self.rank, **kw)
         self.signal_wait()
-        return self.out
+        return self.outs[which]
 
     def signal_wait(self) -> None:
         from . import ops
@@ -160,3 +178,8 @@ class PeerGather:
     def timed_out(self) -> bool:
         """True when a wait gave up (synchronises)."""
         return bool(int(self.status.item()) != 0)
+
+
+def step_buffer(step: int) -> int:
+    """Which of the two output copies step ``step`` (1, 2, ...) of a :class:`PeerGather` uses."""
+    return step & 1

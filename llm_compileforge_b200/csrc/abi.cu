@@ -235,7 +235,8 @@ int64_t sfb_prefill_workspace_bytes(int64_t total_q_tokens) {
 
 static int prefill_impl(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache, const SFBTensor* block_tables,
                         const SFBTensor* cu_q, const SFBTensor* ctx_lens, SFBTensor* out, int dtype, float scale, int causal,
-                        int64_t max_q_tokens, void* workspace, int64_t workspace_bytes, void* stream, bool clear_status) {
+                        int64_t max_q_tokens, void* workspace, int64_t workspace_bytes, void* stream, bool clear_status,
+                        const SFBTensor* row_limits = nullptr) {
     const int e = dtype_size(dtype);
     if (!e || dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "prefill: dtype %d", dtype);
     View vq, vk, vv, vt, vc, vl, vo;
@@ -256,6 +257,11 @@ static int prefill_impl(const SFBTensor* q, const SFBTensor* k_cache, const SFBT
     if (vo.size[1] != T || vo.size[2] != H || vo.size[3] != D) return fail(SFB_ERR_INVALID_ARG, "prefill: out shape differs from q");
     if (Hkv <= 0 || H % Hkv) return fail(SFB_ERR_INVALID_ARG, "prefill: query heads not a multiple of kv heads");
     if ((D * e) % 16 || !aligned16(vk, 0) || !aligned16(vv, 0)) return fail(SFB_ERR_UNSUPPORTED, "prefill: pools must be 16-byte aligned");
+    View vr;
+    if (row_limits) {
+        if ((rc = make_view(row_limits, "row_limits", 1, 1, 4, &vr))) return rc;
+        if (vr.size[3] != T || (T > 1 && vr.stride[3] != 1)) return fail(SFB_ERR_INVALID_ARG, "prefill: row_limits must be a contiguous int32 [T]");
+    }
     if (T == 0 || R == 0 || max_q_tokens <= 0) return SFB_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (workspace && workspace_bytes < kWorkspaceHeader) workspace = nullptr;
@@ -263,6 +269,7 @@ static int prefill_impl(const SFBTensor* q, const SFBTensor* k_cache, const SFBT
     const float sc = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
 
     PrefillLaunch p{};
+    p.row_limits = row_limits ? reinterpret_cast<const int32_t*>(vr.base) : nullptr;
     p.q = vq.base; p.k = vk.base; p.v = vv.base; p.out = vo.base;
     p.cu_q = reinterpret_cast<const int32_t*>(vc.base);
     p.ctx_lens = reinterpret_cast<const int32_t*>(vl.base);
@@ -285,7 +292,7 @@ static int prefill_impl(const SFBTensor* q, const SFBTensor* k_cache, const SFBT
                     (long long)(workspace ? workspace_bytes : 0));
     int32_t* rows = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + kWorkspaceHeader);
     int32_t* lens = rows + T;
-    if ((rc = launch_prefill_expand(p.cu_q, p.ctx_lens, (int)R, T, p.max_blocks, (int)bs, causal != 0, rows, lens, st))) return rc;
+    if ((rc = launch_prefill_expand(p.cu_q, p.ctx_lens, p.row_limits, (int)R, T, p.max_blocks, (int)bs, causal != 0, rows, lens, st))) return rc;
     DecodeArgs a{};
     a.q = vq.base; a.k = vk.base; a.v = vv.base; a.out = vo.base;
     a.tables = p.tables; a.table_rows = rows; a.n_table_rows = R; a.seq_lens = lens;
@@ -503,6 +510,14 @@ int sfb_prefill_paged(const SFBTensor* q, const SFBTensor* k_cache, const SFBTen
                       int causal, int64_t max_q_tokens, void* workspace, int64_t workspace_bytes, void* stream) {
     return prefill_impl(q, k_cache, v_cache, block_tables, cu_q, ctx_lens, out, dtype, scale, causal, max_q_tokens, workspace, workspace_bytes,
                         stream, true);
+}
+
+int sfb_prefill_paged_rows(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache, const SFBTensor* block_tables,
+                           const SFBTensor* cu_q, const SFBTensor* ctx_lens, const SFBTensor* row_limits, SFBTensor* out, int dtype,
+                           float scale, int64_t max_q_tokens, void* workspace, int64_t workspace_bytes, void* stream) {
+    if (!row_limits) return fail(SFB_ERR_INVALID_ARG, "prefill_rows: row_limits is NULL");
+    return prefill_impl(q, k_cache, v_cache, block_tables, cu_q, ctx_lens, out, dtype, scale, 0, max_q_tokens, workspace, workspace_bytes,
+                        stream, true, row_limits);
 }
 
 static SFBTensor device_tensor(void* base, int elem, int rank, const int64_t* sizes) {

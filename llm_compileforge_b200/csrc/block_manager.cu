@@ -145,6 +145,7 @@ void sfb_bm_free(SFBBlockManager* bm, const char* rid) {
     auto it = bm->requests.find(rid);
     if (it == bm->requests.end()) return;
     for (int32_t bid : it->second.table) {
+        if (bid < 0 || bid >= bm->num_blocks) continue;  // ids assign_cached_blocks took from outside the pool: skipped like :184
         int32_t& rc = bm->ref_count[(size_t)bid];
         rc = rc > 0 ? rc - 1 : 0;
         if (rc == 0) bm->free_blocks.push_back(bid);
@@ -214,7 +215,13 @@ int64_t sfb_bm_share_prefix(SFBBlockManager* bm, const char* src, const char* ds
     int rc = take_row(bm, r);
     if (rc) return rc;
     r.table.assign(it->second.table.begin(), it->second.table.begin() + n);
-    for (int32_t bid : r.table) bm->ref_count[(size_t)bid] += 1;
+    for (int32_t bid : r.table) {
+        if (bid < 0 || bid >= bm->num_blocks) {  // :292-294: the counts raised so far stay raised, the destination gets no table
+            if (r.row >= 0) bm->free_rows.push_back(r.row);
+            return fail(SFB_ERR_INVALID_ARG, "block %d not found in share_prefix", (int)bid);
+        }
+        bm->ref_count[(size_t)bid] += 1;
+    }
     bm->requests.emplace(dst, std::move(r));
     return n;
 }

@@ -39,26 +39,28 @@ __global__ void decode_combine_kernel(DecodeArgs a) {
 }
 
 // Packed prefill tokens -> one decode row each: token i of request r sits at position
-// ctx_len - n_q + i and attends to position + 1 tokens through request r's table row.
-__global__ void prefill_expand_kernel(const int32_t* cu_q, const int32_t* ctx_lens, int n_requests, int max_tokens_cap, int causal,
-                                      int32_t* rows_out, int32_t* lens_out) {
+// ctx_len - n_q + i and attends to position + 1 tokens through request r's table row
+// (or to its own `row_limits` entry of tokens, when those are given).
+__global__ void prefill_expand_kernel(const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* row_limits, int n_requests,
+                                      int max_tokens_cap, int causal, int32_t* rows_out, int32_t* lens_out) {
     const int req = blockIdx.y;
     const int begin = cu_q[req], n_q = cu_q[req + 1] - begin;
     int ctx = ctx_lens[req];
     if (ctx > max_tokens_cap) ctx = max_tokens_cap;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_q; i += gridDim.x * blockDim.x) {
         rows_out[begin + i] = req;
-        lens_out[begin + i] = causal ? ctx - n_q + i + 1 : ctx;  // <= 0 (inconsistent request) is flagged by the decode kernel
+        // <= 0 (inconsistent request, or a row that may see nothing) is flagged by the decode kernel and gives a zero row
+        lens_out[begin + i] = row_limits ? min(row_limits[begin + i], ctx) : causal ? ctx - n_q + i + 1 : ctx;
     }
 }
 
 }  // namespace
 
-int launch_prefill_expand(const int32_t* cu_q, const int32_t* ctx_lens, int n_requests, int64_t total_q, int max_blocks,
-                          int block_size, int causal, int32_t* rows_out, int32_t* lens_out, cudaStream_t stream) {
+int launch_prefill_expand(const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* row_limits, int n_requests, int64_t total_q,
+                          int max_blocks, int block_size, int causal, int32_t* rows_out, int32_t* lens_out, cudaStream_t stream) {
     (void)total_q;
     dim3 grid(8, (unsigned)n_requests);
-    prefill_expand_kernel<<<grid, 256, 0, stream>>>(cu_q, ctx_lens, n_requests, max_blocks * block_size, causal, rows_out, lens_out);
+    prefill_expand_kernel<<<grid, 256, 0, stream>>>(cu_q, ctx_lens, row_limits, n_requests, max_blocks * block_size, causal, rows_out, lens_out);
     SFB_CUDA_CHECK(cudaGetLastError());
     return SFB_OK;
 }

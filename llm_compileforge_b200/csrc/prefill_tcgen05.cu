@@ -36,22 +36,9 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "sfb_common.cuh"
-
-// Optional stage stamps (-DSFB_PREFILL_TRACE): thread block (0,0,0) records clock64 at its barrier waits - the first softmax
-// warp of each query tile (rows 0 / 1 of the table) and the MMA warp (row 2) - into a device array that
-// sfb_debug_prefill_trace copies out: per KV tile {wait begin, S ready, first pass done, maxima exchanged, second pass done,
-// P handed over}, and for the MMA warp {tile 0 before / after issue, tile 1 before / after issue}.
-#ifdef SFB_PREFILL_TRACE
-__device__ long long g_prefill_trace[6][64][6];
-extern "C" __attribute__((visibility("default"))) int sfb_debug_prefill_trace(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_prefill_trace, sizeof(g_prefill_trace));
-}
-#define SFB_TR(w, j, k) do { if (trace_on && (j) < 64) g_prefill_trace[w][j][k] = clock64(); } while (0)
-#else
-#define SFB_TR(w, j, k) do { } while (0)
-#endif
 
 namespace sfb {
 namespace {
@@ -63,7 +50,7 @@ constexpr int kSubBytes = kTileKV * 128;     // one [128 rows][128 B] swizzled s
 constexpr int kTileBytes = 2 * kSubBytes;    // D = 128 16-bit values = two sub-tiles
 constexpr int kThreads = 640;  // 2 x 8 softmax warps (one group per query tile) + a warpgroup with the TMA, MMA and fix-up warps
 constexpr int kMmaWarp = 0, kTmaWarp = 1, kTmaWarpV = 2, kFirstSoftmaxWarp = 4;
-constexpr int kPParts = 2;  // P is handed to the MMA thread in this many parts per KV tile (1 or 2)
+constexpr int kPParts = 1;  // P is handed to the MMA thread in this many parts per KV tile (1 or 2)
 constexpr uint32_t kSpin = 1u << 21;  // bounded waits: a stuck pipeline gives up (status bit) within about a second
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;    // log2 units
@@ -73,6 +60,7 @@ struct PrefillArgs {
     void* out;
     const int32_t* cu_q;      // [R+1] packed query offsets
     const int32_t* ctx_lens;  // [R]   tokens cached after this chunk was written
+    const int32_t* row_limits;  // optional [T]: query row r sees positions 0 .. row_limits[r] - 1 (instead of `causal`)
     const int32_t* tables;
     int64_t table_stride;
     int max_blocks;
@@ -257,8 +245,9 @@ constexpr uint32_t kColTile = 256;
 constexpr uint32_t kColO = 128;
 
 // Register allowances after the role split (five warpgroups of 128 threads; the kernel is compiled for
-// 65536 / 640 -> 96 registers per thread): 4 * 128 * kSoftmaxRegs + 128 * kOtherRegs must not exceed the 640 * 96
-// registers the block owns from launch, so that the raise never waits for registers from outside the block.
+// 65536 / 640 -> 96 registers per thread, and shared memory admits one thread block per SM, so the block may
+// grow into the rest of the register file): 4 * 128 * kSoftmaxRegs + 128 * kOtherRegs <= 65536, and the first
+// warpgroup lowers its allowance before the others can finish raising theirs.
 constexpr int kSoftmaxRegs = 104;
 constexpr int kOtherRegs = 64;
 
@@ -275,20 +264,37 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     if (qb < 0) return;
     int ctx = a.cu_q ? a.ctx_lens[req] : a.fixed_ctx;
     if (ctx > a.max_blocks * 16) ctx = a.max_blocks * 16;
-    if ((a.causal && ctx < n_q) || n_q <= 0 || ctx <= 0) {  // inconsistent request: flag it, write nothing
+    if ((a.causal && !a.row_limits && ctx < n_q) || n_q <= 0 || ctx <= 0) {  // inconsistent request: flag it, write nothing
         if (a.status && threadIdx.x == 0) atomicOr(a.status, SFB_STATUS_EMPTY_REQUEST);
         return;
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef SFB_PREFILL_TRACE
-    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == kFirstSoftmaxWarp || warp == kFirstSoftmaxWarp + 8 || warp < kFirstSoftmaxWarp);
-#endif
     const int q0 = qb * 2 * kTileQ;                       // first query row of the block
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + 6 * kTileBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
+    int* limit_max = reinterpret_cast<int*>(tmem_slot + 1);  // [2]: with row limits, the largest limit of each query tile
+    float* xch = reinterpret_cast<float*>(tmem_slot + 4);
+    int my_limit = 0;
+    if (a.row_limits) {  // one row per thread of the first eight warps; the tiles' maxima go through shared memory
+        if (threadIdx.x < 2 * kTileQ) {
+            if (q0 + (int)threadIdx.x < n_q) my_limit = min(max(a.row_limits[q_begin + q0 + threadIdx.x], 0), ctx);
+            const int wmax = __reduce_max_sync(0xffffffffu, my_limit);
+            if (lane == 0) reinterpret_cast<int*>(xch)[warp] = wmax;
+        }
+        __syncthreads();
+        if (threadIdx.x < 2) {
+            const int* w = reinterpret_cast<const int*>(xch) + 4 * threadIdx.x;
+            limit_max[threadIdx.x] = max(max(w[0], w[1]), max(w[2], w[3]));
+        }
+        __syncthreads();
+    }
     int rows_t[2], tiles_t[2];
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
         rows_t[t] = max(0, min(kTileQ, n_q - q0 - t * kTileQ));
-        const int last_pos = a.causal ? ctx - n_q + q0 + t * kTileQ + rows_t[t] - 1 : ctx - 1;
+        const int last_pos = a.row_limits ? max(limit_max[t], 1) - 1 : a.causal ? ctx - n_q + q0 + t * kTileQ + rows_t[t] - 1 : ctx - 1;
         tiles_t[t] = rows_t[t] > 0 ? last_pos / kTileKV + 1 : 0;
     }
     const int n_tiles = max(tiles_t[0], tiles_t[1]);
@@ -299,12 +305,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     const int fix_tile = (ctx - 1) / kTileKV;
     const bool fix_v = (ctx & 15) != 0 && fix_tile < n_tiles;
 
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t q_s = base, k_s = base + 2 * kTileBytes, v_s = base + 4 * kTileBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + 6 * kTileBytes);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
-    float* xch = reinterpret_cast<float*>(tmem_slot + 4);
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
@@ -331,27 +332,28 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
 
     if (warp < kFirstSoftmaxWarp) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
-        if (warp == kTmaWarp || warp == kTmaWarpV) {
+        auto produce = [&](auto is_v_tag) {
+            constexpr bool is_v = decltype(is_v_tag)::value;
             // ============================ TMA producers ===========================
             // Warp 1 feeds Q and K, warp 2 feeds V: the issue of one step's boxes (a few tens of clocks per box) is
             // shared between two warps.  For MMA step j the K warp loads K(j+1), the V warp V(j), both behind the
             // step's "empty" barrier and onto its "full" barrier.
-            const bool is_v = warp == kTmaWarpV;
             // K: lane = (block of the tile, 64-value half), a [16 tokens x 128 B] box each, laid out [half][128 tokens][128 B].
             // V: lane = block of the tile, one [2 halves x 16 tokens x 128 B] box each, laid out [block][half][16 tokens][128 B].
             const int blk = is_v ? (lane & 7) : ((lane & 15) >> 1), sub = lane & 1;
             const bool active = is_v ? lane < 8 : lane < 16;
             const uint32_t dst_off = is_v ? blk * 4096 : sub * kSubBytes + blk * 2048;
-            const int32_t* table = a.tables + (int64_t)req * a.table_stride;
+            const int32_t* table = a.tables + (int64_t)req * a.table_stride + blk;
+            const int pool = (int)a.n_pool_blocks;  // the launcher keeps the pool below 2^31 blocks
+            const int limit = min(n_tiles * 8, used_blocks) - blk;
             auto lookup = [&](int tile) -> int {
-                const int e = tile * 8 + blk;
-                if (tile >= n_tiles || e >= used_blocks) return (int)a.n_pool_blocks;  // out of range -> zero fill
-                const int64_t p = table[e];
-                if (p < 0 || p >= a.n_pool_blocks) {
+                if (tile * 8 >= limit) return pool;  // past the context -> an out-of-range block index, TMA fills zeros
+                const int p = table[tile * 8];
+                if ((unsigned)p >= (unsigned)pool) {
                     if (a.status && !is_v) atomicOr(a.status, SFB_STATUS_BAD_BLOCK_ID);
-                    return (int)a.n_pool_blocks;
+                    return pool;
                 }
-                return (int)p;
+                return p;
             };
             const int first = is_v ? 0 : 1;  // KV tile of step 0
             int phys = lookup(first), phys1 = lookup(first + 1);
@@ -373,9 +375,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                 // "empty" phases: parity 0 completes at the end of step 0 (pair 0) resp. once Q.K(0)^T is done (pair 1)
                 const uint32_t par = s ? ((j >> 1) & 1) : (((j >> 1) & 1) ^ 1);
                 const int phys2 = lookup(first + j + 2);  // table entries are fetched two tiles ahead of their use
-                SFB_TR(4 + (int)is_v, j, 0);
                 if (!mbar_wait(bar(B_KV_EMPTY + s), par)) { timed_out = true; break; }
-                SFB_TR(4 + (int)is_v, j, 1);
                 if (is_v) {
                     if (lane == 0) mbar_expect_tx(bar(B_KV_FULL + s), kTileBytes);
                     __syncwarp();
@@ -387,7 +387,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                 } else if (lane == 0) {
                     mbar_arrive(bar(B_KV_FULL + s));  // no further K tile: the step's barrier still counts two arrivals
                 }
-                SFB_TR(4 + (int)is_v, j, 2);
                 phys = phys1;
                 phys1 = phys2;
             }
@@ -409,6 +408,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     timed_out = true;
                 }
             }
+        };
+        if (warp == kTmaWarp) {
+            produce(std::false_type{});
+        } else if (warp == kTmaWarpV) {
+            produce(std::true_type{});
         } else if (warp == kMmaWarp) {
             // ============================ MMA issuer ==============================
             // One thread issues every MMA, in the order PV0(j), QK0(j+1), PV1(j), QK1(j+1): while one query tile's rows
@@ -437,7 +441,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
 #pragma unroll
                     for (int part = 0; part < kPParts; ++part) {  // with two parts: keys {0-31, 64-95}, then {32-63, 96-127}
                         if (!mbar_wait(bar(B_P_FULL + 2 * t + part), j & 1)) return false;
-                        SFB_TR(2 + t, j, 1 + part);
                         tc_fence_after();
 #pragma unroll
                         for (int i = 0; i < 8 / kPParts; ++i) {  // 16 KV tokens per instruction
@@ -457,15 +460,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     tc_commit(bar(B_KV_EMPTY + 1));  // K slot 0 may take K(2) once these are done
                 }
                 for (int j = 0; ok && j < n_tiles; ++j) {
-                    SFB_TR(2, j, 0);
                     ok = mbar_wait(bar(B_KV_FULL + (j & 1)), (j >> 1) & 1);
                     if (ok && fix_v && j == fix_tile) ok = mbar_wait(bar(B_V_FIXED), 0);
 #pragma unroll
                     for (int t = 0; t < 2; ++t) {
                         if (ok && j < tiles_t[t]) ok = issue_pv(t, j);
-                        SFB_TR(2 + t, j, 3);
                         if (ok && j + 1 < tiles_t[t]) issue_qk(t, (j + 1) & 1);
-                        SFB_TR(2 + t, j, 4);
                     }
                     if (ok && j + 2 < n_tiles) tc_commit(bar(B_KV_EMPTY + (j & 1)));  // the producers wait for it before step j + 2
                 }
@@ -487,7 +487,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         const float sl2 = a.scale * kLog2e;
         float m_used = -INFINITY, l = 0.f;
         const int my_rows = my_t ? rows_t[1] : rows_t[0], my_tiles = my_t ? tiles_t[1] : tiles_t[0];
-        const int pos = (row < my_rows && a.causal) ? ctx - n_q + q0 + my_t * kTileQ + row : ctx - 1;  // padding rows see everything
+        // last visible position of this thread's row; padding rows see everything
+        int pos = (row < my_rows && a.causal) ? ctx - n_q + q0 + my_t * kTileQ + row : ctx - 1;
+        if (a.row_limits && row < my_rows) pos = min(max(a.row_limits[q_begin + q0 + my_t * kTileQ + row], 0), ctx) - 1;
         const uint32_t s_addr = lane_addr + my_t * kColTile + hf * 64;  // this thread's 64 score columns
         const uint32_t o_addr = lane_addr + my_t * kColTile + kColO + hf * 64;
 
@@ -500,10 +502,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         };
 
         auto softmax_tile = [&](int j) -> bool {
-            SFB_TR(my_t, j, 0);
             if (!mbar_wait(bar(B_S_FULL + my_t), j & 1)) return false;
             tc_fence_after();
-            SFB_TR(my_t, j, 1);
             const int kv0 = j * kTileKV + hf * 64;
             // tcgen05.ld / st are warp-collective: the masked / unmasked choice must be uniform across the warp
             const bool full = __all_sync(0xffffffffu, kv0 + 63 <= pos);
@@ -525,9 +525,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     mx0 = fmaxf(mx0, s[i]);
                 }
             }
-            SFB_TR(my_t, j, 2);
             const float mx = fmaxf(fmaxf(mx0, mx1), exchange(j, fmaxf(mx0, mx1)));
-            SFB_TR(my_t, j, 3);
             const float m_new = fmaxf(m_used, mx * sl2);
             if (j == 0) {
                 m_used = m_new;
@@ -552,7 +550,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             }
             // P (16-bit pairs, 32 columns) goes over the first half of this thread's own score columns, in two halves
             // packed fp32 pairs: one FFMA2 scales and shifts two scores, one FADD2 adds two probabilities
-            const float2 sl2v = make_float2(sl2, sl2), nmv = make_float2(-m_used, -m_used);
+            const float neg_m = m_used == -INFINITY ? 0.f : -m_used;  // a row that sees nothing yet: every score is -inf, P = 0
+            const float2 sl2v = make_float2(sl2, sl2), nmv = make_float2(neg_m, neg_m);
             float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
             for (int ch = 0; ch < 2; ++ch) {
@@ -572,7 +571,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar(B_P_FULL + 2 * my_t + (kPParts == 2 ? ch : 0)));
                 }
-                SFB_TR(my_t, j, 4 + ch);
             }
             l += (acc0.x + acc1.x) + (acc0.y + acc1.y);
             return true;
@@ -679,7 +677,7 @@ bool encode(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims
 // Returns SFB_ERR_UNSUPPORTED when the shape is outside this kernel (the caller then takes the generic route).
 int launch_prefill_tcgen05(const PrefillLaunch& p, cudaStream_t stream) {
     if (p.head_dim != kHeadDim || p.block_size != 16 || (p.dtype != SFB_BF16 && p.dtype != SFB_F16)) return SFB_ERR_UNSUPPORTED;
-    if (p.n_heads % p.n_kv_heads || p.n_requests > 65535 || p.n_heads > 65535) return SFB_ERR_UNSUPPORTED;
+    if (p.n_heads % p.n_kv_heads || p.n_requests > 65535 || p.n_heads > 65535 || p.n_pool_blocks >= (1ll << 31) - 1) return SFB_ERR_UNSUPPORTED;
     if (!p.part_o && (reinterpret_cast<uintptr_t>(p.out) % 16 || p.out_stride[0] % 8 || p.out_stride[1] % 8)) return SFB_ERR_UNSUPPORTED;
     CUtensorMap qmap, kmap, vmap;
     {
@@ -696,7 +694,7 @@ int launch_prefill_tcgen05(const PrefillLaunch& p, cudaStream_t stream) {
         if (!encode(which ? &vmap : &kmap, which ? p.v : p.k, 5, dims, strides, box)) return SFB_ERR_UNSUPPORTED;
     }
     PrefillArgs a{};
-    a.q = p.q; a.out = p.out; a.cu_q = p.cu_q; a.ctx_lens = p.ctx_lens; a.tables = p.tables;
+    a.q = p.q; a.out = p.out; a.cu_q = p.cu_q; a.ctx_lens = p.ctx_lens; a.row_limits = p.row_limits; a.tables = p.tables;
     a.table_stride = p.table_stride; a.max_blocks = p.max_blocks; a.n_requests = p.n_requests;
     a.n_heads = p.n_heads; a.n_kv_heads = p.n_kv_heads; a.n_pool_blocks = p.n_pool_blocks;
     a.out_stride[0] = p.out_stride[0]; a.out_stride[1] = p.out_stride[1];

@@ -250,6 +250,7 @@ struct PrefillLaunch {
     void* out;
     const int32_t* cu_q;
     const int32_t* ctx_lens;
+    const int32_t* row_limits;  // optional [total_q]: query row r attends to positions 0 .. row_limits[r] - 1 (replaces `causal`)
     const int32_t* tables;
     int64_t table_stride;
     int max_blocks, block_size, head_dim;
@@ -273,8 +274,8 @@ struct PrefillLaunch {
 };
 int launch_prefill_tcgen05(const PrefillLaunch& p, cudaStream_t stream);
 // token r of the packed query batch -> (table row, attended length) for the decode-kernel route
-int launch_prefill_expand(const int32_t* cu_q, const int32_t* ctx_lens, int n_requests, int64_t total_q, int max_blocks,
-                          int block_size, int causal, int32_t* rows_out, int32_t* lens_out, cudaStream_t stream);
+int launch_prefill_expand(const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* row_limits, int n_requests, int64_t total_q,
+                          int max_blocks, int block_size, int causal, int32_t* rows_out, int32_t* lens_out, cudaStream_t stream);
 
 struct NormArgs {
     const void* x;

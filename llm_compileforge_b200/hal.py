@@ -21,7 +21,7 @@ from typing import Any
 
 import torch
 
-from . import kernels_api, ops
+from . import _lib, kernels_api, ops
 
 try:  # the reference's own ABC when its package is importable, else a local twin
     from python_runtime.hal.interface import OpExecutor  # type: ignore
@@ -60,6 +60,8 @@ class B200Backend(OpExecutor):
         self._ops: dict[str, Callable[..., Any]] = {
             "paged_attention": self._op_paged_attention,
             "cache_write": self._op_cache_write,
+            "cache_read": self._op_cache_read,
+            "attention_forward": self._op_attention_forward,
             "quantize": self._op_quantize,
             "dequantize": self._op_dequantize,
             "rms_norm": self._op_rms_norm,
@@ -150,30 +152,81 @@ class B200Backend(OpExecutor):
                                                causal=kw.get("causal", kw.get("is_causal", True)))
 
     def _op_scaled_dot_product_attention(self, inputs: list[Any], **kw: Any) -> torch.Tensor:
-        """Dense SDPA with the reference backend's keywords (pytorch_backend/_ops_attention.py:13-53):
-        ``[q, k, v(, attn_mask)]`` each ``[B,H,S,D]``, ``is_causal`` default False, ``scale``, ``dropout_p``.
-        As there, a floating-point (positional) mask given together with ``is_causal=True`` is dropped.
-        Calls that need an explicit mask, dropout or mixed sequence lengths under a causal mask go to the
-        fallback executor (``ValueError`` without one): the kernel masks by position only."""
+        """Dense SDPA with the reference backend's keywords and mask conventions
+        (pytorch_backend/_ops_attention.py:13-53): ``[q, k, v(, attn_mask)]`` each ``[B,H,S,D]``, ``is_causal`` default
+        False, ``scale``, ``dropout_p``.  As there:
+
+        * a mask of more than four dimensions loses dimension 2, and a mask ``[B, B, S, ...]`` keeps its first entry of
+          dimension 1 (``:17-22``);
+        * a floating-point mask together with ``is_causal=True`` is dropped (``:33-35``);
+        * a floating-point mask with ``is_causal=False`` holds POSITION VALUES, ``[B,1,S,1]`` (or that expanded to
+          ``[B,1,S,S]``): key j is visible to query i iff ``pos[i] >= pos[j]`` (``:36-43``) - the call the compiled model
+          makes for prefill (python_runtime/engine/mlir_executor.py:358).  It runs on the prefill kernels with one visible
+          length per query row; the positions must not decrease along the sequence (the kernel reports it otherwise and
+          the call goes to the fallback executor, ``ValueError`` without one).
+
+        Boolean / additive masks of other kinds, dropout, and ``is_causal=True`` with different query and key lengths go
+        to the fallback executor."""
         q, k, v = inputs[:3]
         mask = kw.get("attn_mask")
         if mask is None and len(inputs) > 3:
             mask = inputs[3]
+        if mask is not None and mask.dim() > 4:
+            mask = mask.squeeze(2)
+        if mask is not None and mask.dim() == 4 and mask.shape[1] > 1 and mask.shape[1] == q.shape[0]:
+            mask = mask[:, :1, :, :]
         causal = bool(kw.get("is_causal", False))
         if mask is not None and mask.dtype.is_floating_point and causal:
             mask = None
-        own = (mask is None and float(kw.get("dropout_p", 0.0)) == 0.0 and q.dim() == 4 and q.is_cuda
-               and not (causal and q.shape[2] != k.shape[2]) and q.shape[1] % k.shape[1] == 0)
-        if not own:
-            if self._fallback is None:
-                raise ValueError("scaled_dot_product_attention: explicit masks and dropout need a fallback executor")
-            return self._fallback.execute("scaled_dot_product_attention", inputs, **kw)
-        return kernels_api.flash_attention_fwd(q, k, v, scale=kw.get("scale"), causal=causal)
+        positions = None
+        if mask is not None and mask.dtype.is_floating_point and mask.dim() == 4 and mask.shape[1] == 1 and mask.shape[-2] > 1:
+            s_len = mask.shape[-2]
+            column = mask.shape[-1] == 1 or (mask.shape[-1] == s_len and mask.stride(-1) == 0)  # [B,1,S,1] or its expand
+            if column and q.shape[2] == s_len and k.shape[2] == s_len and mask.shape[0] in (1, q.shape[0]):
+                positions = mask[:, 0, :, 0]
+        basic = (float(kw.get("dropout_p", 0.0)) == 0.0 and q.dim() == 4 and q.is_cuda and q.shape[1] % k.shape[1] == 0
+                 and not (causal and q.shape[2] != k.shape[2]))
+        if basic and positions is not None:
+            out, ws = ops.attention_dense(q, k, v, mask="positions", positions=positions, scale=kw.get("scale"), return_workspace=True)
+            if not ops.read_status(ws) & _lib.SFB_STATUS_UNSORTED_POSITIONS:
+                return out
+        elif basic and mask is None:
+            return ops.attention_dense(q, k, v, mask="causal" if causal else "none", scale=kw.get("scale"))
+        if self._fallback is None:
+            raise ValueError("scaled_dot_product_attention: this mask / dropout combination needs a fallback executor")
+        return self._fallback.execute("scaled_dot_product_attention", inputs, **kw)
+
+    def _op_attention_forward(self, inputs: list[Any], **kw: Any) -> torch.Tensor:
+        """The Rust runtime's dense attention (runtime/src/engine/kernels.rs:97-302) as an operator: ``[q [H,S,D], k, v
+        [H,Skv,D]]`` head-major float32 with q already scaled, ``is_decode`` (no mask) or prefill (row i sees keys 0..i);
+        the result is position-major ``[S, H*D]`` like its ``ctx_flat``."""
+        q, k, v = inputs[:3]
+        h, s_len, d = q.shape
+        out = torch.empty((s_len, h, d), dtype=q.dtype, device=q.device)
+        ops.attention_dense(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), mask="none" if kw.get("is_decode", s_len == 1) else "causal",
+                            scale=1.0, out=out.permute(1, 0, 2).unsqueeze(0))
+        return out.view(s_len, h * d)
+
+    def _op_cache_read(self, inputs: list[Any], **kw: Any) -> Any:
+        """``cache_read(block_table [R,max_blocks])`` -> ``(key, value)`` each ``[R, max_seq_len, Hkv, D]``
+        (sf-dialect/include/Sf/HALOps.td:190-194; CacheManager.read_paged, python_runtime/engine/cache_manager.py:173-197).
+        Keywords: ``k_cache``, ``v_cache``, ``max_seq_len``, optional ``seq_lens`` (default: every table entry is read,
+        as read_paged does), ``k_scale`` / ``v_scale`` for an e4m3 pool, ``out_dtype``."""
+        table = inputs[0]
+        bs = kw["k_cache"].shape[1]
+        max_len = int(kw.get("max_seq_len", table.shape[1] * bs))
+        lens = kw.get("seq_lens")
+        if lens is None:
+            lens = torch.full((table.shape[0],), table.shape[1] * bs, dtype=torch.int32, device=table.device)
+        key = ops.cache_read(kw["k_cache"], table, lens, max_len, scale=kw.get("k_scale"), out_dtype=kw.get("out_dtype"))
+        value = ops.cache_read(kw["v_cache"], table, lens, max_len, scale=kw.get("v_scale"), out_dtype=kw.get("out_dtype"))
+        return key, value
 
     def _op_fused_rms_norm_matmul(self, inputs: list[Any], **kw: Any) -> torch.Tensor:
         """``[x, rms_weight, mat_weight]`` with ``eps`` (default 1e-5), as pytorch_backend/_ops_norm.py:47-65:
         ``rms_norm(x) * rms_weight @ mat_weight``, result in x's dtype.  The folded weight ``diag(rms_weight) mat_weight``
-        is built on first use of a weight pair and kept (keyed by the two tensors' storage and version counters).
+        is built on first use of a weight pair and kept (keyed by the two tensors' storage and version counters; the entry
+        keeps both tensors alive so that their addresses cannot be reused).
         fp32 and unaligned shapes go to the fallback executor."""
         x, g, w = inputs[0], inputs[1], inputs[-1]
         own = (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and w.dtype == x.dtype and g.dtype == x.dtype and w.dim() == 2
@@ -183,12 +236,14 @@ class B200Backend(OpExecutor):
                 raise ValueError("fused_rms_norm_matmul: bf16 / fp16 with K and N multiples of 8, or a fallback executor")
             return self._fallback.execute("fused_rms_norm_matmul", inputs, **kw)
         key = (g.data_ptr(), g._version, w.data_ptr(), w._version, tuple(w.shape))
-        folded = self._folded.get(key)
-        if folded is None:
+        entry = self._folded.get(key)
+        if entry is None:
             if len(self._folded) >= 256:
                 self._folded.clear()
-            folded = self._folded[key] = ops.fold_norm_weight(g.contiguous(), w)
-        return ops.fused_rms_norm_matmul(x, folded, eps=kw.get("eps", 1e-5))
+            # the entry holds g and w: while it lives their storage cannot be freed and handed to other tensors that
+            # would then match the key with different contents
+            entry = self._folded[key] = (ops.fold_norm_weight(g.contiguous(), w), g, w)
+        return ops.fused_rms_norm_matmul(x, entry[0], eps=kw.get("eps", 1e-5))
 
     def _op_chunked_prefill(self, inputs: list[Any], **kw: Any) -> torch.Tensor:
         """inputs ``[query [T,H,D], key_cache, value_cache, block_table [R,max_blocks]]``

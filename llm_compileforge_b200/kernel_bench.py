@@ -3,9 +3,6 @@
     python -m llm_compileforge_b200.kernel_bench [--iters 20] [--chunk-tokens 0] \
         [--only prefill,norm_matmul,append,norm,decode_c2,decode_c3,shared_prefix]
 
-``--only prefill_trace`` prints the prefill kernel's per-stage time stamps; it needs a library built with
-``-DSFB_PREFILL_TRACE`` and is not part of the default list.
-
 ``bench.py`` at the repository root reports the headline decode metric; this
 module times the remaining kernels on their configurations with CUDA events
 (at least 3 warm-ups; inputs larger than L2 or an L2 flush between iterations)
@@ -100,35 +97,6 @@ def bench_prefill(dev, iters):
             "ms": ms, "flops": flops, "achieved_tflops": tf, "peak_tflops": p["bf16_tflops"],
             "frac": tf / p["bf16_tflops"], "frac_of_sustained": tf / p["bf16_tflops_sustained"], "peak_kind": p["kind"],
             "status": ops.read_status(ws)}
-
-
-def prefill_trace(dev):
-    """Stage timing of the prefill kernel's thread block 0 on config 4; needs a library built with -DSFB_PREFILL_TRACE
-    (``SFB_NVCC_FLAGS=-DSFB_PREFILL_TRACE SFB_LIB_OUT=<path> python -m llm_compileforge_b200.build``, then ``SFB_LIBRARY=<path>``)."""
-    import ctypes
-
-    from . import _lib
-
-    lib = _lib.load()
-    if not hasattr(lib, "sfb_debug_prefill_trace"):
-        raise SystemExit("this libsfb.so was built without -DSFB_PREFILL_TRACE")
-    r = bench_prefill(dev, 3)
-    torch.cuda.synchronize()
-    buf = (ctypes.c_longlong * (3 * 64 * 6))()
-    if lib.sfb_debug_prefill_trace(buf) != 0:
-        raise SystemExit("reading the trace failed")
-    t = [[[buf[(w * 64 + j) * 6 + k] for k in range(6)] for j in range(64)] for w in range(3)]
-    rows = {}
-    for w in (0, 1):
-        steady = [t[w][j] for j in range(3, 16)]
-        mean = lambda f: sum(f(x) for x in steady) / len(steady)
-        rows[f"tile_group_{w}"] = {
-            "wait_for_S": mean(lambda x: x[1] - x[0]), "first_pass": mean(lambda x: x[2] - x[1]), "exchange": mean(lambda x: x[3] - x[2]),
-            "second_pass": mean(lambda x: x[4] - x[3]), "hand_over": mean(lambda x: x[5] - x[4]),
-            "period": (steady[-1][0] - steady[0][0]) / (len(steady) - 1)}
-    mma = [t[2][j] for j in range(3, 16)]
-    rows["mma_warp"] = {"issue_tile0": sum(x[1] - x[0] for x in mma) / len(mma), "issue_tile1": sum(x[3] - x[2] for x in mma) / len(mma)}
-    return {"kernel": "prefill_tcgen05 (traced build)", "tflops_with_stamps": r["achieved_tflops"], "clocks_per_kv_tile": rows}
 
 
 def bench_norm_matmul(dev, iters, m=16384, k=4096, n=6144):
@@ -274,8 +242,6 @@ def main() -> None:
     sys.path.insert(0, ROOT)
     if "prefill" in which:
         print(json.dumps(bench_prefill(dev, args.iters)), flush=True)
-    if "prefill_trace" in which:
-        print(json.dumps(prefill_trace(dev)), flush=True)
     if "norm_matmul" in which:
         print(json.dumps(bench_norm_matmul(dev, args.iters)), flush=True)
         print(json.dumps(bench_norm_matmul(dev, args.iters, m=256)), flush=True)

@@ -76,32 +76,15 @@ def flash_attention_fwd(
     ``[batch, heads, seq, head_dim]`` -> same shape; ``causal`` defaults to True,
     ``scale`` to ``1/sqrt(head_dim)``.
 
-    The dense K/V are viewed as a paged pool with identity block tables (one copy
-    to token-major layout, zero padding to whole 16-token blocks) and run through
-    the chunked-prefill kernel; K/V may have fewer heads than Q (GQA).  As in the
-    reference's CPU path, ``causal=True`` needs equal query and key lengths."""
+    Runs through the library's dense-attention entry point, which repacks K/V as a
+    private paged pool (16-token blocks, identity tables) and uses the chunked-prefill
+    kernels; K/V may have fewer heads than Q (GQA).  As in the reference's CPU path,
+    ``causal=True`` needs equal query and key lengths."""
     if q.dim() != 4 or k.shape != v.shape or k.shape[0] != q.shape[0] or k.shape[-1] != q.shape[-1]:
         raise ValueError("flash_attention_fwd expects q [B,H,S,D] and k, v [B,Hkv,Skv,D]")
-    b, h, sq, d = q.shape
-    hkv, skv = k.shape[1], k.shape[2]
-    if causal and sq != skv:
+    if causal and q.shape[2] != k.shape[2]:
         raise ValueError("causal flash_attention_fwd needs equal query and key lengths")
-    bs = 16
-    nblk = -(-skv // bs)
-    dev = q.device
-
-    def pool(x: torch.Tensor) -> torch.Tensor:
-        t = x.permute(0, 2, 1, 3)  # [B, S, Hkv, D]
-        if nblk * bs != skv:
-            t = torch.nn.functional.pad(t, (0, 0, 0, 0, 0, nblk * bs - skv))
-        return t.contiguous().view(b * nblk, bs, hkv, d)
-
-    tables = torch.arange(b * nblk, dtype=torch.int32, device=dev).view(b, nblk)
-    cu_q = torch.arange(b + 1, dtype=torch.int32, device=dev) * sq
-    ctx = torch.full((b,), skv, dtype=torch.int32, device=dev)
-    q_tok = q.permute(0, 2, 1, 3).contiguous().view(b * sq, h, d)
-    out = ops.prefill_paged(q_tok, pool(k), pool(v), tables, cu_q, ctx, max_q_tokens=sq, scale=scale, causal=causal)
-    return out.view(b, sq, h, d).permute(0, 2, 1, 3).contiguous()
+    return ops.attention_dense(q, k, v, mask="causal" if causal else "none", scale=scale)
 
 
 def chunked_prefill(

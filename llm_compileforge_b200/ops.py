@@ -269,15 +269,29 @@ def prefill_paged(
     out: torch.Tensor | None = None,
     k_scale: torch.Tensor | None = None,
     v_scale: torch.Tensor | None = None,
+    row_limits: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """Attention of packed query chunks ``q [T,H,D]`` over prefix + chunk read from
     the paged pool.  Request ``r`` owns rows ``cu_q[r]:cu_q[r+1]``; its chunk ends
     at cached position ``ctx_lens[r] - 1`` (the chunk's K/V are already in the pool).
     With ``k_scale`` / ``v_scale`` (float32 ``[NB,Hkv]``) the pool holds e4m3 codes; the attended blocks are expanded
-    into a 16-bit scratch inside the workspace first (:func:`prefill_fp8_workspace_bytes`)."""
+    into a 16-bit scratch inside the workspace first (:func:`prefill_fp8_workspace_bytes`).
+    ``row_limits`` (int32 ``[T]``) replaces the causal rule: row ``t`` attends to positions ``0 .. row_limits[t]-1``."""
     lib = _lib.load()
     if out is None:
         out = torch.empty_like(q)
+    if row_limits is not None:
+        if k_scale is not None:
+            raise ValueError("prefill_paged: row_limits are not implemented over an e4m3 pool")
+        if workspace is None:
+            workspace = torch.empty(prefill_workspace_bytes(q.shape[0]), dtype=torch.uint8, device=q.device)
+        check(lib.sfb_prefill_paged_rows(
+            desc(q, "q"), desc(k_cache, "k_cache"), desc(v_cache, "v_cache"), desc(block_tables, "block_tables"),
+            desc(cu_q, "cu_q"), desc(ctx_lens, "ctx_lens"), desc(row_limits, "row_limits"), desc(out, "out"), dtype_code(q.dtype),
+            float(scale) if scale is not None else 0.0, int(max_q_tokens), workspace.data_ptr(),
+            workspace.numel() * workspace.element_size(), current_stream(q.device),
+        ))
+        return out
     if k_scale is not None:
         kc, vc = _as_codes(k_cache), _as_codes(v_cache)
         need = prefill_fp8_workspace_bytes(q.shape[0], block_tables.shape[0], block_tables.shape[1], kc.shape[2], kc.shape[3])
@@ -298,6 +312,59 @@ def prefill_paged(
         desc(cu_q, "cu_q"), desc(ctx_lens, "ctx_lens"), desc(out, "out"), dtype_code(q.dtype),
         float(scale) if scale is not None else 0.0, 1 if causal else 0, int(max_q_tokens), workspace.data_ptr(),
         workspace.numel() * workspace.element_size(), current_stream(q.device),
+    ))
+    return out
+
+
+MASK_MODES = {"none": _lib.SFB_MASK_NONE, "causal": _lib.SFB_MASK_CAUSAL_TOP_LEFT, "causal_bottom_right": _lib.SFB_MASK_CAUSAL_BOTTOM_RIGHT,
+              "positions": _lib.SFB_MASK_POSITIONS}
+
+
+def attention_dense(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, mask: str = "none", positions: torch.Tensor | None = None,
+                    scale: float | None = None, out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
+                    return_workspace: bool = False):
+    """``softmax(q k^T scale + mask) v`` for dense ``q [B,H,Sq,D]``, ``k, v [B,Hkv,Skv,D]`` (any batch / head / token strides).
+    ``mask``: ``"none"``, ``"causal"`` (row i sees keys 0..i), ``"causal_bottom_right"`` (row i sees keys 0..Skv-Sq+i) or
+    ``"positions"`` with ``positions [B or 1, S]`` float32: key j visible to query i iff ``positions[i] >= positions[j]``
+    (the reference backend's positional mask; positions must not decrease - the status word says so otherwise, read it
+    with :func:`read_status` on the returned workspace)."""
+    lib = _lib.load()
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("attention_dense: q, k, v must be [B, H, S, D]")
+    if mask not in MASK_MODES:
+        raise ValueError(f"attention_dense: mask {mask!r} not in {sorted(MASK_MODES)}")
+    if out is None:
+        out = torch.empty_like(q, memory_format=torch.contiguous_format)
+    b, h, sq, d = q.shape
+    need = int(lib.sfb_attention_dense_workspace_bytes(b, h, k.shape[1], sq, k.shape[2], d, dtype_code(q.dtype)))
+    if need < 0:
+        raise ValueError("attention_dense: bad shape")
+    if workspace is None:
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=q.device)
+    if positions is not None:
+        positions = positions.to(torch.float32).contiguous()
+    check(lib.sfb_attention_dense(
+        desc(q, "q"), desc(k, "k"), desc(v, "v"), desc(positions, "positions"), desc(out, "out"), dtype_code(q.dtype),
+        float(scale) if scale is not None else 0.0, MASK_MODES[mask], workspace.data_ptr(),
+        workspace.numel() * workspace.element_size(), current_stream(q.device),
+    ))
+    return (out, workspace) if return_workspace else out
+
+
+def cache_read(cache: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor, max_seq_len: int, *,
+               scale: torch.Tensor | None = None, out_dtype: torch.dtype | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """Dense ``[R, max_seq_len, Hkv, D]`` copy of the pool rows the block tables point at (zero past ``seq_lens[r]``), the
+    reference's ``CacheManager.read_paged`` (python_runtime/engine/cache_manager.py:173-197).  With ``scale [NB,Hkv]`` the
+    pool holds e4m3 codes and the result is ``code * scale`` in ``out_dtype`` (default float32)."""
+    lib = _lib.load()
+    fp8 = scale is not None
+    pool = _as_codes(cache) if fp8 else cache
+    odt = out_dtype or (torch.float32 if fp8 else cache.dtype)
+    out = torch.empty((block_tables.shape[0], int(max_seq_len), pool.shape[2], pool.shape[3]), dtype=odt, device=cache.device)
+    check(lib.sfb_cache_read(
+        desc(pool, "cache"), desc(scale, "scale"), desc(block_tables, "block_tables"), desc(seq_lens, "seq_lens"), desc(out, "out"),
+        _lib.SFB_F8E4M3 if fp8 else dtype_code(cache.dtype), dtype_code(odt), status.data_ptr() if status is not None else None,
+        current_stream(cache.device),
     ))
     return out
 

@@ -253,3 +253,40 @@ def make_norm_matmul_inputs(m: int, k: int, n: int, dtype: torch.dtype = torch.b
     rms_w = (1.0 + 0.02 * torch.randn((k,), generator=g)).to(dtype)
     mat_w = (torch.randn((k, n), generator=g) / math.sqrt(k)).to(dtype)
     return x, rms_w, mat_w, 1e-5
+
+
+SDPA_MASK_CASES = ("positions_bf16", "ties_f32", "rank5_batch_slice_bf16", "expanded_f32", "causal_drops_mask_bf16")
+
+
+def make_sdpa_mask_case(name: str):
+    """Seeded inputs for the dense-attention operator with the reference backend's mask conventions
+    (python_runtime/hal/pytorch_backend/_ops_attention.py:13-53).  Returns ``(inputs, kwargs)`` for
+    ``execute("scaled_dot_product_attention", inputs, **kwargs)``; the mask is the fourth input."""
+    g = _gen(2000 + SDPA_MASK_CASES.index(name))
+    if name == "positions_bf16":  # the compiled model's prefill call: positions 0..S-1 as a [B,1,S,1] column
+        b, h, s, d, dt = 2, 2, 144, 128, torch.bfloat16
+        mask = torch.arange(s, dtype=torch.float32).view(1, 1, s, 1).expand(b, 1, s, 1).contiguous()
+        kw = {}
+    elif name == "ties_f32":  # equal positions see one another: blocks of three tokens, offset 5
+        b, h, s, d, dt = 1, 3, 77, 64, torch.float32
+        mask = (torch.arange(s) // 3 + 5).to(torch.float32).view(1, 1, s, 1)
+        kw = {"scale": 0.2}
+    elif name == "rank5_batch_slice_bf16":  # [B,B,1,S,1]: dimension 2 squeezed, then the first entry of dimension 1 kept
+        b, h, s, d, dt = 2, 2, 40, 128, torch.bfloat16
+        pos = torch.stack([torch.arange(s), torch.arange(s) // 2]).to(torch.float32)  # per batch entry
+        mask = pos.view(b, 1, 1, s, 1).expand(b, b, 1, s, 1).contiguous()
+        kw = {}
+    elif name == "expanded_f32":  # the column already expanded to [B,1,S,S]
+        b, h, s, d, dt = 2, 1, 33, 32, torch.float32
+        mask = (torch.arange(s, dtype=torch.float32) * 2.0).view(1, 1, s, 1).expand(b, 1, s, s)
+        kw = {}
+    elif name == "causal_drops_mask_bf16":  # is_causal=True: the floating-point mask is ignored
+        b, h, s, d, dt = 1, 2, 130, 128, torch.bfloat16
+        mask = torch.zeros((b, 1, s, 1), dtype=torch.float32)
+        kw = {"is_causal": True}
+    else:
+        raise KeyError(name)
+    q = torch.randn((b, h, s, d), generator=g).to(dt)
+    k = torch.randn((b, h, s, d), generator=g).to(dt)
+    v = torch.randn((b, h, s, d), generator=g).to(dt)
+    return [q, k, v, mask], kw

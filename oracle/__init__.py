@@ -9,6 +9,6 @@ it; the shipped package never does and fails loudly without its CUDA library.
 Parity status: pinned.  ``tests/golden/*.npz`` were produced by importing the
 reference's own Python modules (``tests/golden/make_golden.py`` is the
 generating script) and ``tests/test_oracle_golden.py`` checks every function of
-this package against those vectors, and against the reference's own
-known-answer tests restated in ``tests/test_reference_kats.py``.
+this package against those vectors, which include the set-ups of the reference's
+own known-answer tests.
 """

@@ -95,6 +95,8 @@ class BlockManagerPort:
             raise ValueError(f"Source has {len(table)} blocks, cannot share {n}")
         shared = table[:n]
         for bid in shared:
+            if not 0 <= bid < self.num_blocks:  # block.rs:292-294: counts raised so far stay, no table for dst
+                raise ValueError(f"block {bid} not found in share_prefix")
             self.ref[bid] += 1
         self.block_tables[dst] = list(shared)
         return list(shared)
@@ -109,6 +111,9 @@ class BlockManagerPort:
 
     def num_allocated_blocks(self) -> int:
         return self.num_blocks - len(self.free_blocks)
+
+    def ref_count(self, block_id: int) -> int:
+        return self.ref[block_id] if 0 <= block_id < self.num_blocks else -1
 
     def increment_ref_count(self, block_id: int) -> None:
         if 0 <= block_id < self.num_blocks:

@@ -106,4 +106,7 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    sys.path.insert(0, REPO)
+    from oracle.build_ref import reference_root  # argument, $SFB_REFERENCE_ROOT, or ../reference beside this repository
+
+    main(reference_root(sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--") else None))

@@ -61,6 +61,25 @@ def norm_matmul_fixture(ref_root: str) -> None:
     np.savez_compressed(os.path.join(HERE, "norm_matmul.npz"), **blob)
 
 
+def sdpa_mask_fixture(ref_root: str) -> None:
+    """sdpa_masks.npz: the reference backend's scaled_dot_product_attention (pytorch_backend/_ops_attention.py:13-53) on the
+    seeded mask cases of workloads.make_sdpa_mask_case; only the outputs are stored."""
+    sys.path.insert(0, ref_root)
+    sys.path.insert(0, REPO)
+    from python_runtime.hal.pytorch_backend import PyTorchBackend
+
+    from llm_compileforge_b200 import workloads as wl
+
+    torch.set_num_threads(1)
+    hal = PyTorchBackend("cpu")
+    blob = {}
+    for name in wl.SDPA_MASK_CASES:
+        inputs, kw = wl.make_sdpa_mask_case(name)
+        out = hal.execute("scaled_dot_product_attention", inputs, **kw)
+        blob[name] = bits(out) if out.dtype == torch.bfloat16 else out.numpy()
+    np.savez_compressed(os.path.join(HERE, "sdpa_masks.npz"), **blob)
+
+
 def main(ref_root: str) -> None:
     sys.path.insert(0, ref_root)
     sys.path.insert(0, REPO)
@@ -257,14 +276,20 @@ def main(ref_root: str) -> None:
     np.savez_compressed(os.path.join(HERE, "prefill.npz"), **blob)
 
     norm_matmul_fixture(ref_root)
+    sdpa_mask_fixture(ref_root)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    sys.path.insert(0, REPO)
+    from oracle.build_ref import reference_root  # argument, $SFB_REFERENCE_ROOT, or ../reference beside this repository
+
+    root = reference_root(sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--") else None)
     if "--only-norm-matmul" in sys.argv:  # adds that one fixture without rewriting the others
         norm_matmul_fixture(root)
+    elif "--only-sdpa-masks" in sys.argv:
+        sdpa_mask_fixture(root)
     else:
         main(root)

@@ -111,6 +111,23 @@ class TestReferenceCases:
             bm.allocate("a", 4)
         assert "need 0 blocks" in str(e.value)
 
+    def test_ids_from_outside_the_pool(self, cls):
+        # block.rs:214-232 takes any id into the table and counts only the ones it knows; free skips the others
+        # (:184) and share_prefix refuses them (:292-294)
+        bm = cls(8, 16)
+        bm.assign_cached_blocks("a", [0, 999, -5])
+        assert bm.get_blocks("a") == [0, 999, -5]
+        assert bm.ref_count(0) == 1
+        with pytest.raises(ValueError, match="block 999 not found in share_prefix"):
+            bm.share_prefix("a", "b", 48)
+        assert bm.ref_count(0) == 2  # raised before the unknown id was met, as in the reference
+        with pytest.raises(KeyError):
+            bm.get_blocks("b")
+        assert bm.share_prefix("a", "c", 16) == [0]
+        bm.free("a")
+        bm.free("c")
+        assert bm.ref_count(0) == 1 and bm.num_free_blocks() == 8
+
     def test_share_prefix_errors(self, cls):
         bm = cls(8, 4)
         bm.allocate("a", 8)

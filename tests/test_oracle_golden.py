@@ -202,3 +202,56 @@ def test_flash_and_chunked_prefill():
     # all requests share the prefix blocks: identical ids at the head of every table
     heads = [t[:4] for t in pw.block_tables.values()]
     assert heads[0] == heads[1] == heads[2]
+
+
+@pytest.mark.parametrize("case", wl.SDPA_MASK_CASES)
+def test_hal_sdpa_mask_conventions(case):
+    """The restated backend operator against the reference backend's own outputs (tests/golden/sdpa_masks.npz)."""
+    inputs, kw = wl.make_sdpa_mask_case(case)
+    got = ref.hal_scaled_dot_product_attention(inputs, **kw)
+    want = from_bits(golden("sdpa_masks.npz")[case], got.dtype)
+    assert_same(got, want.view(got.shape))
+
+
+def test_positional_mask_is_a_prefix_per_row():
+    """What the GPU path relies on: for positions that do not decrease, ``pos[i] >= pos[j]`` selects the first
+    ``#{j: pos[j] <= pos[i]}`` keys of the row."""
+    inputs, kw = wl.make_sdpa_mask_case("ties_f32")
+    q, k, v, mask = inputs
+    pos = mask[0, 0, :, 0]
+    limits = torch.searchsorted(pos.contiguous(), pos.contiguous(), right=True)
+    rows = []
+    for i in range(q.shape[2]):
+        n = int(limits[i])
+        rows.append(torch.nn.functional.scaled_dot_product_attention(q[:, :, i : i + 1], k[:, :, :n], v[:, :, :n], scale=kw["scale"]))
+    assert_f32_close(torch.cat(rows, dim=2), ref.hal_scaled_dot_product_attention(inputs, **kw), rel=2e-6)
+
+
+def test_rust_attention_forward_known_answers():
+    """runtime/src/engine/kernels.rs:345-419: the Rust file's own two unit tests, restated."""
+    # attention_decode_is_unmasked_dot_product: one head, dim 2, two keys
+    q = torch.tensor([[[1.0, 2.0]]])
+    k = torch.tensor([[[3.0, 0.0], [0.0, 4.0]]])
+    v = torch.tensor([[[5.0, 0.0], [0.0, 6.0]]])
+    ctx, _ = ref.attention_forward(q, k, v, is_decode=True)
+    e5 = math.exp(-5.0)
+    assert abs(ctx[0, 0].item() - e5 / (e5 + 1.0) * 5.0) < 1e-5 and abs(ctx[0, 1].item() - 1.0 / (e5 + 1.0) * 6.0) < 1e-5
+    # attention_prefill_applies_causal_mask: seq 2, kv_len 2, dim 1
+    q = torch.tensor([[[1.0], [1.0]]])
+    k = torch.tensor([[[1.0], [1.0]]])
+    v = torch.tensor([[[10.0], [20.0]]])
+    ctx, probs = ref.attention_forward(q, k, v, is_decode=False)
+    assert probs[0, 0, 0].item() == 1.0 and probs[0, 0, 1].item() == 0.0
+    assert abs(probs[0, 1, 0].item() - probs[0, 1, 1].item()) < 1e-6
+    assert ctx[0, 0].item() == 10.0 and abs(ctx[1, 0].item() - 15.0) < 1e-6
+
+
+def test_read_paged_restates_the_sorted_request_order():
+    """cache_manager.py:173-197: rows follow the SORTED request ids, whole blocks are copied up to max_seq_len."""
+    g = torch.Generator().manual_seed(3)
+    slab = torch.randn((6, 2, 4, 1, 2), generator=g)  # [NB, layers, bs, heads, dim]
+    tables = {"b": [5, 0], "a": [2]}
+    got = ref.read_paged(slab, tables, 6, layer_idx=1)
+    assert got.shape == (2, 6, 1, 2)
+    assert torch.equal(got[0, :4], slab[2, 1]) and torch.equal(got[0, 4:], torch.zeros(2, 1, 2))
+    assert torch.equal(got[1, :4], slab[5, 1]) and torch.equal(got[1, 4:6], slab[0, 1, :2])
