@@ -181,8 +181,11 @@ class B200Backend(OpExecutor):
         positions = None
         if mask is not None and mask.dtype.is_floating_point and mask.dim() == 4 and mask.shape[1] == 1 and mask.shape[-2] > 1:
             s_len = mask.shape[-2]
-            column = mask.shape[-1] == 1 or (mask.shape[-1] == s_len and mask.stride(-1) == 0)  # [B,1,S,1] or its expand
-            if column and q.shape[2] == s_len and k.shape[2] == s_len and mask.shape[0] in (1, q.shape[0]):
+            fits = q.shape[2] == s_len and k.shape[2] == s_len and mask.shape[0] in (1, q.shape[0])
+            # [B,1,S,1], or that column expanded to [B,1,S,S] (a view, or a copy whose rows are constant: one device check)
+            column = mask.shape[-1] == 1 or (mask.shape[-1] == s_len and fits and
+                                             (mask.stride(-1) == 0 or bool((mask == mask[..., :1]).all().item())))
+            if column and fits:
                 positions = mask[:, 0, :, 0]
         basic = (float(kw.get("dropout_p", 0.0)) == 0.0 and q.dim() == 4 and q.is_cuda and q.shape[1] % k.shape[1] == 0
                  and not (causal and q.shape[2] != k.shape[2]))

@@ -155,7 +155,7 @@ def test_cache_read_matches_read_paged(cuda, fp8):
         assert got.dtype == torch.float32 and torch.equal(got.cpu(), want)  # code * scale in fp32: bit-exact
         be = B200Backend()
         key, value = be.execute("cache_read", [dense.to(cuda)], k_cache=codes.view(torch.uint8).to(cuda), v_cache=codes.view(torch.uint8).to(cuda),
-                                k_scale=scales.to(cuda), v_scale=scales.to(cuda), max_seq_len=40)
+                                k_scale=scales.to(cuda), v_scale=scales.to(cuda), max_seq_len=40, seq_lens=cap.to(cuda))
         assert torch.equal(key.cpu(), want) and torch.equal(value.cpu(), want)
 
 
