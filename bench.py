@@ -77,6 +77,9 @@ def parse_args() -> argparse.Namespace:
                    help="decode (default): the headline step.  The others print one line for that kernel of the path alone "
                         "(device time against its roofline, the oracle port timed on the host cores beside it); 1 GPU")
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--headline-only", action="store_true",
+                   help="skip the extra objects of the default run: `kernels` (every other kernel of the path, 1 GPU) and "
+                        "`head_partition` (the configuration split by kv head with the output gathered, N GPUs)")
     p.add_argument("--cpu-sample", type=int, default=48, help="requests in the CPU-baseline sample")
     return p.parse_args()
 
@@ -384,58 +387,183 @@ def _best_of(fn, repeats: int = 3) -> float:
     return best
 
 
-def run_kernel_line(args: argparse.Namespace) -> None:
-    """One JSON line for a single kernel of the path (not the headline step): device time from the kernel benchmark of
-    the package, the reference's CPU algorithm (oracle port) on a bounded sample of the same workload beside it."""
+KERNEL_KINDS = ("append", "norm_256", "norm_16384", "prefill", "decode_c2", "decode_c3", "norm_matmul")
+
+
+def kernel_entry(kind: str, iters: int, dev: torch.device, cpu: bool = True) -> dict:
+    """One kernel of the path, timed alone on its configuration (``llm_compileforge_b200.kernel_bench``: CUDA events,
+    >= 3 warm-ups, inputs larger than L2 or an L2 flush between iterations) with the SM clocks sampled while it runs, its
+    roofline fraction, and the reference's CPU algorithm (oracle port) on a bounded sample of the same workload."""
     from llm_compileforge_b200 import kernel_bench as kb
     from oracle import reference_port as ref
 
-    dev = torch.device("cuda", 0)
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    iters = max(args.steps, 3)
-    if args.kernel == "append":
-        r = kb.bench_append(dev, iters)
+    with ClockSampler(dev.index or 0) as clocks:
+        if kind == "append":
+            r = kb.bench_append(dev, iters)
+        elif kind in ("norm_256", "norm_16384"):
+            r = kb.bench_norm(dev, iters, int(kind.split("_")[1]))
+        elif kind == "prefill":
+            r = kb.bench_prefill(dev, iters)
+        elif kind in ("decode_c2", "decode_c3"):
+            r = kb.bench_decode(dev, iters, wl.C2 if kind == "decode_c2" else wl.C3)
+        elif kind == "norm_matmul":
+            r = kb.bench_norm_matmul(dev, iters)
+        else:
+            raise KeyError(kind)
+        torch.cuda.synchronize(dev)
+    tensor = "achieved_tflops" in r
+    unit = "TFLOP/s" if tensor else "GB/s"
+    entry = {"kernel": r["kernel"], "workload": r["workload"], "ms": r["ms"], "bound": "tensor" if tensor else "hbm",
+             "achieved": r["achieved_tflops"] if tensor else r["achieved_gbs"], "peak": r["peak_tflops"] if tensor else r["peak_gbs"],
+             "unit": unit, "frac": r["frac"],
+             "peak_kind": f"of {r['peak_kind']}" + (" (burst GEMM rate: the kernel is timed alone)" if tensor else ""),
+             "clocks": clocks.summary(), "device_status": r.get("status", 0)}
+    for k in ("frac_of_sustained", "frac_of_nominal_8TBs", "tokens_per_s", "timing", "ms_copy_same_bytes", "ms_eager_launch"):
+        if k in r:
+            entry[k] = r[k]
+    if not cpu:
+        return entry
+    if kind == "append":
         n_tok, hkv, d = 262144, 8, 128
         g = torch.Generator().manual_seed(5)
         pool = (torch.randn((n_tok // 16, 16, hkv, d), generator=g) * 2).to(torch.bfloat16)
         sec = _best_of(lambda: ref.fp8_quantize_pool_fast(pool))
-        cpu_bytes = wl.append_algorithmic_bytes(n_tok, hkv, d, 2) / 2  # one of K / V
-        metric, unit, value, bound = "fp8_quantize_on_append_GBps", "GB/s", r["achieved_gbs"], "hbm"
-        cpu = {"value": cpu_bytes / sec / 1e9, "unit": unit, "cores": cores, "kind": "port",
-               "sample": f"{n_tok} tokens of one of K/V (Hkv 8, D 128) through the per-(block, head) quantiser, best of 3, {sec:.3f} s"}
-        roof = {"bound": bound, "achieved": value, "peak": r["peak_gbs"], "unit": unit, "frac": r["frac"], "traffic": None}
-    elif args.kernel == "norm":
-        r = kb.bench_norm(dev, iters, 16384)
-        x, w, eps = wl.make_rms_norm_inputs(rows=16384, hidden=4096)
+        value = wl.append_algorithmic_bytes(n_tok, hkv, d, 2) / 2 / sec / 1e9  # one of K / V
+        sample = f"{n_tok} tokens of one of K/V (Hkv 8, D 128) through the per-(block, head) quantiser, best of 3, {sec:.3f} s"
+    elif kind in ("norm_256", "norm_16384"):
+        rows = int(kind.split("_")[1])
+        x, w, eps = wl.make_rms_norm_inputs(rows=rows, hidden=4096)
         sec = _best_of(lambda: ref.rms_norm_hal(x, w, eps))
-        metric, unit, value, bound = "rms_norm_GBps", "GB/s", r["achieved_gbs"], "hbm"
-        cpu = {"value": wl.rms_norm_algorithmic_bytes(16384, 4096, 2) / sec / 1e9, "unit": unit, "cores": cores, "kind": "port",
-               "sample": f"the same [16384, 4096] bf16 rows, best of 3, {sec:.3f} s"}
-        roof = {"bound": bound, "achieved": value, "peak": r["peak_gbs"], "unit": unit, "frac": r["frac"], "traffic": None}
-    elif args.kernel == "prefill":
-        r = kb.bench_prefill(dev, iters)
+        value = wl.rms_norm_algorithmic_bytes(rows, 4096, 2) / sec / 1e9
+        sample = f"the same [{rows}, 4096] bf16 rows, best of 3, {sec:.4f} s"
+    elif kind == "prefill":
         pw = wl.make_prefill_workload(n_requests=1)
         rid = next(iter(pw.block_tables))
         sec = _best_of(lambda: ref.chunked_prefill(pw.q, pw.k_cache, pw.v_cache, pw.block_tables[rid], pw.ctx_lens[rid], scale=pw.scale))
-        metric, unit, value, bound = "chunked_prefill_TFLOPs", "TFLOP/s", r["achieved_tflops"], "tensor"
-        cpu = {"value": wl.prefill_flops(1, pw.n_heads, pw.head_dim, pw.chunk_len, pw.prefix_len) / sec / 1e12, "unit": unit, "cores": cores,
-               "kind": "port", "sample": f"one of the 32 requests (2048-token prefix + 512-token chunk), best of 3, {sec:.3f} s"}
-        roof = {"bound": bound, "achieved": value, "peak": r["peak_tflops"], "unit": unit, "frac": r["frac"], "traffic": None}
+        value = wl.prefill_flops(1, pw.n_heads, pw.head_dim, pw.chunk_len, pw.prefix_len) / sec / 1e12
+        sample = f"one of the 32 requests (2048-token prefix + 512-token chunk), best of 3, {sec:.3f} s"
+    elif kind in ("decode_c2", "decode_c3"):
+        shape = wl.C2 if kind == "decode_c2" else wl.C3
+        lengths = wl.config_lengths(shape)
+        base = cpu_baseline(shape, lengths, 16, repeats=2)
+        st_bytes = wl.decode_algorithmic_bytes(lengths, shape.n_heads, shape.n_kv_heads, shape.head_dim, 1 if shape.kv_fp8 else 2, 2, 2,
+                                               shape.kv_fp8, shape.block_size)
+        value = base["value"] * st_bytes / len(lengths) / 1e9  # requests/s of the sample x mean bytes per request
+        sample = base["sample"] + "; GB/s = requests/s x the workload's mean algorithmic bytes per request"
     else:
-        r = kb.bench_norm_matmul(dev, iters)
         x, g, w, eps = wl.make_norm_matmul_inputs(2048, 4096, 6144)
         sec = _best_of(lambda: ref.fused_rms_norm_matmul(x, g, w, eps))
-        metric, unit, value, bound = "fused_rms_norm_matmul_TFLOPs", "TFLOP/s", r["achieved_tflops"], "tensor"
-        cpu = {"value": 2.0 * 2048 * 4096 * 6144 / sec / 1e12, "unit": unit, "cores": cores, "kind": "port",
-               "sample": f"2048 of the 16384 rows against the same [4096, 6144] weight, best of 3, {sec:.3f} s"}
-        roof = {"bound": bound, "achieved": value, "peak": r["peak_tflops"], "unit": unit, "frac": r["frac"], "traffic": None}
-    roof["peak_kind"] = f"of {r['peak_kind']}" + (" (burst GEMM rate: the kernel is timed alone)" if bound == "tensor" else "")
-    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": iters, "warmup": 3, "ms_per_step": r["ms"],
+        value = 2.0 * 2048 * 4096 * 6144 / sec / 1e12
+        sample = f"2048 of the 16384 rows against the same [4096, 6144] weight, best of 3, {sec:.3f} s"
+    entry["cpu_baseline"] = {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample}
+    return entry
+
+
+def run_kernel_line(args: argparse.Namespace) -> None:
+    """One JSON line for a single kernel of the path (not the headline step)."""
+    dev = torch.device("cuda", 0)
+    iters = max(args.steps, 3)
+    kind = {"append": "append", "norm": "norm_16384", "prefill": "prefill", "norm_matmul": "norm_matmul"}[args.kernel]
+    e = kernel_entry(kind, iters, dev)
+    metric = {"append": "fp8_quantize_on_append_GBps", "norm": "rms_norm_GBps", "prefill": "chunked_prefill_TFLOPs",
+              "norm_matmul": "fused_rms_norm_matmul_TFLOPs"}[args.kernel]
+    roof = {"bound": e["bound"], "achieved": e["achieved"], "peak": e["peak"], "unit": e["unit"], "frac": e["frac"], "traffic": None,
+            "peak_kind": e["peak_kind"]}
+    line = {"metric": metric, "value": e["achieved"], "unit": e["unit"], "n_gpus": 1, "steps": iters, "warmup": 3, "ms_per_step": e["ms"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic",
-            "config": {"workload": r["workload"], "kernel": r["kernel"]}, "roofline": roof, "cpu_baseline": cpu,
-            "device_status": r.get("status", 0)}
+            "config": {"workload": e["workload"], "kernel": e["kernel"]}, "roofline": roof, "cpu_baseline": e["cpu_baseline"],
+            "clocks": e["clocks"], "device_status": e["device_status"]}
     print(json.dumps(line), flush=True)
+
+
+def head_partition_report(args: argparse.Namespace, world: int, rank: int, dev: torch.device, one_gpu_ms: float) -> dict | None:
+    """The configuration split by kv head over the GPUs of the run (one kv head = eight query heads per GPU at eight
+    GPUs): every GPU decodes ALL requests for its heads and ends the step holding the whole [B, H, D] output - gathered
+    by NCCL after the decode, and by the decode kernel's own peer stores plus one signal kernel.  Strong scaling:
+    `one_gpu_ms` is this run's own per-step time of one GPU serving the whole configuration."""
+    import dataclasses
+
+    import torch.distributed as dist
+
+    from llm_compileforge_b200 import ops
+    from llm_compileforge_b200.comm import PeerGather
+
+    full = shape_of(args.workload)
+    if full.n_kv_heads % world:
+        return None
+    shape = dataclasses.replace(full, n_heads=full.n_heads // world, n_kv_heads=full.n_kv_heads // world)
+    total = args.warmup + args.steps
+    st = DecodeState(shape, args.batch or shape.batch, 2 * total + 2, dev, seed_offset=0)
+    chunk = pick_chunk_tokens(st.lengths, args.chunk_tokens)
+    workspace = torch.zeros(ops.decode_workspace_bytes(st.batch, shape.n_heads, shape.head_dim, st.tables.shape[1], shape.block_size, chunk),
+                            dtype=torch.uint8, device=dev)
+    out = torch.empty_like(st.q)
+    gathered = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device=dev)
+    peer = PeerGather(st.batch, shape.n_heads, shape.head_dim, shape.dtype, dev)
+    fp8kw = dict(k_scale=st.k_scale, v_scale=st.v_scale) if st.fp8 else {}
+    tailkw = dict(k_tail=st.k_tail, v_tail=st.v_tail) if st.fp8 else {}
+
+    def step(s: int, mode: str, ev=None) -> None:
+        ops.cache_write(st.new_k, st.new_v, st.cu_one, st.pos_steps[s], st.tables, st.k_cache, st.v_cache, max_new_tokens=1, **fp8kw, **tailkw)
+        if ev:
+            ev[0].record()
+        if mode == "peer":
+            peer.decode(st.q, st.k_cache, st.v_cache, st.tables, st.len_steps[s], chunk_tokens=chunk, workspace=workspace, **fp8kw)
+        else:
+            ops.paged_attention_decode(st.q, st.k_cache, st.v_cache, st.tables, st.len_steps[s], scale=None, chunk_tokens=chunk,
+                                       workspace=workspace, out=out, **fp8kw)
+        if ev:
+            ev[1].record()
+        if mode == "nccl":
+            dist.all_gather_into_tensor(gathered, out)
+
+    def sync_all() -> None:
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    report = {"workload": f"{full.name}: {st.batch} requests on every GPU, {shape.n_kv_heads} of {full.n_kv_heads} kv heads "
+                          f"({shape.n_heads} query heads) per GPU, output gathered on every GPU"}
+    off = 0
+    for mode in ("nccl", "peer"):
+        for s in range(args.warmup):
+            step(off + s, mode)
+        sync_all()
+        check = None
+        if mode == "peer":  # the peer-stored output of the last warm-up step against decode + NCCL all-gather of the same step
+            ops.paged_attention_decode(st.q, st.k_cache, st.v_cache, st.tables, st.len_steps[off + args.warmup - 1], scale=None,
+                                       chunk_tokens=chunk, workspace=workspace, out=out, **fp8kw)
+            dist.all_gather_into_tensor(gathered, out)
+            same = torch.equal(gathered.permute(1, 0, 2, 3).reshape(peer.out.shape), peer.out) and not peer.timed_out()
+            flag = torch.tensor([int(same)], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            check = "equal" if int(flag.item()) else "MISMATCH"
+            sync_all()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(args.steps):
+            step(off + args.warmup + i, mode, evs[i])
+        t1.record()
+        sync_all()
+        t = torch.tensor([t0.elapsed_time(t1), sum(a.elapsed_time(b) for a, b in evs) / args.steps], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t[0].item() / args.steps
+        entry = {"tokens_per_s": st.batch / (ms / 1e3), "ms_per_step": ms, "decode_call_ms": t[1].item(),
+                 "decode_gbs_per_gpu": st.algorithmic_bytes(off + args.warmup + args.steps // 2) / (t[1].item() / 1e3) / 1e9,
+                 "strong_scaling_vs_one_gpu": one_gpu_ms / ms}
+        if check:
+            entry["gather_check"] = check
+        report["gather_" + mode] = entry
+        off += total
+    st_bits = ops.read_status(workspace) | (4 if peer.timed_out() else 0)
+    flag = torch.tensor([st_bits], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    report["device_status"] = int(flag.item())
+    report["one_gpu_ms_per_step"] = one_gpu_ms
+    return report if rank == 0 else {}
 
 
 def workload_config(shape: wl.DecodeShape, batch: int, args: argparse.Namespace, chunk: int) -> dict:
@@ -605,17 +733,38 @@ def main() -> None:
     else:
         total_requests = st.batch
 
+    extras: dict = {}
+    cpu_line = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_line = cpu_baseline(shape, st.lengths, min(args.cpu_sample, st.batch), repeats=3)
+    algorithmic = st.algorithmic_bytes(args.warmup + args.steps // 2)
+    state_batch = st.batch
+    peer_used, peer_gave_up = peer is not None, bool(peer is not None and peer.timed_out())
+    if not args.headline_only and not by_head and (world > 1 or (args.workload == "c5" and not args.batch)):
+        # the other kernels of the path (1 GPU) / the configuration's own kv-head layout (N GPUs): free the headline state first
+        del pipe, st, workspace, out, gathered, peer
+        torch.cuda.empty_cache()
+        try:
+            if world == 1:
+                extras["kernels"] = {k: kernel_entry(k, 20, dev, cpu=not args.no_cpu_baseline) for k in KERNEL_KINDS if k != "norm_matmul"}
+            elif args.workload == "c5" and shape.n_kv_heads % world == 0:
+                rep = head_partition_report(args, world, rank, dev, elapsed_ms / args.steps)
+                if rep:
+                    extras["head_partition"] = rep
+        except Exception as e:  # noqa: BLE001  (the headline line is still printed)
+            extras["extras_error"] = f"{type(e).__name__}: {e}"
+
     if rank == 0:
         ms_per_step = elapsed_ms / args.steps
         value = total_requests / (ms_per_step / 1e3)
         peak, peak_kind = peaks()
-        alg = st.algorithmic_bytes(args.warmup + args.steps // 2)
+        alg = algorithmic
         achieved = alg / (decode_ms / 1e3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if by_head else "weak", "vs_baseline": None,
-            "dtype": "e4m3 KV, bf16 q/out, f32 accumulate" if st.fp8 else "bf16",
-            "data": "synthetic", "config": workload_config(shape, st.batch, args, chunk),
+            "dtype": "e4m3 KV, bf16 q/out, f32 accumulate" if shape.kv_fp8 else "bf16",
+            "data": "synthetic", "config": workload_config(shape, state_batch, args, chunk),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": alg * TRAFFIC_PER_ALGORITHMIC_BYTE, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
                          "kernel": "decode_tma_kernel (split-K, in-kernel merge)", "algorithmic_bytes_per_launch": alg,
@@ -626,16 +775,17 @@ def main() -> None:
                     "table_upload": "device-resident tables; only ids of added blocks are sent", "host_binding": host_binding},
             # per step: cache_write_kernel + decode_tma_kernel (split merge is in-kernel), + decode_worklist_kernel when the
             # split has >= 600 (request, chunk) slots over a pool bound of >= 1 GiB (the launcher's rule), + the peer signal kernel
-            "gpu_launches": args.steps * (2 + int(worklist) + int(peer is not None)),
+            "gpu_launches": args.steps * (2 + int(worklist) + int(peer_used)),
             "clocks": clocks.summary(),
-            "device_status": status | (4 if (peer is not None and peer.timed_out()) else 0),
+            "device_status": status | (4 if peer_gave_up else 0),
         }
         if args.gather:
             line["config"]["gather"] = args.gather
         if gather_check:
             line["gather_check"] = gather_check
-        if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(shape, st.lengths, min(args.cpu_sample, st.batch), repeats=3)
+        if cpu_line:
+            line["cpu_baseline"] = cpu_line
+        line.update(extras)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
