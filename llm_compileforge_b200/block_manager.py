@@ -51,6 +51,9 @@ class BlockManager:
         self.num_blocks = int(num_blocks)
         self.block_size = int(block_size)
         self.device_tables: torch.Tensor | None = None
+        # counts the calls that can give a request a device-table row or take one away; callers that cache
+        # request -> row lookups (the step pipeline) compare it instead of asking for every row on every step
+        self.row_generation = 0
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
@@ -59,6 +62,7 @@ class BlockManager:
 
     # ── allocation (block.rs:146-268) ────────────────────────────────────────
     def allocate(self, request_id: str, num_tokens: int) -> list[int]:
+        self.row_generation += 1
         cap = -(-int(num_tokens) // self.block_size)
         buf = (ctypes.c_int32 * max(cap, 1))()
         n = self._lib.sfb_bm_allocate(self._h, request_id.encode(), int(num_tokens), buf, cap)
@@ -67,18 +71,21 @@ class BlockManager:
         return list(buf[:n])
 
     def free(self, request_id: str) -> None:
+        self.row_generation += 1
         self._lib.sfb_bm_free(self._h, request_id.encode())
 
     def free_block(self, block_id: int) -> None:
         self._lib.sfb_bm_free_block(self._h, int(block_id))
 
     def assign_cached_blocks(self, request_id: str, block_ids: Sequence[int]) -> None:
+        self.row_generation += 1
         ids = (ctypes.c_int32 * max(len(block_ids), 1))(*[int(b) for b in block_ids])
         rc = self._lib.sfb_bm_assign_cached_blocks(self._h, request_id.encode(), ids, len(block_ids))
         if rc < 0:
             _raise(rc)
 
     def ensure_blocks(self, request_id: str, target_tokens: int) -> None:
+        self.row_generation += 1  # an unknown request is created here (block.rs:236-268)
         rc = self._lib.sfb_bm_ensure_blocks(self._h, request_id.encode(), int(target_tokens))
         if rc < 0:
             _raise(rc)
@@ -101,6 +108,7 @@ class BlockManager:
             _raise(rc)
 
     def share_prefix(self, src_request_id: str, dst_request_id: str, prefix_len: int) -> list[int]:
+        self.row_generation += 1
         n = self._lib.sfb_bm_share_prefix(self._h, src_request_id.encode(), dst_request_id.encode(), int(prefix_len))
         if n < 0:
             _raise(n)

@@ -101,7 +101,9 @@ class AttentionStepPipeline:
         s = self.slots[ticket % len(self.slots)]
         if s.busy:
             s.copied_out.synchronize()  # its result buffer is about to be reused
-        key = tuple(request_ids)
+        # table row of every request: looked up again whenever the batch or the manager's set of requests has changed (an
+        # id that was freed and admitted again may sit in another row)
+        key = (self.bm.row_generation, tuple(request_ids))
         if key != self._rows_key:
             self._rows_key = key
             self._rows = torch.tensor([self.bm.row(r) for r in request_ids], dtype=torch.int32)

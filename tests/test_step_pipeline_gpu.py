@@ -91,3 +91,47 @@ def test_pipelined_steps_equal_serial_steps(fp8):
         assert torch.equal(a["kc"][ids], b["kc"][ids]) and torch.equal(a["vc"][ids], b["vc"][ids])
         if fp8:
             assert torch.equal(a["ks"][ids], b["ks"][ids]) and torch.equal(a["vs"][ids], b["vs"][ids])
+
+
+def test_readmitted_request_id_gets_its_new_table_row():
+    """A request id that is freed and admitted again (preemption) may sit in another row of the device tables while the
+    tuple of ids of the batch stays the same: the pipeline must look its row up again."""
+    dev = torch.device("cuda:0")
+    nb, bs, hkv, h, d = 64, 16, 2, 8, 128
+    g = torch.Generator().manual_seed(8)
+    bm = BlockManager(nb, bs)
+    tables = bm.attach_device_tables(4, 8, dev)
+    kc = torch.zeros((nb, bs, hkv, d), dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros_like(kc)
+    pipe = AttentionStepPipeline(bm, kc, vc, max_batch=2, n_heads=h, dtype=torch.bfloat16, depth=2)
+
+    def admit(rid, n):  # allocate and write a prompt of n tokens
+        bm.allocate(rid, n)
+        bm.sync()
+        row = torch.tensor([bm.row(rid)], dtype=torch.int32, device=dev)
+        k = torch.randn((n, hkv, d), generator=g).to(torch.bfloat16).to(dev)
+        v = torch.randn((n, hkv, d), generator=g).to(torch.bfloat16).to(dev)
+        ops.cache_write(k, v, torch.tensor([0, n], dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev), tables, kc, vc,
+                        max_new_tokens=n, table_rows=row)
+        torch.cuda.synchronize()
+
+    def step(pos):
+        q = torch.randn((2, h, d), generator=g).to(torch.bfloat16).pin_memory()
+        k = torch.randn((2, hkv, d), generator=g).to(torch.bfloat16).pin_memory()
+        v = torch.randn((2, hkv, d), generator=g).to(torch.bfloat16).pin_memory()
+        got = pipe.result(pipe.submit(["a", "b"], q, k, v, torch.tensor(pos, dtype=torch.int32).pin_memory())).clone()
+        dense, lens, _ = dense_block_tables({r: bm.get_blocks(r) for r in ("a", "b")}, {"a": pos[0] + 1, "b": pos[1] + 1}, bs)
+        want = ops.paged_attention_decode(q.to(dev), kc, vc, dense.to(dev), lens.to(dev))  # the pools already hold the new token
+        assert torch.equal(got, want.cpu())
+
+    admit("a", 20)
+    admit("b", 33)
+    admit("c", 5)
+    step([20, 33])
+    row_before = bm.row("a")
+    bm.free("a")
+    bm.free("c")  # rows come back last-freed-first: "a" now takes the row "c" had
+    admit("a", 27)
+    assert bm.row("a") != row_before
+    step([27, 34])
+    assert pipe.status() == 0
