@@ -288,27 +288,54 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         // =========================== consumer warps ===========================
         // Query fragments (B operand of S^T = K.Q^T): column g = query head g of the group.
         uint32_t qf[C::KSTEPS][2];
+        float colq0, colq1;  // softmax scale in log2 units for the score columns 2t, 2t+1 this thread holds
         {
             const QT* qrow = reinterpret_cast<const QT*>(a.q) + req * a.q_stride[0] + (int64_t)(kvh * group + g) * a.q_stride[1];
+            uint2 raw[C::KSTEPS];
 #pragma unroll
             for (int ks = 0; ks < C::KSTEPS; ++ks) {
                 constexpr int per_chunk = C::EPC / 4;
                 const int cc = ks / per_chunk, jj = ks % per_chunk;  // cc = sub*2 + ci
                 const int d0 = (cc >> 1) * C::EPR + (t + 4 * (cc & 1)) * C::EPC + 4 * jj;
-                uint2 raw = make_uint2(0u, 0u);
-                if (g < group) raw = *reinterpret_cast<const uint2*>(qrow + d0);
-                if constexpr (QBF16 && !BF) {  // bf16 query feeding an fp16 MMA: exact widening via float
-                    float f0 = __uint_as_float(raw.x << 16), f1 = __uint_as_float(raw.x & 0xffff0000u);
-                    float f2 = __uint_as_float(raw.y << 16), f3 = __uint_as_float(raw.y & 0xffff0000u);
+                raw[ks] = make_uint2(0u, 0u);
+                if (g < group) raw[ks] = *reinterpret_cast<const uint2*>(qrow + d0);
+            }
+            float colexp = 1.f;
+            if constexpr (QBF16 && !BF) {
+                // A bf16 query feeding the fp16 MMA of an e4m3 pool.  bf16 reaches 3e38, fp16 65504: the row is first
+                // scaled by a power of two that puts its largest magnitude into [2^13, 2^14) (exact in fp32; the 8-bit
+                // bf16 significand then fits fp16's 11 bits, and what falls below fp16's range is 2^-37 of the row's
+                // maximum), and the power goes back into the column's softmax scale.
+                float amax = 0.f;
+#pragma unroll
+                for (int ks = 0; ks < C::KSTEPS; ++ks) {
+                    amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(raw[ks].x << 16)), fabsf(__uint_as_float(raw[ks].x & 0xffff0000u))));
+                    amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(raw[ks].y << 16)), fabsf(__uint_as_float(raw[ks].y & 0xffff0000u))));
+                }
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));  // the four threads of a quad hold one query row
+                int e = 0;
+                if (amax > 0.f && amax < INFINITY) e = min(max((int)((__float_as_uint(amax) >> 23) & 0xffu) - 127 - 13, -100), 114);
+                const float down = __uint_as_float((uint32_t)(127 - e) << 23);  // 2^-e
+                colexp = __uint_as_float((uint32_t)(127 + e) << 23);            // 2^e
+#pragma unroll
+                for (int ks = 0; ks < C::KSTEPS; ++ks) {
+                    const float f0 = __uint_as_float(raw[ks].x << 16) * down, f1 = __uint_as_float(raw[ks].x & 0xffff0000u) * down;
+                    const float f2 = __uint_as_float(raw[ks].y << 16) * down, f3 = __uint_as_float(raw[ks].y & 0xffff0000u) * down;
                     qf[ks][0] = pack2<false>(f0, f1);
                     qf[ks][1] = pack2<false>(f2, f3);
-                } else {
-                    qf[ks][0] = raw.x;
-                    qf[ks][1] = raw.y;
+                }
+            } else {
+#pragma unroll
+                for (int ks = 0; ks < C::KSTEPS; ++ks) {
+                    qf[ks][0] = raw[ks].x;
+                    qf[ks][1] = raw[ks].y;
                 }
             }
+            const float qscale = a.scale * kLog2e;
+            colq0 = qscale * __shfl_sync(0xffffffffu, colexp, (2 * t) * 4);      // lanes 4c .. 4c+3 hold query row c
+            colq1 = qscale * __shfl_sync(0xffffffffu, colexp, (2 * t + 1) * 4);
         }
-        const float qscale = a.scale * kLog2e;
         for (int it = 0; it < n_iters; ++it) {
             const int s = it % STAGES, round = it / STAGES;
             if (!mbar_wait(full0 + 8 * s, round & 1)) { timed_out = true; break; }
@@ -350,11 +377,11 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     }
                 }
                 // ---- online softmax in log2 units; the V scale rides in the exponent
-                const float qk = qscale * ksc;
+                const float qk0 = colq0 * ksc, qk1 = colq1 * ksc;
                 const float lv = FP8 ? __log2f(vsc) : 0.f;
                 const float ivsc = FP8 ? (vsc > 0.f ? __frcp_rn(vsc) : 0.f) : 1.f;
-                float x0 = fmaf(sa[0] + sb[0], qk, lv), x1 = fmaf(sa[1] + sb[1], qk, lv);
-                float x2 = fmaf(sa[2] + sb[2], qk, lv), x3 = fmaf(sa[3] + sb[3], qk, lv);
+                float x0 = fmaf(sa[0] + sb[0], qk0, lv), x1 = fmaf(sa[1] + sb[1], qk1, lv);
+                float x2 = fmaf(sa[2] + sb[2], qk0, lv), x3 = fmaf(sa[3] + sb[3], qk1, lv);
                 if (n_valid < 16) {
                     if (rowk >= n_valid) x0 = x1 = -INFINITY;
                     if (rowk + 8 >= n_valid) x2 = x3 = -INFINITY;

@@ -195,6 +195,47 @@ def test_tensor_core_path_fp8(cuda, heads, kv_heads, dim, qdtype):
         assert cos_deficit(got, stack_outputs(want, rids)) <= 1e-4
 
 
+def test_fp8_mixed_scales_with_rows_of_order_one(cuda):
+    """Blocks whose K and V scales differ by orders of magnitude while every output row stays O(1): the contract's own
+    tolerance (2e-2 absolute, cosine deficit 1e-4) with nothing added."""
+    q, k, v, tables, lens = _random_case(41, 6, 32, 8, 128, 280, torch.bfloat16)
+    g = torch.Generator().manual_seed(42)
+    nb = k.shape[0]
+    # K: per-block gains 1/16 .. 16 change the logits' spread block by block; V: gains 1/32 .. 1, so no block dominates the row
+    k = (k.float() * (2.0 ** torch.randint(-4, 5, (nb, 1, 1, 1), generator=g)) * 0.25).to(torch.bfloat16)
+    v = (v.float() * (2.0 ** torch.randint(-5, 1, (nb, 1, 1, 1), generator=g).float())).to(torch.bfloat16)
+    kc, ks = ref.fp8_quantize_pool_fast(k)
+    vc, vs = ref.fp8_quantize_pool_fast(v)
+    assert ks.max() / ks[ks > 0].min() > 100 and vs.max() / vs[vs > 0].min() > 10
+    kd, vd = ref.fp8_dequantize_pool(kc, ks), ref.fp8_dequantize_pool(vc, vs)
+    want = ref.paged_attention_f64(q, kd, vd, tables, lens)
+    rids = list(tables)
+    assert stack_outputs(want, rids).abs().max() < 4.0
+    for chunk in (0, 64):
+        out = pkg.paged_attention(q.to(cuda), kc.to(cuda), vc.to(cuda), tables, lens, k_scale=ks.to(cuda), v_scale=vs.to(cuda), chunk_tokens=chunk)
+        assert_half_close(stack_outputs(out, rids).cpu(), stack_outputs(want, rids), what=f"mixed scales, chunk {chunk}")
+
+
+@pytest.mark.parametrize("gain", [1e5, 3e4, 1e-6, 1e-30])
+def test_fp8_decode_bf16_query_outside_fp16_range(cuda, gain):
+    """A bf16 query is fed to the fp16 tensor-core path of an e4m3 pool.  Magnitudes beyond fp16's 65504, or far below its
+    smallest normal, must neither overflow to infinity nor lose the row: heads of very different magnitude share a batch."""
+    q, k, v, tables, lens = _random_case(77, 4, 16, 4, 128, 120, torch.bfloat16)
+    q = q.float()
+    q[:, ::2] *= gain          # every other head scaled, the rest left at N(0,1)
+    q[0, 1] = 0.0              # an all-zero query row
+    q = q.to(torch.bfloat16)
+    kc, ks = ref.fp8_quantize_pool_fast(k)
+    vc, vs = ref.fp8_quantize_pool_fast(v)
+    kd, vd = ref.fp8_dequantize_pool(kc, ks), ref.fp8_dequantize_pool(vc, vs)
+    want = ref.paged_attention_f64(q, kd, vd, tables, lens)
+    rids = list(tables)
+    out = pkg.paged_attention(q.to(cuda), kc.to(cuda), vc.to(cuda), tables, lens, k_scale=ks.to(cuda), v_scale=vs.to(cuda))
+    got = stack_outputs(out, rids).cpu()
+    assert torch.isfinite(got.float()).all()
+    assert_half_close(got, stack_outputs(want, rids), what=f"query gain {gain:g}")
+
+
 def test_tensor_core_path_strided_slab_and_bad_block(cuda):
     q, k, v, tables, lens = _random_case(7, 4, 16, 4, 64, 150, torch.bfloat16, layers=2)
     dk, dv = k.to(cuda), v.to(cuda)
