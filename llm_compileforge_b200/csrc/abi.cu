@@ -1,7 +1,9 @@
 // C-ABI entry points of libsfb.so: descriptor validation, error text, dispatch.
 // The kernels live in the sibling .cu files; nothing here touches device data.
 
+#include <cstdlib>
 #include <cstring>
+#include <ctime>
 #include <mutex>
 #include <utility>
 #include <vector>
@@ -25,6 +27,36 @@ int fail(int status, const char* fmt, ...) {
     vsnprintf(g_error, sizeof(g_error), fmt, ap);
     va_end(ap);
     return status;
+}
+
+int trace_level() {
+    static const int level = [] {
+        const char* v = getenv("SFB_TRACE");
+        return v ? atoi(v) : 0;
+    }();
+    return level;
+}
+
+static double now_us() {
+    timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return ts.tv_sec * 1e6 + ts.tv_nsec * 1e-3;
+}
+
+TraceScope::TraceScope(const char* op_name, void* st, const char* fmt, ...) : op(op_name), stream(static_cast<cudaStream_t>(st)), t0(0.0) {
+    what[0] = 0;
+    if (trace_level() <= 0) return;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(what, sizeof(what), fmt, ap);
+    va_end(ap);
+    t0 = now_us();
+}
+
+TraceScope::~TraceScope() {
+    if (trace_level() <= 0) return;
+    const bool synced = trace_level() >= 2 && cudaStreamSynchronize(stream) == cudaSuccess;
+    fprintf(stderr, "[sfb] %-28s %-56s %9.1f us%s\n", op, what, now_us() - t0, synced ? " (stream synchronised)" : " (enqueue)");
 }
 
 int allow_shared_memory_once(const void* kernel, int smem_bytes) {
@@ -111,6 +143,7 @@ static int decode_impl(const SFBTensor* q, const SFBTensor* k_cache, const SFBTe
                        const SFBTensor* v_scale, const SFBTensor* block_tables, const SFBTensor* seq_lens,
                        const SFBTensor* table_rows, SFBTensor* out, int q_dtype, int kv_dtype, float scale, int64_t chunk_tokens,
                        void* workspace, int64_t workspace_bytes, void* stream, void* const* peer_out, int world, int rank) {
+    SFB_TRACE_OP(world > 0 ? "paged_attention_decode_gather" : "paged_attention_decode", stream, "kv dtype %d chunk %lld", kv_dtype, (long long)chunk_tokens);
     const int qe = dtype_size(q_dtype), kve = dtype_size(kv_dtype);
     if (!qe || q_dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "decode: q dtype %d", q_dtype);
     if (!kve) return fail(SFB_ERR_INVALID_ARG, "decode: kv dtype %d", kv_dtype);
@@ -237,6 +270,7 @@ static int prefill_impl(const SFBTensor* q, const SFBTensor* k_cache, const SFBT
                         const SFBTensor* cu_q, const SFBTensor* ctx_lens, SFBTensor* out, int dtype, float scale, int causal,
                         int64_t max_q_tokens, void* workspace, int64_t workspace_bytes, void* stream, bool clear_status,
                         const SFBTensor* row_limits = nullptr) {
+    SFB_TRACE_OP(row_limits ? "prefill_paged_rows" : "prefill_paged", stream, "dtype %d causal %d max_q %lld", dtype, causal, (long long)max_q_tokens);
     const int e = dtype_size(dtype);
     if (!e || dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "prefill: dtype %d", dtype);
     View vq, vk, vv, vt, vc, vl, vo;
@@ -323,6 +357,7 @@ int sfb_paged_attention_decode_shared_prefix(const SFBTensor* q, const SFBTensor
                                              const SFBTensor* block_tables, const SFBTensor* seq_lens, SFBTensor* out, int dtype,
                                              float scale, int64_t shared_prefix_blocks, int64_t chunk_tokens, void* workspace,
                                              int64_t workspace_bytes, void* stream) {
+    SFB_TRACE_OP("decode_shared_prefix", stream, "prefix blocks %lld chunk %lld", (long long)shared_prefix_blocks, (long long)chunk_tokens);
     const int e = dtype_size(dtype);
     if (dtype != SFB_BF16 && dtype != SFB_F16)
         return fail(SFB_ERR_UNSUPPORTED, "shared-prefix decode: bf16 / fp16 pools only (the prefix runs on the tcgen05 kernel)");
@@ -412,6 +447,7 @@ int sfb_cache_write(const SFBTensor* k_new, const SFBTensor* v_new, const SFBTen
                     SFBTensor* k_scale, SFBTensor* v_scale, SFBTensor* k_tail, SFBTensor* v_tail,
                     const SFBTensor* tail_rows, const SFBTensor* table_rows, int src_dtype, int kv_dtype,
                     int64_t max_new_tokens, void* stream) {
+    SFB_TRACE_OP("cache_write", stream, "src dtype %d pool dtype %d max_new %lld", src_dtype, kv_dtype, (long long)max_new_tokens);
     const int se = dtype_size(src_dtype), kve = dtype_size(kv_dtype);
     if (!se || src_dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "cache_write: source dtype %d", src_dtype);
     if (!kve) return fail(SFB_ERR_INVALID_ARG, "cache_write: pool dtype %d", kv_dtype);
@@ -542,6 +578,7 @@ int sfb_prefill_paged_fp8(const SFBTensor* q, const SFBTensor* k_cache, const SF
                           const SFBTensor* v_scale, const SFBTensor* block_tables, const SFBTensor* cu_q, const SFBTensor* ctx_lens,
                           SFBTensor* out, int q_dtype, float scale, int causal, int64_t max_q_tokens, void* workspace,
                           int64_t workspace_bytes, void* stream) {
+    SFB_TRACE_OP("prefill_paged_fp8", stream, "q dtype %d causal %d max_q %lld", q_dtype, causal, (long long)max_q_tokens);
     if (q_dtype != SFB_BF16 && q_dtype != SFB_F16) return fail(SFB_ERR_UNSUPPORTED, "prefill_fp8: bf16 or fp16 queries");
     View vq, vk, vv, vks, vvs, vt, vl;
     int rc;
@@ -600,6 +637,7 @@ int sfb_fused_rms_norm_matmul_plan(int64_t rows, int64_t cols, int sms, int clus
 
 int sfb_fused_rms_norm_matmul(const SFBTensor* x, const SFBTensor* folded_weight, SFBTensor* out, int dtype, float eps, void* workspace,
                               int64_t workspace_bytes, void* stream) {
+    SFB_TRACE_OP("fused_rms_norm_matmul", stream, "dtype %d eps %g", dtype, (double)eps);
     if (dtype != SFB_BF16 && dtype != SFB_F16) return fail(SFB_ERR_UNSUPPORTED, "fused_rms_norm_matmul: bf16 or fp16 (other types go to the fallback executor)");
     View vx, vw, vo;
     int rc;
@@ -648,6 +686,7 @@ static int quant_views(const SFBTensor* x, const SFBTensor* codes, const SFBTens
 }
 
 int sfb_quantize_fp8(const SFBTensor* x, SFBTensor* codes, SFBTensor* scales, int x_dtype, int granularity, void* stream) {
+    SFB_TRACE_OP("quantize_fp8", stream, "dtype %d granularity %d", x_dtype, granularity);
     View vx, vc, vs;
     int rc = quant_views(x, codes, scales, x_dtype, granularity, "quantize", &vx, &vc, &vs);
     if (rc) return rc;
@@ -657,6 +696,7 @@ int sfb_quantize_fp8(const SFBTensor* x, SFBTensor* codes, SFBTensor* scales, in
 
 int sfb_dequantize_fp8(const SFBTensor* codes, const SFBTensor* scales, SFBTensor* out, int out_dtype, int granularity,
                        void* stream) {
+    SFB_TRACE_OP("dequantize_fp8", stream, "dtype %d granularity %d", out_dtype, granularity);
     View vx, vc, vs;
     int rc = quant_views(out, codes, scales, out_dtype, granularity, "dequantize", &vx, &vc, &vs);
     if (rc) return rc;
@@ -666,6 +706,7 @@ int sfb_dequantize_fp8(const SFBTensor* codes, const SFBTensor* scales, SFBTenso
 
 int sfb_rms_norm(const SFBTensor* x, const SFBTensor* residual, const SFBTensor* weight, SFBTensor* out, int dtype,
                  float eps, void* stream) {
+    SFB_TRACE_OP("rms_norm", stream, "dtype %d residual %d", dtype, residual ? 1 : 0);
     const int e = dtype_size(dtype);
     if (!e || dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "rms_norm: dtype %d", dtype);
     View vx, vr, vw, vo;

@@ -187,6 +187,7 @@ int64_t sfb_attention_dense_workspace_bytes(int64_t batch, int64_t n_heads, int6
 
 int sfb_attention_dense(const SFBTensor* q, const SFBTensor* k, const SFBTensor* v, const SFBTensor* positions, SFBTensor* out, int dtype,
                         float scale, int mask_mode, void* workspace, int64_t workspace_bytes, void* stream) {
+    SFB_TRACE_OP("attention_dense", stream, "dtype %d mask %d", dtype, mask_mode);
     const int e = dtype_size(dtype);
     if (!e || dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "attention_dense: dtype %d", dtype);
     if (mask_mode < SFB_MASK_NONE || mask_mode > SFB_MASK_POSITIONS) return fail(SFB_ERR_INVALID_ARG, "attention_dense: mask mode %d", mask_mode);
@@ -272,6 +273,7 @@ int sfb_attention_dense(const SFBTensor* q, const SFBTensor* k, const SFBTensor*
 
 int sfb_cache_read(const SFBTensor* cache, const SFBTensor* scale, const SFBTensor* block_tables, const SFBTensor* seq_lens, SFBTensor* out,
                    int cache_dtype, int out_dtype, void* status, void* stream) {
+    SFB_TRACE_OP("cache_read", stream, "pool dtype %d -> %d", cache_dtype, out_dtype);
     const int ce = dtype_size(cache_dtype), oe = dtype_size(out_dtype);
     if (!ce || !oe || out_dtype == SFB_F8E4M3) return fail(SFB_ERR_INVALID_ARG, "cache_read: dtypes %d -> %d", cache_dtype, out_dtype);
     const bool fp8 = cache_dtype == SFB_F8E4M3;

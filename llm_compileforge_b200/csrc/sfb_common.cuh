@@ -58,6 +58,21 @@ inline int dtype_size(int dt) {
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// One stderr line per operator call when the environment has SFB_TRACE=1 (host time of the call: validation and
+// enqueue) or SFB_TRACE=2 (the stream is synchronised first, so the time covers the kernels too - it serialises the
+// stream, for debugging only).  The counterpart of the reference's per-step ledger (SERVEFORGE_ACCOUNT,
+// runtime/src/engine/account.rs:1-60) at the granularity this library has: one operator.
+int trace_level();
+struct TraceScope {
+    const char* op;
+    cudaStream_t stream;
+    char what[96];
+    double t0;
+    TraceScope(const char* op_name, void* st, const char* fmt, ...);
+    ~TraceScope();
+};
+#define SFB_TRACE_OP(name, stream, ...) ::sfb::TraceScope sfb_trace_scope__(name, stream, __VA_ARGS__)
+
 // ---------------------------------------------------------------------------
 // Workspace layout of the decode path (shared by the kernels and the size query):
 //   [0, 256)                     status word + padding

@@ -241,3 +241,19 @@ def test_block_manager_rejects_bad_handles_and_arguments():
         assert lib.sfb_bm_allocate(bm, b"a", 6, None, 0) == 2 and lib.sfb_bm_num_free_blocks(bm) == 6
     finally:
         lib.sfb_bm_destroy(bm)
+
+
+def test_trace_line_per_operator_call():
+    """SFB_TRACE=1: one stderr line per operator call (the call here fails validation; the line is printed all the same)."""
+    import subprocess
+    import sys
+
+    code = ("import ctypes; from llm_compileforge_b200 import _lib; lib = _lib.load(); "
+            "rc = lib.sfb_rms_norm(None, None, None, None, 0, ctypes.c_float(1e-5), None); print('rc', rc)")
+    env = dict(os.environ, SFB_TRACE="1", PYTHONPATH=ROOT)
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=ROOT)
+    assert "rc -1" in res.stdout, res.stdout + res.stderr
+    lines = [ln for ln in res.stderr.splitlines() if ln.startswith("[sfb] rms_norm")]
+    assert len(lines) == 1 and "us" in lines[0] and "(enqueue)" in lines[0], res.stderr
+    quiet = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=dict(os.environ, PYTHONPATH=ROOT), cwd=ROOT)
+    assert "[sfb]" not in quiet.stderr
