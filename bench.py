@@ -387,7 +387,7 @@ def _best_of(fn, repeats: int = 3) -> float:
     return best
 
 
-KERNEL_KINDS = ("append", "norm_256", "norm_16384", "prefill", "decode_c2", "decode_c3", "norm_matmul")
+KERNEL_KINDS = ("append", "norm_256", "norm_16384", "prefill", "prefill_fp8", "decode_c2", "decode_c3", "norm_matmul")
 
 
 def kernel_entry(kind: str, iters: int, dev: torch.device, cpu: bool = True) -> dict:
@@ -404,8 +404,8 @@ def kernel_entry(kind: str, iters: int, dev: torch.device, cpu: bool = True) -> 
             r = kb.bench_append(dev, iters)
         elif kind in ("norm_256", "norm_16384"):
             r = kb.bench_norm(dev, iters, int(kind.split("_")[1]))
-        elif kind == "prefill":
-            r = kb.bench_prefill(dev, iters)
+        elif kind in ("prefill", "prefill_fp8"):
+            r = kb.bench_prefill(dev, iters, fp8=kind == "prefill_fp8")
         elif kind in ("decode_c2", "decode_c3"):
             r = kb.bench_decode(dev, iters, wl.C2 if kind == "decode_c2" else wl.C3)
         elif kind == "norm_matmul":
@@ -438,7 +438,7 @@ def kernel_entry(kind: str, iters: int, dev: torch.device, cpu: bool = True) -> 
         sec = _best_of(lambda: ref.rms_norm_hal(x, w, eps))
         value = wl.rms_norm_algorithmic_bytes(rows, 4096, 2) / sec / 1e9
         sample = f"the same [{rows}, 4096] bf16 rows, best of 3, {sec:.4f} s"
-    elif kind == "prefill":
+    elif kind in ("prefill", "prefill_fp8"):
         pw = wl.make_prefill_workload(n_requests=1)
         rid = next(iter(pw.block_tables))
         sec = _best_of(lambda: ref.chunked_prefill(pw.q, pw.k_cache, pw.v_cache, pw.block_tables[rid], pw.ctx_lens[rid], scale=pw.scale))

@@ -6,7 +6,8 @@
 // scratch pool [R * max_blocks, 16, Hkv, D] of the query's 16-bit type (value = code * scale, one rounding; every e4m3
 // value is exact in bf16 and fp16, the scale multiplication is what rounds) with identity tables, and the ordinary
 // prefill runs on that.  One pass of 1 byte read + 2 bytes written per attended element, small beside the attention
-// itself; a shared prefix is expanded once per request.  Bad block ids are flagged and expand to zeros.
+// itself; blocks that a request shares with request 0 at the same table position (a common prompt prefix) are expanded
+// once.  Bad block ids are flagged and expand to zeros.
 
 #include "sfb_common.cuh"
 
@@ -35,9 +36,17 @@ __global__ void __launch_bounds__(256) expand_fp8_blocks_kernel(ExpandArgs a) {
     if (ctx > a.max_blocks * 16) ctx = a.max_blocks * 16;
     const int used = (ctx + 15) >> 4;
     const int64_t slot = (int64_t)r * a.max_blocks + b;
-    if (which == 0 && threadIdx.x == 0) a.tables_out[slot] = (int32_t)slot;
-    if (b >= used) return;  // never read by the attention
-    const int64_t phys = a.tables[(int64_t)r * a.table_stride + b];
+    const int64_t phys = b < used ? (int64_t)a.tables[(int64_t)r * a.table_stride + b] : -1;
+    // A block that request 0 holds at the same table position (a radix-shared prefix, runtime/src/cache/block.rs:214-232:
+    // the same physical ids head every table) is expanded once, by request 0; the other requests' tables point at its copy.
+    bool shared = false;
+    if (r > 0 && b < used) {
+        int ctx0 = a.ctx_lens[0];
+        if (ctx0 > a.max_blocks * 16) ctx0 = a.max_blocks * 16;
+        shared = b < ((ctx0 + 15) >> 4) && a.tables[b] == phys;
+    }
+    if (which == 0 && threadIdx.x == 0) a.tables_out[slot] = shared ? b : (int32_t)slot;
+    if (b >= used || shared) return;  // never read by the attention / already there
     const bool ok = phys >= 0 && phys < a.n_pool_blocks;
     if (!ok && a.status && threadIdx.x == 0) atomicOr(a.status, SFB_STATUS_BAD_BLOCK_ID);
     const int cpr = a.head_dim / 16;                 // 16-code pieces per (token, head) row

@@ -1,7 +1,7 @@
 """Per-kernel measurements for the hot path's other kernels (one JSON line each).
 
     python -m llm_compileforge_b200.kernel_bench [--iters 20] [--chunk-tokens 0] \
-        [--only prefill,norm_matmul,append,norm,decode_c2,decode_c3,shared_prefix]
+        [--only prefill,prefill_fp8,norm_matmul,append,norm,decode_c2,decode_c3,shared_prefix]
 
 ``bench.py`` at the repository root reports the headline decode metric; this
 module times the remaining kernels on their configurations with CUDA events
@@ -75,9 +75,14 @@ def time_ms_graph(fn, iters: int, warmup: int = 3, flush=None) -> float:
     return time_ms(graph.replay, iters, warmup=2, flush=flush)
 
 
-def bench_prefill(dev, iters):
+def bench_prefill(dev, iters, fp8: bool = False):
+    """Config 4; with ``fp8`` the pool holds e4m3 codes + per-(block, kv head) scales and the call includes their expansion."""
     pw = wl.make_prefill_workload()  # config 4: 32 requests, 2048 shared prefix + 512 chunk, H 32/8, D 128, bf16
     q, k, v = pw.q.to(dev), pw.k_cache.to(dev), pw.v_cache.to(dev)
+    scales = {}
+    if fp8:
+        (k, ks), (v, vs) = ops.quantize_fp8(k, per_block_head=True), ops.quantize_fp8(v, per_block_head=True)
+        scales = dict(k_scale=ks, v_scale=vs)
     rids = list(pw.block_tables)
     width = max(len(t) for t in pw.block_tables.values())
     tables = torch.zeros((len(rids), width), dtype=torch.int32)
@@ -86,14 +91,17 @@ def bench_prefill(dev, iters):
     tables = tables.to(dev)
     cu = (torch.arange(len(rids) + 1, dtype=torch.int32) * pw.chunk_len).to(dev)
     ctx = torch.full((len(rids),), pw.prefix_len + pw.chunk_len, dtype=torch.int32, device=dev)
-    ws = torch.zeros(ops.prefill_workspace_bytes(q.shape[0]), dtype=torch.uint8, device=dev)
+    ws_bytes = (ops.prefill_fp8_workspace_bytes(q.shape[0], len(rids), width, k.shape[2], k.shape[3]) if fp8
+                else ops.prefill_workspace_bytes(q.shape[0]))
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)
     out = torch.empty_like(q)
-    fn = lambda: ops.prefill_paged(q, k, v, tables, cu, ctx, max_q_tokens=pw.chunk_len, scale=pw.scale, workspace=ws, out=out)
+    fn = lambda: ops.prefill_paged(q, k, v, tables, cu, ctx, max_q_tokens=pw.chunk_len, scale=pw.scale, workspace=ws, out=out, **scales)
     ms = time_ms(fn, iters, flush=L2Flush(dev))
     flops = wl.prefill_flops(len(rids), pw.n_heads, pw.head_dim, pw.chunk_len, pw.prefix_len)
     p = _peaks()
     tf = flops / (ms / 1e3) / 1e12
-    return {"kernel": "prefill_tcgen05", "workload": "config 4: 32 requests, 2048-token shared prefix + 512-token chunk, H 32/8, D 128, bf16",
+    return {"kernel": "prefill_tcgen05" + (" after expand_fp8_blocks" if fp8 else ""),
+            "workload": "config 4: 32 requests, 2048-token shared prefix + 512-token chunk, H 32/8, D 128, " + ("bf16 queries over an e4m3 pool" if fp8 else "bf16"),
             "ms": ms, "flops": flops, "achieved_tflops": tf, "peak_tflops": p["bf16_tflops"],
             "frac": tf / p["bf16_tflops"], "frac_of_sustained": tf / p["bf16_tflops_sustained"], "peak_kind": p["kind"],
             "status": ops.read_status(ws)}
@@ -242,6 +250,8 @@ def main() -> None:
     sys.path.insert(0, ROOT)
     if "prefill" in which:
         print(json.dumps(bench_prefill(dev, args.iters)), flush=True)
+    if "prefill_fp8" in which:
+        print(json.dumps(bench_prefill(dev, args.iters, fp8=True)), flush=True)
     if "norm_matmul" in which:
         print(json.dumps(bench_norm_matmul(dev, args.iters)), flush=True)
         print(json.dumps(bench_norm_matmul(dev, args.iters, m=256)), flush=True)

@@ -324,11 +324,19 @@ def test_chunked_prefill_over_fp8_pool(cuda, dtype):
         sc_v = torch.ones_like(sc_k)
         slab_k[:, 1], slab_v[:, 1] = kc.to(cuda), vc.to(cuda)
         sc_k[:, 1], sc_v[:, 1] = ks.to(cuda), vs.to(cuda)
-        q = torch.randn((sum(chunk.values()), h, d), generator=g).to(dtype)
-        out = pkg.chunked_prefill(q.to(cuda), slab_k[:, 1], slab_v[:, 1], tables, ctx, chunk, k_scale=sc_k[:, 1], v_scale=sc_v[:, 1])
-        at = 0
-        for rid in tables:
-            n = chunk[rid]
-            want = ref.chunked_prefill(q[at : at + n].float(), k_deq, v_deq, tables[rid], ctx[rid])
-            assert_half_close_ulp(out[rid].cpu(), want.to(dtype), what=f"fp8 prefill {rid} D {d} {dtype}")
-            at += n
+        q_of = {rid: torch.randn((chunk[rid], h, d), generator=g).to(dtype) for rid in tables}
+        # the blocks a request shares with the FIRST request of the batch are expanded once: a long and a short first request
+        # must give every request the same bytes
+        first = None
+        for order in (("a", "b", "c"), ("c", "b", "a")):
+            tb = {r: tables[r] for r in order}
+            q = torch.cat([q_of[r] for r in order])
+            out = pkg.chunked_prefill(q.to(cuda), slab_k[:, 1], slab_v[:, 1], tb, ctx, chunk, k_scale=sc_k[:, 1], v_scale=sc_v[:, 1])
+            if first is None:
+                first = {r: out[r].clone() for r in order}
+                for rid in order:
+                    want = ref.chunked_prefill(q_of[rid].float(), k_deq, v_deq, tables[rid], ctx[rid])
+                    assert_half_close_ulp(out[rid].cpu(), want.to(dtype), what=f"fp8 prefill {rid} D {d} {dtype}")
+            else:
+                for rid in order:
+                    assert torch.equal(out[rid], first[rid]), f"request {rid} differs when the batch is reordered (D {d})"
