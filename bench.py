@@ -688,10 +688,14 @@ def main() -> None:
     # one step at a time (submit, then wait for its result), then with IN_FLIGHT steps in flight.
     from llm_compileforge_b200.step_pipeline import AttentionStepPipeline
 
-    host_q = st.q.cpu().pin_memory()
-    host_k, host_v = st.new_k.cpu().pin_memory(), st.new_v.cpu().pin_memory()
+    in_flight_max = IN_FLIGHT + (1 if world >= 4 else 0)  # one more step in flight when several ranks share the host's links
     pipe = AttentionStepPipeline(st.bm, st.k_cache, st.v_cache, max_batch=st.batch, n_heads=shape.n_heads, dtype=shape.dtype,
-                                 chunk_tokens=chunk, depth=IN_FLIGHT, **fp8kw, **tailkw)
+                                 chunk_tokens=chunk, depth=in_flight_max, time_copies=True, **fp8kw, **tailkw)
+    # one pinned arena per rank, laid out like the pipeline's staging slot: q | new K | new V go over in a single copy
+    host_packed, host_q, host_k, host_v = pipe.host_arena()
+    host_q.copy_(st.q)
+    host_k.copy_(st.new_k)
+    host_v.copy_(st.new_v)
     sync_all()
 
     def run_e2e(first: int, n: int, in_flight: int) -> tuple[float, int, int]:
@@ -700,7 +704,7 @@ def main() -> None:
         t0.record()
         pending: list[int] = []
         for i in range(n):
-            pending.append(pipe.submit(st.rids, host_q, host_k, host_v, st.pos_steps_host[first + i]))
+            pending.append(pipe.submit(st.rids, host_q, host_k, host_v, st.pos_steps_host[first + i], packed=host_packed))
             h2d += pipe.h2d_bytes
             d2h += pipe.d2h_bytes
             if len(pending) >= in_flight:
@@ -717,16 +721,22 @@ def main() -> None:
     serial_ms, _, _ = run_e2e(off + args.warmup, args.steps, 1)
     sync_all()
     off += total_steps
-    run_e2e(off, args.warmup, IN_FLIGHT)
+    run_e2e(off, args.warmup, in_flight_max)
     sync_all()
-    e2e_ms, h2d, d2h = run_e2e(off + args.warmup, args.steps, IN_FLIGHT)
+    pipe.h2d_ms = pipe.d2h_ms = 0.0
+    pipe.h2d_timed = pipe.d2h_timed = 0
+    e2e_ms, h2d, d2h = run_e2e(off + args.warmup, args.steps, in_flight_max)
     sync_all()
     status |= pipe.status()
+    # device time of the copies themselves in the pipelined pass (CUDA events on the copy streams)
+    h2d_gbs = pipe.h2d_timed / max(pipe.h2d_ms, 1e-9) / 1e6
+    d2h_gbs = pipe.d2h_timed / max(pipe.d2h_ms, 1e-9) / 1e6
 
     if world > 1:
-        t = torch.tensor([elapsed_ms, e2e_ms, decode_ms, serial_ms], dtype=torch.float64, device=dev)
+        t = torch.tensor([elapsed_ms, e2e_ms, decode_ms, serial_ms, -h2d_gbs, -d2h_gbs], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_ms, decode_ms, serial_ms = t.tolist()
+        elapsed_ms, e2e_ms, decode_ms, serial_ms = t.tolist()[:4]
+        h2d_gbs, d2h_gbs = -t[4].item(), -t[5].item()  # the slowest rank's copy rates
         tot = torch.tensor([st.batch], dtype=torch.int64, device=dev)
         dist.all_reduce(tot)
         total_requests = st.batch if by_head else int(tot.item())
@@ -770,7 +780,8 @@ def main() -> None:
                          "kernel": "decode_tma_kernel (split-K, in-kernel merge)", "algorithmic_bytes_per_launch": alg,
                          "avg_launch_ms": decode_ms},
             "e2e": {"value": total_requests / (e2e_ms / args.steps / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "steps_in_flight": IN_FLIGHT,
+                    "d2h_bytes_per_step": d2h, "steps_in_flight": in_flight_max,
+                    "h2d_gbs_per_rank": h2d_gbs, "d2h_gbs_per_rank": d2h_gbs,
                     "one_step_at_a_time": total_requests / (serial_ms / args.steps / 1e3),
                     "table_upload": "device-resident tables; only ids of added blocks are sent", "host_binding": host_binding},
             # per step: cache_write_kernel + decode_tma_kernel (split merge is in-kernel), + decode_worklist_kernel when the

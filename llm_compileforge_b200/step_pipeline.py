@@ -40,6 +40,9 @@ class _Slot:
     copied_in: torch.cuda.Event
     computed: torch.cuda.Event
     copied_out: torch.cuda.Event
+    arena: torch.Tensor | None = None     # q | k | v staging as one byte range (a single copy fills it when the host side is laid out alike)
+    in_begin: torch.cuda.Event | None = None   # with time_copies: the copies' own device time
+    out_begin: torch.cuda.Event | None = None
     busy: bool = False
     n: int = 0
 
@@ -50,7 +53,7 @@ class AttentionStepPipeline:
     def __init__(self, block_manager: BlockManager, k_cache: torch.Tensor, v_cache: torch.Tensor, *, max_batch: int,
                  n_heads: int, dtype: torch.dtype, k_scale: torch.Tensor | None = None, v_scale: torch.Tensor | None = None,
                  k_tail: torch.Tensor | None = None, v_tail: torch.Tensor | None = None, scale: float | None = None,
-                 chunk_tokens: int = 0, depth: int = 2):
+                 chunk_tokens: int = 0, depth: int = 2, time_copies: bool = False):
         assert block_manager.device_tables is not None, "attach_device_tables() first"
         self.bm = block_manager
         self.tables = block_manager.device_tables
@@ -71,17 +74,25 @@ class AttentionStepPipeline:
                                      dtype=torch.uint8, device=self.dev)
         self.cu_one = torch.arange(max_batch + 1, dtype=torch.int32, device=self.dev)
 
+        self.time_copies = bool(time_copies)
+        self.h2d_ms = self.d2h_ms = 0.0   # device time of the copies of the steps whose result() was taken (time_copies)
+        self.h2d_timed = self.d2h_timed = 0  # bytes those times cover
+        esz = torch.empty((), dtype=dtype).element_size()
+        nq, nk = max_batch * n_heads * d * esz, max_batch * hkv * d * esz
+
         def slot() -> _Slot:
-            ev = lambda: torch.cuda.Event()
+            ev = lambda: torch.cuda.Event(enable_timing=self.time_copies)
+            arena = torch.empty(nq + 2 * nk, dtype=torch.uint8, device=self.dev)
             return _Slot(
-                q=torch.empty((max_batch, n_heads, d), dtype=dtype, device=self.dev),
-                k=torch.empty((max_batch, hkv, d), dtype=dtype, device=self.dev),
-                v=torch.empty((max_batch, hkv, d), dtype=dtype, device=self.dev),
+                q=arena[:nq].view(dtype).view(max_batch, n_heads, d),
+                k=arena[nq : nq + nk].view(dtype).view(max_batch, hkv, d),
+                v=arena[nq + nk :].view(dtype).view(max_batch, hkv, d),
                 meta=torch.empty((3, max_batch), dtype=torch.int32, device=self.dev),
                 meta_host=torch.empty((3, max_batch), dtype=torch.int32).pin_memory(),
                 out=torch.empty((max_batch, n_heads, d), dtype=dtype, device=self.dev),
                 out_host=torch.empty((max_batch, n_heads, d), dtype=dtype).pin_memory(),
-                copied_in=ev(), computed=ev(), copied_out=ev())
+                copied_in=ev(), computed=ev(), copied_out=ev(), arena=arena,
+                in_begin=ev() if self.time_copies else None, out_begin=ev() if self.time_copies else None)
 
         self.slots = [slot() for _ in range(depth)]
         self.submitted = 0
@@ -92,10 +103,11 @@ class AttentionStepPipeline:
         self.d2h_bytes = 0
 
     def submit(self, request_ids: Sequence[str], q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
-               positions: torch.Tensor) -> int:
+               positions: torch.Tensor, packed: torch.Tensor | None = None) -> int:
         """Queue one decode step.  ``q [B,H,D]``, ``k_new / v_new [B,Hkv,D]`` and ``positions [B]`` (int32: where each
         request's new token goes; it then attends to ``positions + 1`` tokens) are host tensors, pinned for the
-        copies to be asynchronous.  Returns a ticket for :meth:`result`."""
+        copies to be asynchronous.  ``packed``: the same q, k_new, v_new as ONE pinned uint8 buffer (q's bytes, then k's,
+        then v's - see :meth:`host_arena`); a full batch then goes over in a single copy.  Returns a ticket for :meth:`result`."""
         n = len(request_ids)
         ticket = self.submitted
         s = self.slots[ticket % len(self.slots)]
@@ -114,9 +126,14 @@ class AttentionStepPipeline:
         # host's table work below runs while the copies are already moving
         self.copy_in.wait_event(s.computed)
         with torch.cuda.stream(self.copy_in):
-            s.q[:n].copy_(q, non_blocking=True)
-            s.k[:n].copy_(k_new, non_blocking=True)
-            s.v[:n].copy_(v_new, non_blocking=True)
+            if s.in_begin is not None:
+                s.in_begin.record()
+            if packed is not None and n == s.q.shape[0]:  # q | k | v back to back in one pinned buffer: one copy instead of three
+                s.arena.copy_(packed, non_blocking=True)
+            else:
+                s.q[:n].copy_(q, non_blocking=True)
+                s.k[:n].copy_(k_new, non_blocking=True)
+                s.v[:n].copy_(v_new, non_blocking=True)
             s.meta.copy_(s.meta_host, non_blocking=True)
             s.copied_in.record()
         # host: grow the tables to cover the new token (runtime/src/engine/scheduler.rs:239-246), queue the delta
@@ -134,6 +151,8 @@ class AttentionStepPipeline:
             s.computed.record()
         self.copy_out.wait_event(s.computed)
         with torch.cuda.stream(self.copy_out):
+            if s.out_begin is not None:
+                s.out_begin.record()
             s.out_host[:n].copy_(s.out[:n], non_blocking=True)
             s.copied_out.record()
         s.busy, s.n = True, n
@@ -143,11 +162,26 @@ class AttentionStepPipeline:
         self.d2h_bytes = q.numel() * e
         return ticket
 
+    def host_arena(self) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+        """A pinned buffer laid out like a staging slot: ``(packed uint8, q [B,H,D], k [B,Hkv,D], v [B,Hkv,D])`` views of it, for
+        callers that fill their step inputs in place and pass ``packed`` to :meth:`submit`."""
+        s = self.slots[0]
+        packed = torch.empty(s.arena.numel(), dtype=torch.uint8).pin_memory()
+        nq, nk = s.q.numel() * s.q.element_size(), s.k.numel() * s.k.element_size()
+        return (packed, packed[:nq].view(s.q.dtype).view(s.q.shape), packed[nq : nq + nk].view(s.k.dtype).view(s.k.shape),
+                packed[nq + nk :].view(s.v.dtype).view(s.v.shape))
+
     def result(self, ticket: int) -> torch.Tensor:
         """Host tensor ``[B,H,D]`` of a submitted step (valid until ``depth`` more steps were submitted)."""
         assert self.submitted - len(self.slots) <= ticket < self.submitted, "ticket no longer in flight"
         s = self.slots[ticket % len(self.slots)]
         s.copied_out.synchronize()
+        if self.time_copies and s.busy:
+            self.h2d_ms += s.in_begin.elapsed_time(s.copied_in)
+            self.d2h_ms += s.out_begin.elapsed_time(s.copied_out)
+            e = s.q.element_size()
+            self.h2d_timed += (s.n * (s.q.shape[1] + 2 * s.k.shape[1]) * s.q.shape[2]) * e + s.meta_host.numel() * 4
+            self.d2h_timed += s.n * s.q.shape[1] * s.q.shape[2] * e
         s.busy = False
         return s.out_host[: s.n]
 
