@@ -9,32 +9,34 @@
 // physical blocks at the head of several tables.  GQA: query head h reads kv
 // head h / (H / Hkv).
 //
-// One thread block = 256 query tokens (two 128-row tiles) of one (request, query head), five warpgroups:
-//   warps 0-15 softmax, eight warps per query tile, two threads per query row (64 key columns each; a warp
-//             can only reach its own 32 tensor-memory lanes, so warps w and w+4 share lanes and split the
-//             columns).  With two warps per SM sub-partition on a tile, one warp's FMA / pack instructions
-//             issue while the other's ex2 occupy the XU pipe.  A thread reads its 64 scores ONCE
-//             (tcgen05.ld into registers; the softmax warpgroups raise their register allowance with
-//             setmaxnreg, the fifth warpgroup lowers its own), swaps half-row maxima with its partner
-//             through shared memory under a 64-thread named barrier, keeps running max / sum in log2
-//             units, writes P as bf16/fp16 over its own S columns in two halves so that the P.V product
-//             starts on the first half while the second is still being computed, rescales O in tensor
-//             memory only when the max grew by more than 2^8 (the stale max stays exact in fp32), adds the
-//             partial sums in the epilogue and writes O / l.
-//   warp 16   TMA producer: both Q tiles once, then per 128-token KV tile sixteen
-//             [16 tokens x 128 B] boxes for K and sixteen for V, two stages each
-//   warp 17   issues tcgen05.mma: S_t = Q_t K^T (128x128x128, both operands K-major
-//             in 128B-swizzled shared memory) and O_t += P_t V with P_t read from
-//             tensor memory and V as an MN-major shared-memory operand, alternating
-//             between the two query tiles so that one tile's MMAs run while the
-//             other tile's rows are in the softmax warps
-//   warp 18   clears the V rows past the context in the last KV tile (a pool that was never
-//             zero-filled may hold NaN patterns there, and 0 * NaN would reach O)
+// A work item is 256 query tokens (two 128-row tiles) of one (request, query head).  The grid is one resident thread block per
+// SM; a block takes items blockIdx.x, blockIdx.x + gridDim.x, ... of a list ordered heaviest first, and runs them as ONE
+// pipeline: the K / V tiles of consecutive items form a single stream through the two-slot rings, the next item's Q tiles
+// land as soon as the current item's last Q.K^T has read the old ones, and the next item's first Q.K^T is issued in the place
+// of the step's usual next score tile - the tensor pipe keeps running while the softmax warps write an item's rows out.
+// Twenty warps (five warpgroups):
+//   warp 0    issues tcgen05.mma (one thread): S_t = Q_t K^T (128x128x128, both operands K-major in 128B-swizzled shared
+//             memory) and O_t += P_t V with P_t read from tensor memory and V as an MN-major shared-memory operand,
+//             alternating between the two query tiles so that one tile's MMAs run while the other's rows are in the softmax warps
+//   warp 1    TMA producer for Q and K: per 128-token KV tile sixteen [16 tokens x 128 B] boxes (block table entries are
+//             fetched two tiles ahead; entries past the context become an out-of-range block index, which TMA zero-fills)
+//   warp 2    TMA producer for V: eight [2 halves x 16 tokens x 128 B] boxes per tile; it also clears the V rows past the
+//             context in the last KV tile (a pool that was never zero-filled may hold NaN there, and 0 * NaN would reach O)
+//   warp 3    scheduler: works out each item's geometry (request offsets and lengths from global memory) ahead of time and
+//             hands it to the other nineteen warps through a four-slot ring in shared memory
+//   warps 4-19 softmax, eight warps per query tile, two threads per query row (64 key columns each; a warp can only reach its
+//             own 32 tensor-memory lanes, so warps w and w+4 share lanes and split the columns).  A thread reads its 64
+//             scores ONCE (tcgen05.ld into registers; the softmax warpgroups raise their register allowance with setmaxnreg,
+//             the first warpgroup lowers its own), swaps half-row maxima with its partner through shared memory under a
+//             64-thread named barrier, keeps running max / sum in log2 units, writes P as bf16/fp16 over its own S columns,
+//             rescales O in tensor memory only when the max grew by more than 2^8 (the stale max stays exact in fp32), adds
+//             the partial sums in the epilogue and writes O / l.
 // Tensor memory: per query tile S|P (128 columns) and O (128) = 512 columns in all.
-// Bound: tensor pipe (4*D*Sq*Skv flops per head against ~1.4 PFLOP/s dense).
+// Bound: tensor pipe (4*D*Sq*Skv flops per head); every wait is bounded and reports SFB_STATUS_WAIT_TIMEOUT.
 
 #include <cuda.h>
 
+#include <algorithm>
 #include <mutex>
 #include <type_traits>
 
@@ -49,8 +51,7 @@ constexpr int kHeadDim = 128;
 constexpr int kSubBytes = kTileKV * 128;     // one [128 rows][128 B] swizzled sub-tile
 constexpr int kTileBytes = 2 * kSubBytes;    // D = 128 16-bit values = two sub-tiles
 constexpr int kThreads = 640;  // 2 x 8 softmax warps (one group per query tile) + a warpgroup with the TMA, MMA and fix-up warps
-constexpr int kMmaWarp = 0, kTmaWarp = 1, kTmaWarpV = 2, kFirstSoftmaxWarp = 4;
-constexpr int kPParts = 1;  // P is handed to the MMA thread in this many parts per KV tile (1 or 2)
+constexpr int kMmaWarp = 0, kTmaWarp = 1, kTmaWarpV = 2, kSchedWarp = 3, kFirstSoftmaxWarp = 4;
 constexpr uint32_t kSpin = 1u << 21;  // bounded waits: a stuck pipeline gives up (status bit) within about a second
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;    // log2 units
@@ -76,6 +77,9 @@ struct PrefillArgs {
     float* part_ml;
     const int32_t* part_seq_lens;
     int part_n_chunks, part_chunk_tokens, part_max_tokens;
+    int q_blocks;             // 256-row query blocks of the longest chunk
+    int n_items;              // q_blocks * n_heads * n_requests work items
+    int out_vec8;             // output rows allow 32-byte stores
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -213,20 +217,26 @@ __host__ __device__ constexpr uint32_t instr_desc(bool bf16, bool b_mn_major, in
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// barrier slots.  Ring slot j&1 of K holds K(j), of V holds V(j); the MMA step j needs V(j) and K(j+1), so one
-// "full" / "empty" pair per step parity covers V slot j&1 together with K slot (j+1)&1.
+// barrier slots.  The KV tiles of all work items of a thread block form ONE stream of steps g = 0, 1, ...: ring slot g&1 of
+// K holds K(g), of V holds V(g); step g needs V(g) and K(g+1) (the next tile's scores, or the first tile of the next item), so
+// one "full" / "empty" pair per step parity covers V slot g&1 together with K slot (g+1)&1.
 enum {
-    B_Q_FULL = 0,    // both Q tiles and K(0)
-    B_KV_FULL = 1,   // +step parity: V(j) and K(j+1) have landed (one arrival per producer warp)
-    B_KV_EMPTY = 3,  // +step parity: every MMA that read them is complete
-    B_S_FULL = 5,    // +query tile
-    B_P_FULL = 7,    // +2 * query tile + half: keys 0-31 of both column halves, then keys 32-63
-    B_PV_DONE = 11,  // +query tile: the tile's last P.V product is complete
-    B_V_FIXED = 13,  // the last KV tile's V rows past the context are cleared
-    B_COUNT = 14
+    B_Q_FULL = 0,    // +query tile: the tile's Q rows have landed (tile 0 of the first item: and K(0))
+    B_Q_EMPTY = 2,   // +query tile: the item's last Q.K^T of the tile is complete, the next item's rows may land
+    B_KV_FULL = 4,   // +step parity: V(g) and K(g+1) have landed (one arrival per producer warp)
+    B_KV_EMPTY = 6,  // +step parity: every MMA that read them is complete
+    B_S_FULL = 8,    // +query tile
+    B_P_FULL = 10,   // +query tile: P is in tensor memory (eight warps arrive)
+    B_PV_DONE = 12,  // +query tile: the item's last P.V product of the tile is complete
+    B_V_FIXED = 14,  // the last KV tile's V rows past the context are cleared
+    B_FINAL = 15,    // every MMA and every commit of this thread block is complete
+    B_ITEM_FULL = 16,   // +ring slot: the scheduler warp has written the item record
+    B_ITEM_EMPTY = 20,  // +ring slot: all nineteen consumer warps have read it
+    B_COUNT = 24
 };
-constexpr int kXchFloats = 2 * 2 * 2 * kTileQ;  // [step parity][query tile][column half][row]
-constexpr int kSmemBytes = 6 * kTileBytes + B_COUNT * 8 + 16 + kXchFloats * 4 + 1024;  // 2 Q tiles, 2 K stages, 2 V stages
+constexpr int kItemSlots = 4, kItemConsumers = 19;  // K, V, MMA and sixteen softmax warps
+constexpr int kXchFloats = 2 * 2 * 2 * kTileQ;  // [exchange parity][query tile][column half][row]
+constexpr int kSmemBytes = 6 * kTileBytes + B_COUNT * 8 + 16 + kXchFloats * 4 + kItemSlots * 64 + 1024;  // 2 Q tiles, 2 K stages, 2 V stages
 
 // Tensor-memory columns of query tile t: S (fp32, 128 columns) at t*256, with P (16-bit pairs,
 // 64 columns) written over its first half once the row has been read; O (fp32) at t*256 + 128.
@@ -235,40 +245,79 @@ constexpr uint32_t kColO = 128;
 
 // Register allowances after the role split (five warpgroups of 128 threads; the kernel is compiled for
 // 65536 / 640 -> 96 registers per thread, and shared memory admits one thread block per SM, so the block may
-// grow into the rest of the register file): 4 * 128 * kSoftmaxRegs + 128 * kOtherRegs <= 65536, and the first
-// warpgroup lowers its allowance before the others can finish raising theirs.
+// grow into the rest of the register file): 4 * 128 * kSoftmaxRegs + 128 * kOtherRegs <= 640 * 96 - a split that
+// asks for more than the block owned at launch never returns from setmaxnreg.inc.
 constexpr int kSoftmaxRegs = 104;
 constexpr int kOtherRegs = 64;
+
+// One work item: 256 query rows (two 128-row tiles) of one (request, query head).
+struct Item {
+    int req, head, q_begin, q0, n_q, ctx;
+    int rows[2], tiles[2], n_tiles;
+    bool valid;
+};
+
+// Items are numbered heaviest first (the last query block of every request, all heads, then the block before ...); a thread
+// block takes items blockIdx.x, blockIdx.x + gridDim.x, ...  `idx` moves to the first item at or after it that has work.
+__device__ __forceinline__ Item find_item(const PrefillArgs& a, int& idx, const int* limit_max, bool report) {
+    Item it;
+    it.valid = false;
+    const int per_rank = a.n_heads * a.n_requests;
+    for (; idx < a.n_items; idx += gridDim.x) {
+        const int rank = idx / per_rank, rem = idx - rank * per_rank;
+        it.req = rem / a.n_heads;
+        it.head = rem - it.req * a.n_heads;
+        it.q_begin = a.cu_q ? a.cu_q[it.req] : 0;
+        it.n_q = a.cu_q ? a.cu_q[it.req + 1] - it.q_begin : a.fixed_nq;
+        const int qb = (it.n_q + 2 * kTileQ - 1) / (2 * kTileQ) - 1 - rank;
+        if (qb < 0) continue;
+        int ctx = a.cu_q ? a.ctx_lens[it.req] : a.fixed_ctx;
+        if (ctx > a.max_blocks * 16) ctx = a.max_blocks * 16;
+        if ((a.causal && !a.row_limits && ctx < it.n_q) || it.n_q <= 0 || ctx <= 0) {  // inconsistent request: flag it, write nothing
+            if (report && a.status) atomicOr(a.status, SFB_STATUS_EMPTY_REQUEST);
+            continue;
+        }
+        it.ctx = ctx;
+        it.q0 = qb * 2 * kTileQ;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            it.rows[t] = max(0, min(kTileQ, it.n_q - it.q0 - t * kTileQ));
+            const int last_pos = a.row_limits ? max(limit_max[t], 1) - 1
+                                 : a.causal   ? ctx - it.n_q + it.q0 + t * kTileQ + it.rows[t] - 1
+                                              : ctx - 1;
+            it.tiles[t] = it.rows[t] > 0 ? last_pos / kTileKV + 1 : 0;
+        }
+        it.n_tiles = max(it.tiles[0], it.tiles[1]);
+        it.valid = true;
+        return it;
+    }
+    return it;
+}
 
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                        const __grid_constant__ CUtensorMap vmap, const PrefillArgs a) {
     extern __shared__ uint8_t smem_raw[];
-    const int req = blockIdx.z, head = blockIdx.y;
-    const int q_begin = a.cu_q ? a.cu_q[req] : 0, n_q = a.cu_q ? a.cu_q[req + 1] - q_begin : a.fixed_nq;
-    // heaviest blocks (latest queries) first
-    const int q_blocks = (n_q + 2 * kTileQ - 1) / (2 * kTileQ);
-    const int qb = q_blocks - 1 - (int)blockIdx.x;
-    if (qb < 0) return;
-    int ctx = a.cu_q ? a.ctx_lens[req] : a.fixed_ctx;
-    if (ctx > a.max_blocks * 16) ctx = a.max_blocks * 16;
-    if ((a.causal && !a.row_limits && ctx < n_q) || n_q <= 0 || ctx <= 0) {  // inconsistent request: flag it, write nothing
-        if (a.status && threadIdx.x == 0) atomicOr(a.status, SFB_STATUS_EMPTY_REQUEST);
-        return;
-    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int q0 = qb * 2 * kTileQ;                       // first query row of the block
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
     uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + 6 * kTileBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
     int* limit_max = reinterpret_cast<int*>(tmem_slot + 1);  // [2]: with row limits, the largest limit of each query tile
     float* xch = reinterpret_cast<float*>(tmem_slot + 4);
-    int my_limit = 0;
-    if (a.row_limits) {  // one row per thread of the first eight warps; the tiles' maxima go through shared memory
+    int* item_ring = reinterpret_cast<int*>(xch + kXchFloats);  // [kItemSlots][16]
+    if (a.row_limits) {
+        // Row limits: the grid has one thread block per item (the tile counts depend on the rows' limits, which takes the
+        // whole block to reduce).  One row per thread of the first eight warps; the tiles' maxima go through shared memory.
+        int idx = blockIdx.x;
+        limit_max[0] = limit_max[1] = 1;
+        const Item it = find_item(a, idx, limit_max, false);
+        __syncthreads();
+        int my_limit = 0;
         if (threadIdx.x < 2 * kTileQ) {
-            if (q0 + (int)threadIdx.x < n_q) my_limit = min(max(a.row_limits[q_begin + q0 + threadIdx.x], 0), ctx);
+            if (it.valid && idx == (int)blockIdx.x && it.q0 + (int)threadIdx.x < it.n_q)
+                my_limit = min(max(a.row_limits[it.q_begin + it.q0 + threadIdx.x], 0), it.ctx);
             const int wmax = __reduce_max_sync(0xffffffffu, my_limit);
             if (lane == 0) reinterpret_cast<int*>(xch)[warp] = wmax;
         }
@@ -277,38 +326,27 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             const int* w = reinterpret_cast<const int*>(xch) + 4 * threadIdx.x;
             limit_max[threadIdx.x] = max(max(w[0], w[1]), max(w[2], w[3]));
         }
-        __syncthreads();
     }
-    int rows_t[2], tiles_t[2];
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-        rows_t[t] = max(0, min(kTileQ, n_q - q0 - t * kTileQ));
-        const int last_pos = a.row_limits ? max(limit_max[t], 1) - 1 : a.causal ? ctx - n_q + q0 + t * kTileQ + rows_t[t] - 1 : ctx - 1;
-        tiles_t[t] = rows_t[t] > 0 ? last_pos / kTileKV + 1 : 0;
-    }
-    const int n_tiles = max(tiles_t[0], tiles_t[1]);
-    const int used_blocks = (ctx + 15) >> 4;
-    const int group = a.n_heads / a.n_kv_heads;
-    const int kvh = head / group;
-    // the KV tile that holds the last cached token may end inside a 16-token block: its V rows past the context are cleared
-    const int fix_tile = (ctx - 1) / kTileKV;
-    const bool fix_v = (ctx & 15) != 0 && fix_tile < n_tiles;
-
     const uint32_t q_s = base, k_s = base + 2 * kTileBytes, v_s = base + 4 * kTileBytes;
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
     if (threadIdx.x == 0) {
-        mbar_init(bar(B_Q_FULL), 1);
         for (int s = 0; s < 2; ++s) {
+            mbar_init(bar(B_Q_FULL + s), 1);
+            mbar_init(bar(B_Q_EMPTY + s), 1);
             mbar_init(bar(B_KV_FULL + s), 2);
             mbar_init(bar(B_KV_EMPTY + s), 1);
             mbar_init(bar(B_S_FULL + s), 1);
-            mbar_init(bar(B_P_FULL + 2 * s), 8);
-            mbar_init(bar(B_P_FULL + 2 * s + 1), 8);
+            mbar_init(bar(B_P_FULL + s), 8);
             mbar_init(bar(B_PV_DONE + s), 1);
         }
         mbar_init(bar(B_V_FIXED), 1);
+        mbar_init(bar(B_FINAL), 1);
+        for (int s = 0; s < kItemSlots; ++s) {
+            mbar_init(bar(B_ITEM_FULL + s), 1);
+            mbar_init(bar(B_ITEM_EMPTY + s), kItemConsumers);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -318,105 +356,200 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     bool timed_out = false;
+    const int group = a.n_heads / a.n_kv_heads;
+    const int pool = (int)a.n_pool_blocks;  // the launcher keeps the pool below 2^31 blocks
+    // Items reach the other warps through a small ring in shared memory that the scheduler warp fills ahead of time, so that
+    // nobody waits for the global loads behind an item's geometry (request offsets and lengths) at an item boundary.
+    auto fetch_item = [&](uint32_t n, Item& it) -> bool {
+        const int slot = n & (kItemSlots - 1);
+        if (!mbar_wait(bar(B_ITEM_FULL + slot), (n / kItemSlots) & 1)) return false;
+        const int4* r = reinterpret_cast<const int4*>(item_ring + slot * 16);
+        const int4 r0 = r[0], r1 = r[1], r2 = r[2];
+        it.req = r0.x; it.head = r0.y; it.q_begin = r0.z; it.q0 = r0.w;
+        it.n_q = r1.x; it.ctx = r1.y; it.rows[0] = r1.z; it.rows[1] = r1.w;
+        it.tiles[0] = r2.x; it.tiles[1] = r2.y; it.n_tiles = r2.z; it.valid = r2.w != 0;
+        return true;
+    };
+    auto release_item = [&](uint32_t n) { mbar_arrive(bar(B_ITEM_EMPTY + (n & (kItemSlots - 1)))); };  // one lane per consumer warp
 
     if (warp < kFirstSoftmaxWarp) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
-        auto produce = [&](auto is_v_tag) {
-            constexpr bool is_v = decltype(is_v_tag)::value;
-            // ============================ TMA producers ===========================
-            // Warp 1 feeds Q and K, warp 2 feeds V: the issue of one step's boxes (a few tens of clocks per box) is
-            // shared between two warps.  For MMA step j the K warp loads K(j+1), the V warp V(j), both behind the
-            // step's "empty" barrier and onto its "full" barrier.
-            // K: lane = (block of the tile, 64-value half), a [16 tokens x 128 B] box each, laid out [half][128 tokens][128 B].
-            // V: lane = block of the tile, one [2 halves x 16 tokens x 128 B] box each, laid out [block][half][16 tokens][128 B].
-            const int blk = is_v ? (lane & 7) : ((lane & 15) >> 1), sub = lane & 1;
-            const bool active = is_v ? lane < 8 : lane < 16;
-            const uint32_t dst_off = is_v ? blk * 4096 : sub * kSubBytes + blk * 2048;
-            const int32_t* table = a.tables + (int64_t)req * a.table_stride + blk;
-            const int pool = (int)a.n_pool_blocks;  // the launcher keeps the pool below 2^31 blocks
-            const int limit = min(n_tiles * 8, used_blocks) - blk;
-            auto lookup = [&](int tile) -> int {
-                if (tile * 8 >= limit) return pool;  // past the context -> an out-of-range block index, TMA fills zeros
-                const int p = table[tile * 8];
+        if (warp == kTmaWarp) {
+            // ============================ TMA producer: Q and K ===================
+            // lane = (block of the tile, 64-value half), a [16 tokens x 128 B] box each, laid out [half][128 tokens][128 B].
+            // At step g it loads K(g+1): the item's next tile or, at the item's last step, the first tile of the next item.
+            const int blk = (lane & 15) >> 1, sub = lane & 1;
+            const bool active = lane < 16;
+            const uint32_t dst_off = sub * kSubBytes + blk * 2048;
+            auto lookup = [&](const Item& it, int tile) -> int {
+                if (!it.valid || tile * 8 + blk >= min(it.n_tiles * 8, (it.ctx + 15) >> 4)) return pool;  // past the context: TMA fills zeros
+                const int p = a.tables[(int64_t)it.req * a.table_stride + tile * 8 + blk];
                 if ((unsigned)p >= (unsigned)pool) {
-                    if (a.status && !is_v) atomicOr(a.status, SFB_STATUS_BAD_BLOCK_ID);
+                    if (a.status) atomicOr(a.status, SFB_STATUS_BAD_BLOCK_ID);
                     return pool;
                 }
                 return p;
             };
-            const int first = is_v ? 0 : 1;  // KV tile of step 0
-            int phys = lookup(first), phys1 = lookup(first + 1);
-            if (!is_v) {
-                const int phys0 = lookup(0);
+            uint32_t q_loaded = 0, q_phase = 0;  // bit t: tile t has been loaded before / parity of its next "empty" wait
+            auto load_q = [&](const Item& it, int t, bool with_k0) -> bool {  // rows past the packed batch read as zeros
+                if ((q_loaded >> t) & 1) {
+                    if (!mbar_wait(bar(B_Q_EMPTY + t), (q_phase >> t) & 1)) return false;
+                    q_phase ^= 1u << t;
+                }
+                q_loaded |= 1u << t;
                 if (lane == 0) {
-                    mbar_expect_tx(bar(B_Q_FULL), 3 * kTileBytes);
+                    mbar_expect_tx(bar(B_Q_FULL + t), (with_k0 ? 2 : 1) * kTileBytes);
+                    tma_load_4d(q_s + t * kTileBytes, &qmap, bar(B_Q_FULL + t), it.q_begin + it.q0 + t * kTileQ, 0, it.head);
+                    tma_load_4d(q_s + t * kTileBytes + kSubBytes, &qmap, bar(B_Q_FULL + t), it.q_begin + it.q0 + t * kTileQ, 1, it.head);
+                }
+                __syncwarp();
+                return true;
+            };
+            int g = 0;
+            uint32_t n = 0;
+            Item cur, nxt;
+            cur.valid = false;
+            if (!fetch_item(0, cur)) timed_out = true;
+            if (cur.valid) {
+                const int phys0 = lookup(cur, 0);
+                load_q(cur, 0, true);
+                if (active) tma_load_5d(k_s + dst_off, &kmap, bar(B_Q_FULL), sub, cur.head / group, phys0);  // K(0) into slot 0
+                if (cur.tiles[1] > 0) load_q(cur, 1, false);
+            }
+            while (cur.valid && !timed_out) {
+                nxt.valid = false;
+                if (!fetch_item(n + 1, nxt)) { timed_out = true; break; }
+                const int kvh = cur.head / group;
+                const int next_first = lookup(nxt, 0);
+                int phys = lookup(cur, 1), phys1 = lookup(cur, 2);
+                for (int j = 0; j < cur.n_tiles; ++j, ++g) {
 #pragma unroll
-                    for (int t = 0; t < 2; ++t) {  // rows past the packed batch read as zeros
-                        tma_load_4d(q_s + t * kTileBytes, &qmap, bar(B_Q_FULL), q_begin + q0 + t * kTileQ, 0, head);
-                        tma_load_4d(q_s + t * kTileBytes + kSubBytes, &qmap, bar(B_Q_FULL), q_begin + q0 + t * kTileQ, 1, head);
+                    for (int t = 0; t < 2; ++t)
+                        if (nxt.valid && j == cur.tiles[t] && nxt.tiles[t] > 0 && !load_q(nxt, t, false)) timed_out = true;
+                    const int s = g & 1;
+                    const int phys2 = lookup(cur, j + 3);  // table entries are fetched two tiles ahead of their use
+                    // "empty" phases: slot 0 completes at the end of steps 0, 2, ...; slot 1 once the first Q.K(0)^T is done, then at
+                    // the end of steps 1, 3, ...
+                    const uint32_t par = s ? ((g >> 1) & 1) : (((g >> 1) & 1) ^ 1);
+                    if (timed_out || !mbar_wait(bar(B_KV_EMPTY + s), par)) { timed_out = true; break; }
+                    if (j + 1 < cur.n_tiles || nxt.valid) {
+                        const bool own = j + 1 < cur.n_tiles;
+                        if (lane == 0) mbar_expect_tx(bar(B_KV_FULL + s), kTileBytes);
+                        __syncwarp();
+                        if (active)
+                            tma_load_5d(k_s + (s ^ 1) * kTileBytes + dst_off, &kmap, bar(B_KV_FULL + s), sub, own ? kvh : nxt.head / group,
+                                        own ? phys : next_first);
+                    } else if (lane == 0) {
+                        mbar_arrive(bar(B_KV_FULL + s));  // no further K tile: the step's barrier still counts two arrivals
+                    }
+                    phys = phys1;
+                    phys1 = phys2;
+                }
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+                    if (!timed_out && nxt.valid && cur.tiles[t] == cur.n_tiles && nxt.tiles[t] > 0 && !load_q(nxt, t, false)) timed_out = true;
+                __syncwarp();
+                if (lane == 0) release_item(n);
+                cur = nxt;
+                ++n;
+            }
+        } else if (warp == kTmaWarpV) {
+            // ============================ TMA producer: V =========================
+            // lane = block of the tile, one [2 halves x 16 tokens x 128 B] box each, laid out [block][half][16 tokens][128 B].
+            const int blk = lane & 7;
+            const bool active = lane < 8;
+            auto lookup = [&](const Item& it, int tile) -> int {  // bad ids are reported by the K warp
+                if (tile * 8 + blk >= min(it.n_tiles * 8, (it.ctx + 15) >> 4)) return pool;
+                const int p = a.tables[(int64_t)it.req * a.table_stride + tile * 8 + blk];
+                return (unsigned)p >= (unsigned)pool ? pool : p;
+            };
+            int g = 0;
+            uint32_t n = 0;
+            Item cur;
+            cur.valid = false;
+            if (!fetch_item(0, cur)) timed_out = true;
+            while (cur.valid && !timed_out) {
+                const int kvh = cur.head / group, g0 = g;
+                int phys = lookup(cur, 0), phys1 = lookup(cur, 1);
+                for (int j = 0; j < cur.n_tiles; ++j, ++g) {
+                    const int s = g & 1;
+                    const int phys2 = lookup(cur, j + 2);
+                    const uint32_t par = s ? ((g >> 1) & 1) : (((g >> 1) & 1) ^ 1);
+                    if (!mbar_wait(bar(B_KV_EMPTY + s), par)) { timed_out = true; break; }
+                    if (lane == 0) mbar_expect_tx(bar(B_KV_FULL + s), kTileBytes);
+                    __syncwarp();
+                    if (active) tma_load_5d(v_s + s * kTileBytes + blk * 4096, &vmap, bar(B_KV_FULL + s), 0, kvh, phys);
+                    phys = phys1;
+                    phys1 = phys2;
+                }
+                // The KV tile that holds the last cached token may end inside a 16-token block: its V rows past the context are
+                // cleared (an unzeroed pool may hold NaN there, and 0 * NaN would reach O).  A 128-byte row of a swizzled sub-tile
+                // is permuted only inside itself, so whole rows can be cleared in place.
+                const int fix_tile = (cur.ctx - 1) / kTileKV;
+                if (!timed_out && (cur.ctx & 15) != 0 && fix_tile < cur.n_tiles) {
+                    const int gf = g0 + fix_tile, s = gf & 1;
+                    if (mbar_wait(bar(B_KV_FULL + s), (gf >> 1) & 1)) {
+                        const int fblk = ((cur.ctx - 1) >> 4) & 7, first = cur.ctx & 15;
+                        uint8_t* v_tile = base_ptr + 4 * kTileBytes + s * kTileBytes + fblk * 4096;
+                        for (int i = lane; i < (16 - first) * 16; i += 32) {  // (row, 64-value half, 16-byte piece)
+                            const int r = first + (i >> 4), h = (i >> 3) & 1, piece = i & 7;
+                            *reinterpret_cast<uint4*>(v_tile + h * 2048 + r * 128 + piece * 16) = make_uint4(0, 0, 0, 0);
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar(B_V_FIXED));
+                    } else {
+                        timed_out = true;
                     }
                 }
                 __syncwarp();
-                if (active) tma_load_5d(k_s + dst_off, &kmap, bar(B_Q_FULL), sub, kvh, phys0);  // K(0) into slot 0
+                if (lane == 0) release_item(n);
+                ++n;
+                cur.valid = false;
+                if (!timed_out && !fetch_item(n, cur)) timed_out = true;
             }
-            for (int j = 0; j < n_tiles; ++j) {
-                const int s = j & 1;
-                // "empty" phases: parity 0 completes at the end of step 0 (pair 0) resp. once Q.K(0)^T is done (pair 1)
-                const uint32_t par = s ? ((j >> 1) & 1) : (((j >> 1) & 1) ^ 1);
-                const int phys2 = lookup(first + j + 2);  // table entries are fetched two tiles ahead of their use
-                if (!mbar_wait(bar(B_KV_EMPTY + s), par)) { timed_out = true; break; }
-                if (is_v) {
-                    if (lane == 0) mbar_expect_tx(bar(B_KV_FULL + s), kTileBytes);
-                    __syncwarp();
-                    if (active) tma_load_5d(v_s + s * kTileBytes + dst_off, &vmap, bar(B_KV_FULL + s), 0, kvh, phys);
-                } else if (j + 1 < n_tiles) {
-                    if (lane == 0) mbar_expect_tx(bar(B_KV_FULL + s), kTileBytes);
-                    __syncwarp();
-                    if (active) tma_load_5d(k_s + (s ^ 1) * kTileBytes + dst_off, &kmap, bar(B_KV_FULL + s), sub, kvh, phys);
-                } else if (lane == 0) {
-                    mbar_arrive(bar(B_KV_FULL + s));  // no further K tile: the step's barrier still counts two arrivals
+        } else if (warp == kSchedWarp) {
+            // ============================ item scheduler ==========================
+            int idx = blockIdx.x;
+            for (uint32_t n = 0;; ++n) {
+                const int slot = n & (kItemSlots - 1);
+                if (n >= kItemSlots && !mbar_wait(bar(B_ITEM_EMPTY + slot), (n / kItemSlots - 1) & 1)) { timed_out = true; break; }
+                const Item it = find_item(a, idx, limit_max, lane == 0);
+                if (lane == 0) {
+                    int4* r = reinterpret_cast<int4*>(item_ring + slot * 16);
+                    r[0] = make_int4(it.req, it.head, it.q_begin, it.q0);
+                    r[1] = make_int4(it.n_q, it.ctx, it.rows[0], it.rows[1]);
+                    r[2] = make_int4(it.tiles[0], it.tiles[1], it.n_tiles, it.valid ? 1 : 0);
+                    mbar_arrive(bar(B_ITEM_FULL + slot));
                 }
-                phys = phys1;
-                phys1 = phys2;
+                __syncwarp();
+                if (!it.valid) break;  // the end-of-work record
+                idx += gridDim.x;
             }
-            if (is_v && fix_v && !timed_out) {
-                // Clear the V rows past the context in the last KV tile.  A 128-byte row of a swizzled sub-tile is permuted
-                // only inside itself, so whole rows can be cleared in place.
-                const int s = fix_tile & 1;
-                if (mbar_wait(bar(B_KV_FULL + s), (fix_tile >> 1) & 1)) {
-                    const int fblk = ((ctx - 1) >> 4) & 7, first = ctx & 15;
-                    uint8_t* v_tile = base_ptr + 4 * kTileBytes + s * kTileBytes + fblk * 4096;
-                    for (int i = lane; i < (16 - first) * 16; i += 32) {  // (row, 64-value half, 16-byte piece)
-                        const int r = first + (i >> 4), h = (i >> 3) & 1, piece = i & 7;
-                        *reinterpret_cast<uint4*>(v_tile + h * 2048 + r * 128 + piece * 16) = make_uint4(0, 0, 0, 0);
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(B_V_FIXED));
-                } else {
-                    timed_out = true;
-                }
-            }
-        };
-        if (warp == kTmaWarp) {
-            produce(std::false_type{});
-        } else if (warp == kTmaWarpV) {
-            produce(std::true_type{});
         } else if (warp == kMmaWarp) {
             // ============================ MMA issuer ==============================
-            // One thread issues every MMA, in the order PV0(j), QK0(j+1), PV1(j), QK1(j+1): while one query tile's rows
-            // are in the softmax warps, the tensor pipe works on the other tile (two issuing threads, one per tile, were
-            // measured: the tiles then fall into step and the pipe idles while both are in their softmax).  An issue
-            // returns when the pipe accepts the MMA, so whatever else this thread runs is time with nothing queued: per
-            // step it waits once for the operands and once or twice per tile for P, and commits the S tiles and the
-            // operand slots; descriptors are a constant plus a slot / K-step offset in the low word.
+            // One thread issues every MMA, per step in the order PV0(j), QK0(j+1), PV1(j), QK1(j+1): while one query tile's rows
+            // are in the softmax warps, the tensor pipe works on the other tile.  At an item's last step the place of QK_t(j+1)
+            // is taken by the NEXT item's first Q_t.K(0)^T, so the pipe runs on while the softmax warps write the item's rows
+            // out.  An issue returns when the pipe accepts the MMA; descriptors are a constant plus a slot / K-step offset in
+            // the low word.
             if (lane == 0) {
                 constexpr uint32_t idesc_qk = instr_desc(BF16, false, kTileQ, kTileKV);
                 constexpr uint32_t idesc_pv = instr_desc(BF16, true, kTileQ, kHeadDim);
                 const uint32_t hi = (uint32_t)(smem_desc(0, 0, 1024) >> 32);
                 const uint32_t q_lo = (uint32_t)smem_desc(q_s, 16, 0);
                 const uint32_t k_lo = (uint32_t)smem_desc(k_s, 16, 0), v_lo = (uint32_t)smem_desc(v_s, 2048, 0);
-                auto issue_qk = [&](int t, int slot) {  // 16 head-dim values per instruction
+                uint32_t q_phase = 0, p_phase = 0, fix_waits = 0;  // bit t: parity of tile t's next wait
+                bool ok = true;
+                // Q_t . K(slot)^T, 16 head-dim values per instruction; `first` = the item's first score tile (its Q rows must
+                // have landed), `last` = the item's last one (the tile's Q rows may be replaced afterwards)
+                auto issue_qk = [&](int t, int slot, bool first, bool last) {
+                    if (first) {
+                        ok = mbar_wait(bar(B_Q_FULL + t), (q_phase >> t) & 1);
+                        q_phase ^= 1u << t;
+                        if (!ok) return;
+                        tc_fence_after();
+                    }
                     const uint32_t qb_lo = q_lo + t * (kTileBytes >> 4), kb = k_lo + slot * (kTileBytes >> 4);
 #pragma unroll
                     for (int ks = 0; ks < 8; ++ks) {
@@ -424,40 +557,57 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                         mma_ss(tmem + t * kColTile, qb_lo + off, hi, kb + off, hi, idesc_qk, ks > 0);
                     }
                     tc_commit(bar(B_S_FULL + t));
+                    if (last) tc_commit(bar(B_Q_EMPTY + t));
                 };
-                auto issue_pv = [&](int t, int j) -> bool {
-                    const uint32_t vb = v_lo + (j & 1) * (kTileBytes >> 4), s_tm = tmem + t * kColTile;
-#pragma unroll
-                    for (int part = 0; part < kPParts; ++part) {  // with two parts: keys {0-31, 64-95}, then {32-63, 96-127}
-                        if (!mbar_wait(bar(B_P_FULL + 2 * t + part), j & 1)) return false;
-                        tc_fence_after();
-#pragma unroll
-                        for (int i = 0; i < 8 / kPParts; ++i) {  // 16 KV tokens per instruction
-                            const int ks = kPParts == 2 ? (i >> 1) * 4 + part * 2 + (i & 1) : i;
-                            mma_ts(s_tm + kColO, s_tm + (ks >> 2) * 64 + (ks & 3) * 8, vb + ks * (4096 >> 4), hi, idesc_pv,
-                                   (j > 0 || part > 0 || i > 0));
-                        }
-                    }
-                    if (j + 1 == tiles_t[t]) tc_commit(bar(B_PV_DONE + t));  // the tile's last product: the epilogue waits for it
-                    return true;
-                };
-                bool ok = mbar_wait(bar(B_Q_FULL), 0);
-                if (ok) {
+                auto issue_pv = [&](int t, int slot, bool first, bool last) {  // 16 KV tokens per instruction
+                    ok = mbar_wait(bar(B_P_FULL + t), (p_phase >> t) & 1);
+                    p_phase ^= 1u << t;
+                    if (!ok) return;
                     tc_fence_after();
-                    if (tiles_t[0] > 0) issue_qk(0, 0);
-                    if (tiles_t[1] > 0) issue_qk(1, 0);
-                    tc_commit(bar(B_KV_EMPTY + 1));  // K slot 0 may take K(2) once these are done
-                }
-                for (int j = 0; ok && j < n_tiles; ++j) {
-                    ok = mbar_wait(bar(B_KV_FULL + (j & 1)), (j >> 1) & 1);
-                    if (ok && fix_v && j == fix_tile) ok = mbar_wait(bar(B_V_FIXED), 0);
+                    const uint32_t vb = v_lo + slot * (kTileBytes >> 4), s_tm = tmem + t * kColTile;
 #pragma unroll
-                    for (int t = 0; t < 2; ++t) {
-                        if (ok && j < tiles_t[t]) ok = issue_pv(t, j);
-                        if (ok && j + 1 < tiles_t[t]) issue_qk(t, (j + 1) & 1);
-                    }
-                    if (ok && j + 2 < n_tiles) tc_commit(bar(B_KV_EMPTY + (j & 1)));  // the producers wait for it before step j + 2
+                    for (int ks = 0; ks < 8; ++ks)
+                        mma_ts(s_tm + kColO, s_tm + (ks >> 2) * 64 + (ks & 3) * 8, vb + ks * (4096 >> 4), hi, idesc_pv, !first || ks > 0);
+                    if (last) tc_commit(bar(B_PV_DONE + t));  // the epilogue waits for it
+                };
+                int g = 0;
+                uint32_t n = 0;
+                Item cur, nxt;
+                cur.valid = false;
+                ok = fetch_item(0, cur);
+                if (cur.valid) {
+#pragma unroll
+                    for (int t = 0; t < 2; ++t)
+                        if (ok && cur.tiles[t] > 0) issue_qk(t, 0, true, cur.tiles[t] == 1);
+                    if (ok) tc_commit(bar(B_KV_EMPTY + 1));  // K slot 0 may take K(2) once these are done
                 }
+                while (ok && cur.valid) {
+                    nxt.valid = false;
+                    ok = fetch_item(n + 1, nxt);
+                    const int fix_tile = (cur.ctx - 1) / kTileKV;
+                    const bool fix_v = (cur.ctx & 15) != 0 && fix_tile < cur.n_tiles;
+                    for (int j = 0; ok && j < cur.n_tiles; ++j, ++g) {
+                        ok = mbar_wait(bar(B_KV_FULL + (g & 1)), (g >> 1) & 1);
+                        if (ok && fix_v && j == fix_tile) {
+                            ok = mbar_wait(bar(B_V_FIXED), fix_waits & 1);
+                            ++fix_waits;
+                        }
+                        const bool last_step = j + 1 == cur.n_tiles;
+#pragma unroll
+                        for (int t = 0; t < 2; ++t) {
+                            if (ok && j < cur.tiles[t]) issue_pv(t, g & 1, j == 0, j + 1 == cur.tiles[t]);
+                            if (ok && j + 1 < cur.tiles[t]) issue_qk(t, (g + 1) & 1, false, j + 2 == cur.tiles[t]);
+                            else if (ok && last_step && nxt.valid && nxt.tiles[t] > 0) issue_qk(t, (g + 1) & 1, true, nxt.tiles[t] == 1);
+                        }
+                        if (ok) tc_commit(bar(B_KV_EMPTY + (g & 1)));  // the producers wait for it before step g + 2
+                    }
+                    release_item(n);
+                    cur = nxt;
+                    ++n;
+                }
+                // every commit above arrives on a barrier of this block's shared memory: all of them must have landed before exit
+                tc_commit(bar(B_FINAL));
+                if (!mbar_wait(bar(B_FINAL), 0)) ok = false;
                 timed_out = !ok;
             }
         }
@@ -465,8 +615,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         // ======================= softmax / correction / epilogue ==============
         // Eight warps per query tile.  Warp w owns tensor-memory lanes 32*(w&3).. (its hardware window) and key
         // columns 64*((w>>2)&1).. of its tile: two threads share a query row, swap their half-row maxima through
-        // shared memory (64-thread named barrier, slots alternate by step) and keep partial sums that are only
-        // added up in the epilogue.
+        // shared memory (64-thread named barrier, slots alternate) and keep partial sums that are only added up in the epilogue.
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
         const int my_t = (warp - kFirstSoftmaxWarp) >> 3;  // query tile of this 8-warp group
         const int hf = ((warp - kFirstSoftmaxWarp) >> 2) & 1;
@@ -474,24 +623,24 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t pair_bar = 1 + my_t * 4 + (warp & 3);  // named barrier of the two warps that share a lane window
         const float sl2 = a.scale * kLog2e;
-        float m_used = -INFINITY, l = 0.f;
-        const int my_rows = my_t ? rows_t[1] : rows_t[0], my_tiles = my_t ? tiles_t[1] : tiles_t[0];
-        // last visible position of this thread's row; padding rows see everything
-        int pos = (row < my_rows && a.causal) ? ctx - n_q + q0 + my_t * kTileQ + row : ctx - 1;
-        if (a.row_limits && row < my_rows) pos = min(max(a.row_limits[q_begin + q0 + my_t * kTileQ + row], 0), ctx) - 1;
         const uint32_t s_addr = lane_addr + my_t * kColTile + hf * 64;  // this thread's 64 score columns
         const uint32_t o_addr = lane_addr + my_t * kColTile + kColO + hf * 64;
+        uint32_t s_waits = 0, e_waits = 0, x_count = 0;
+        float m_used = -INFINITY, l = 0.f;
+        int pos = 0;
 
         // both warps of a pair run the same waits in the same order, so they reach this barrier together or not at all
-        auto exchange = [&](int step, float mine) -> float {
-            float* slot = xch + ((step & 1) * 2 + my_t) * 2 * kTileQ;
+        auto exchange = [&](float mine) -> float {
+            float* slot = xch + ((x_count & 1) * 2 + my_t) * 2 * kTileQ;
+            ++x_count;
             slot[hf * kTileQ + row] = mine;
             asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
             return slot[(hf ^ 1) * kTileQ + row];
         };
 
         auto softmax_tile = [&](int j) -> bool {
-            if (!mbar_wait(bar(B_S_FULL + my_t), j & 1)) return false;
+            if (!mbar_wait(bar(B_S_FULL + my_t), s_waits & 1)) return false;
+            ++s_waits;
             tc_fence_after();
             const int kv0 = j * kTileKV + hf * 64;
             // tcgen05.ld / st are warp-collective: the masked / unmasked choice must be uniform across the warp
@@ -514,7 +663,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     mx0 = fmaxf(mx0, s[i]);
                 }
             }
-            const float mx = fmaxf(fmaxf(mx0, mx1), exchange(j, fmaxf(mx0, mx1)));
+            const float mx = fmaxf(fmaxf(mx0, mx1), exchange(fmaxf(mx0, mx1)));
             const float m_new = fmaxf(m_used, mx * sl2);
             if (j == 0) {
                 m_used = m_new;
@@ -537,7 +686,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     tmem_wait_st();
                 }
             }
-            // P (16-bit pairs, 32 columns) goes over the first half of this thread's own score columns, in two halves
+            // P (16-bit pairs, 32 columns) goes over the first half of this thread's own score columns;
             // packed fp32 pairs: one FFMA2 scales and shifts two scores, one FADD2 adds two probabilities
             const float neg_m = m_used == -INFINITY ? 0.f : -m_used;  // a row that sees nothing yet: every score is -inf, P = 0
             const float2 sl2v = make_float2(sl2, sl2), nmv = make_float2(neg_m, neg_m);
@@ -554,72 +703,101 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     pk[i] = pack2<BF16>(pr.x, pr.y);
                 }
                 tmem_st16(s_addr + ch * 16, pk);
-                if (kPParts == 2 || ch == 1) {
-                    tmem_wait_st();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(B_P_FULL + 2 * my_t + (kPParts == 2 ? ch : 0)));
-                }
             }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_P_FULL + my_t));
             l += (acc0.x + acc1.x) + (acc0.y + acc1.y);
             return true;
         };
 
         bool ok = true;
-        for (int j = 0; j < my_tiles && ok; ++j) ok = softmax_tile(j);
-        // ---- epilogue: O / l, each thread its 64 output columns
-        if (ok && my_tiles > 0) ok = mbar_wait(bar(B_PV_DONE + my_t), 0);
-        if (ok && my_tiles > 0) {
-            tc_fence_after();
-            const float l_row = l + exchange(my_tiles, l);
-            const bool row_valid = row < my_rows;
-            if (a.part_o) {
-                // shared-prefix mode: this row is decode request `qrow`; its partial goes to the chunk slot right after
-                // the request's own chunks, in the decode kernel's format (unnormalised O, max in log2 units, sum)
-                const int qrow = q0 + my_t * kTileQ + row;
-                int64_t pslot = 0;
-                if (row_valid) {
-                    int len = a.part_seq_lens[qrow];
-                    if (len > a.part_max_tokens) len = a.part_max_tokens;
-                    const int chunk = (max(0, len - ctx) + a.part_chunk_tokens - 1) / a.part_chunk_tokens;
-                    pslot = ((int64_t)qrow * a.part_n_chunks + chunk) * a.n_heads + head;
-                    if (hf == 0) {
-                        a.part_ml[pslot * 2] = m_used;
-                        a.part_ml[pslot * 2 + 1] = l_row;
-                    }
+        uint32_t n = 0;
+        Item cur;
+        cur.valid = false;
+        ok = fetch_item(0, cur);
+        while (ok && cur.valid) {
+            const int my_rows = my_t ? cur.rows[1] : cur.rows[0], my_tiles = my_t ? cur.tiles[1] : cur.tiles[0];
+            if (my_tiles > 0) {
+                // last visible position of this thread's row; padding rows see everything
+                pos = (row < my_rows && a.causal) ? cur.ctx - cur.n_q + cur.q0 + my_t * kTileQ + row : cur.ctx - 1;
+                if (a.row_limits && row < my_rows) pos = min(max(a.row_limits[cur.q_begin + cur.q0 + my_t * kTileQ + row], 0), cur.ctx) - 1;
+                m_used = -INFINITY;
+                l = 0.f;
+                for (int j = 0; j < my_tiles && ok; ++j) ok = softmax_tile(j);
+                // ---- epilogue: O / l, each thread its 64 output columns
+                if (ok) {
+                    ok = mbar_wait(bar(B_PV_DONE + my_t), e_waits & 1);
+                    ++e_waits;
                 }
+                if (ok) {
+                    tc_fence_after();
+                    const float l_row = l + exchange(l);
+                    const bool row_valid = row < my_rows;
+                    if (a.part_o) {
+                        // shared-prefix mode: this row is decode request `qrow`; its partial goes to the chunk slot right after
+                        // the request's own chunks, in the decode kernel's format (unnormalised O, max in log2 units, sum)
+                        const int qrow = cur.q0 + my_t * kTileQ + row;
+                        int64_t pslot = 0;
+                        if (row_valid) {
+                            int len = a.part_seq_lens[qrow];
+                            if (len > a.part_max_tokens) len = a.part_max_tokens;
+                            const int chunk = (max(0, len - cur.ctx) + a.part_chunk_tokens - 1) / a.part_chunk_tokens;
+                            pslot = ((int64_t)qrow * a.part_n_chunks + chunk) * a.n_heads + cur.head;
+                            if (hf == 0) {
+                                a.part_ml[pslot * 2] = m_used;
+                                a.part_ml[pslot * 2 + 1] = l_row;
+                            }
+                        }
 #pragma unroll 1
-                for (int ch = 0; ch < 2; ++ch) {
-                    float o[32];
-                    tmem_ld32(o_addr + ch * 32, o);
-                    if (row_valid) {
-                        float* dst = a.part_o + pslot * kHeadDim + hf * 64 + ch * 32;
+                        for (int ch = 0; ch < 2; ++ch) {
+                            float o[32];
+                            tmem_ld32(o_addr + ch * 32, o);
+                            if (row_valid) {
+                                float* dst = a.part_o + pslot * kHeadDim + hf * 64 + ch * 32;
 #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-                    }
-                }
-            } else {
-                const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-                uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(q_begin + q0 + my_t * kTileQ + row) * a.out_stride[0] +
-                                (int64_t)head * a.out_stride[1] + hf * 64;
+                                for (int i = 0; i < 8; ++i)
+                                    *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                            }
+                        }
+                    } else {
+                        const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+                        uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(cur.q_begin + cur.q0 + my_t * kTileQ + row) * a.out_stride[0] +
+                                        (int64_t)cur.head * a.out_stride[1] + hf * 64;
 #pragma unroll 1
-                for (int ch = 0; ch < 2; ++ch) {
-                    float o[32];
-                    tmem_ld32(o_addr + ch * 32, o);
-                    if (row_valid) {
+                        for (int ch = 0; ch < 2; ++ch) {
+                            float o[32];
+                            tmem_ld32(o_addr + ch * 32, o);
+                            if (row_valid) {
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            uint4 w;
-                            w.x = pack2<BF16>(o[8 * i] * inv, o[8 * i + 1] * inv);
-                            w.y = pack2<BF16>(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
-                            w.z = pack2<BF16>(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
-                            w.w = pack2<BF16>(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
-                            *reinterpret_cast<uint4*>(dst + ch * 32 + i * 8) = w;
+                                for (int i = 0; i < 2; ++i) {
+                                    uint32_t w[8];
+#pragma unroll
+                                    for (int k = 0; k < 8; ++k) w[k] = pack2<BF16>(o[16 * i + 2 * k] * inv, o[16 * i + 2 * k + 1] * inv);
+                                    uint16_t* p = dst + ch * 32 + i * 16;
+                                    if (a.out_vec8) {
+                                        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                                                     "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                                                     : "memory");
+                                    } else {
+                                        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+                                        *reinterpret_cast<uint4*>(p + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                                    }
+                                }
+                            }
                         }
                     }
+                    // the next item's first P.V overwrites O: it waits for this warp's next P, which follows these loads in program
+                    // order (tcgen05.wait::ld above), so nothing else has to say that O has been read
+                    tc_fence_before();
                 }
             }
+            __syncwarp();
+            if (lane == 0) release_item(n);
+            ++n;
+            cur.valid = false;
+            ok = ok && fetch_item(n, cur);
         }
         timed_out = !ok;
     }
@@ -661,6 +839,16 @@ bool encode(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) n = v;
+        else return 148;
+    }
+    return n;
+}
+
 }  // namespace
 
 // Returns SFB_ERR_UNSUPPORTED when the shape is outside this kernel (the caller then takes the generic route).
@@ -691,7 +879,15 @@ int launch_prefill_tcgen05(const PrefillLaunch& p, cudaStream_t stream) {
     a.fixed_nq = p.fixed_nq; a.fixed_ctx = p.fixed_ctx; a.part_o = p.part_o; a.part_ml = p.part_ml;
     a.part_seq_lens = p.part_seq_lens; a.part_n_chunks = p.part_n_chunks; a.part_chunk_tokens = p.part_chunk_tokens;
     a.part_max_tokens = p.part_max_tokens;
-    dim3 grid((unsigned)ceil_div(p.max_q_tokens, 2 * kTileQ), (unsigned)p.n_heads, (unsigned)p.n_requests);
+    // Work items (256 query rows of one head of one request) are spread over one resident thread block per SM; with per-row
+    // limits every item gets its own thread block (the tile counts then take a block-wide reduction at the start).
+    a.q_blocks = (int)ceil_div(p.max_q_tokens, 2 * kTileQ);
+    const int64_t n_items = (int64_t)a.q_blocks * p.n_heads * p.n_requests;
+    if (n_items <= 0) return SFB_OK;
+    if (n_items > 0x7fffffffLL) return SFB_ERR_UNSUPPORTED;
+    a.n_items = (int)n_items;
+    a.out_vec8 = !p.part_o && reinterpret_cast<uintptr_t>(p.out) % 32 == 0 && p.out_stride[0] % 16 == 0 && p.out_stride[1] % 16 == 0;
+    const dim3 grid((unsigned)(p.row_limits ? n_items : std::min<int64_t>(n_items, sm_count())));
     if (a.bf16) {
         if (const int rc = allow_shared_memory_once(reinterpret_cast<const void*>(prefill_tcgen05_kernel<true>), kSmemBytes)) return rc;
         prefill_tcgen05_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(qmap, kmap, vmap, a);
