@@ -142,6 +142,13 @@ struct Divider {
         const float q = __fmul_rn(x, rcp);
         return __fmaf_rn(__fmaf_rn(-q, scale, x), rcp, q);
     }
+    // two quotients at once on the packed fp32 pipe (fmul2 / ffma2: each half rounds like the scalar instruction, so the
+    // result is bit-identical; half the instructions)
+    __device__ __forceinline__ float2 quick2_unsigned_zero(float2 x) const {
+        const float2 r2 = make_float2(rcp, rcp), ns2 = make_float2(-scale, -scale);
+        const float2 q = __fmul2_rn(x, r2);
+        return __ffma2_rn(__ffma2_rn(q, ns2, x), r2, q);
+    }
     __device__ __forceinline__ float quick(float x) const {
         return copysignf(quick_unsigned_zero(x), x);  // scale > 0: the quotient has x's sign, also when it is zero (-0.0 encodes as 0x80)
     }
@@ -156,8 +163,10 @@ __device__ __forceinline__ void encode_quick(const float* x, const uint4& raw, c
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            uint16_t lo = float2_to_e4m3x2(div.quick_unsigned_zero(x[4 * i]), div.quick_unsigned_zero(x[4 * i + 1]));
-            uint16_t hi = float2_to_e4m3x2(div.quick_unsigned_zero(x[4 * i + 2]), div.quick_unsigned_zero(x[4 * i + 3]));
+            const float2 qa = div.quick2_unsigned_zero(make_float2(x[4 * i], x[4 * i + 1]));
+            const float2 qb = div.quick2_unsigned_zero(make_float2(x[4 * i + 2], x[4 * i + 3]));
+            uint16_t lo = float2_to_e4m3x2(qa.x, qa.y);
+            uint16_t hi = float2_to_e4m3x2(qb.x, qb.y);
             words[i] = ((uint32_t)lo | ((uint32_t)hi << 16)) | (__byte_perm(w[2 * i], w[2 * i + 1], 0x7531) & 0x80808080u);
         }
     } else {
@@ -188,7 +197,9 @@ __device__ __noinline__ uint2 encode_exact_chunk(uint4 raw, float scale) {
 // CPL = 16-byte source chunks each lane keeps; a slice has bs * D / N chunks.
 // Grid: x strides over the blocks a request touches, y = request, z = K / V.
 template <typename ST, int CPL, bool FP8, bool EVEN, bool FIRST>
-__global__ void __launch_bounds__(kThreads) cache_write_kernel(AppendArgs a) {
+// The quantising kernel for 16-bit sources is held to 96 registers (five thread blocks per SM instead of four): measured 1.4 %
+// faster on 638 k appended tokens than the 128 the compiler takes by itself; six (80 registers) and eight (64) are slower.
+__global__ void __launch_bounds__(kThreads, (FP8 && sizeof(ST) == 2 && CPL <= 8 && EVEN) ? 5 : 1) cache_write_kernel(AppendArgs a) {
     constexpr bool first_pass = FIRST;
     constexpr int N = Src<ST>::N;
     const int req = blockIdx.y, which = blockIdx.z;
