@@ -28,7 +28,8 @@
 //             own 32 tensor-memory lanes, so warps w and w+4 share lanes and split the columns).  A thread reads its 64
 //             scores ONCE (tcgen05.ld into registers; the softmax warpgroups raise their register allowance with setmaxnreg,
 //             the first warpgroup lowers its own), swaps half-row maxima with its partner through shared memory under a
-//             64-thread named barrier, keeps running max / sum in log2 units, writes P as bf16/fp16 over its own S columns,
+//             64-thread named barrier (only when a barrier-wide OR says a row outgrew the rescale threshold), keeps running
+//             max / sum in log2 units, writes P as bf16/fp16 over its own S columns,
 //             rescales O in tensor memory only when the max grew by more than 2^8 (the stale max stays exact in fp32), adds
 //             the partial sums in the epilogue and writes O / l.
 // Tensor memory: per query tile S|P (128 columns) and O (128) = 512 columns in all.
@@ -615,7 +616,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         // ======================= softmax / correction / epilogue ==============
         // Eight warps per query tile.  Warp w owns tensor-memory lanes 32*(w&3).. (its hardware window) and key
         // columns 64*((w>>2)&1).. of its tile: two threads share a query row, swap their half-row maxima through
-        // shared memory (64-thread named barrier, slots alternate) and keep partial sums that are only added up in the epilogue.
+        // shared memory (64-thread named barrier, slots alternate) in the steps where the barrier's OR says some row of the pair
+        // outgrew the rescale threshold, and keep partial sums that are only added up in the epilogue.
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
         const int my_t = (warp - kFirstSoftmaxWarp) >> 3;  // query tile of this 8-warp group
         const int hf = ((warp - kFirstSoftmaxWarp) >> 2) & 1;
@@ -663,15 +665,29 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     mx0 = fmaxf(mx0, s[i]);
                 }
             }
-            const float mx = fmaxf(fmaxf(mx0, mx1), exchange(fmaxf(mx0, mx1)));
-            const float m_new = fmaxf(m_used, mx * sl2);
-            if (j == 0) {
-                m_used = m_new;
-            } else {
-                const bool need = m_new > m_used + kRescaleThreshold;  // the same for both threads of a row
-                if (__any_sync(0xffffffffu, need)) {
+            // The row maximum is only needed when it moves the running maximum by more than the rescale threshold.  Whether
+            // any row of this warp pair needs that is an OR over the pair's 64 threads, taken in the named barrier itself
+            // (no shared memory); only then do the partners swap their half-row maxima.
+            const float mx_half = fmaxf(mx0, mx1);
+            bool grow = j == 0;
+            if (j > 0) {
+                uint32_t any;
+                asm volatile(
+                    "{\n .reg .pred p, q;\n setp.ne.u32 q, %2, 0;\n barrier.cta.red.or.pred p, %1, 64, q;\n selp.u32 %0, 1, 0, p;\n}\n"
+                    : "=r"(any)
+                    : "r"(pair_bar), "r"((uint32_t)(mx_half * sl2 > m_used + kRescaleThreshold))
+                    : "memory");
+                grow = any != 0;
+            }
+            if (grow) {
+                const float mx = fmaxf(mx_half, exchange(mx_half));
+                const float m_new = fmaxf(m_used, mx * sl2);
+                if (j == 0) {
+                    m_used = m_new;
+                } else {
                     // O is only touched between P.V products.  The previous one is complete: this tile's S was committed by
                     // the same thread after it, and a commit covers everything that thread issued before.
+                    const bool need = m_new > m_used + kRescaleThreshold;  // the same for both threads of a row
                     const float f = need ? fast_exp2(m_used - m_new) : 1.f;
                     l *= f;
                     if (need) m_used = m_new;
