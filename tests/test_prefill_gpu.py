@@ -89,6 +89,39 @@ def test_prefill_multi_request_shared_prefix_and_generic_route(cuda):
             at += nq[r]
 
 
+def test_prefill_many_ragged_items_per_thread_block(cuda):
+    """More work items than SMs, of very different sizes: every resident thread block runs several items back to back (K / V
+    stream, Q tiles and first score tile of the next item issued during the current one's last step), including requests whose
+    second query tile is empty, one-token chunks and contexts that end inside a 16-token block.  Every request against the
+    plain-C oracle."""
+    g = torch.Generator().manual_seed(29)
+    h, hkv, d = 8, 2, 128
+    n_req = 28
+    nq = {f"r{i}": int(torch.randint(1, 300, (1,), generator=g)) for i in range(n_req)}
+    nq["r3"], nq["r7"], nq["r11"] = 1, 128, 257
+    ctx = {r: n + int(torch.randint(0, 400, (1,), generator=g)) for r, n in nq.items()}
+    ctx["r5"] = nq["r5"]  # no prefix at all
+    blocks = {r: -(-c // 16) for r, c in ctx.items()}
+    nb = sum(blocks.values()) + 7
+    perm = torch.randperm(nb, generator=g).tolist()
+    tables, at = {}, 0
+    for r, n in blocks.items():
+        tables[r] = perm[at : at + n]
+        at += n
+    k = torch.randn((nb, 16, hkv, d), generator=g).to(torch.bfloat16)
+    v = torch.randn((nb, 16, hkv, d), generator=g).to(torch.bfloat16)
+    q = torch.randn((sum(nq.values()), h, d), generator=g).to(torch.bfloat16)
+    assert 2 * h * n_req > 148  # two query blocks for the longest chunk: more items than a B200 has SMs
+    out = pkg.chunked_prefill(q.to(cuda), k.to(cuda), v.to(cuda), tables, ctx, nq)
+    kf, vf = k.float().numpy(), v.float().numpy()
+    at = 0
+    for r in tables:
+        want = torch.from_numpy(c_oracle.chunk_prefill(q[at : at + nq[r]].float().numpy(), kf, vf, np.array(tables[r], dtype=np.int32), ctx[r],
+                                                       1 / math.sqrt(d)))
+        assert_half_close(out[r].cpu(), want, what=f"ragged batch {r} n_q {nq[r]} ctx {ctx[r]}")
+        at += nq[r]
+
+
 def test_prefill_matches_decode_for_last_token(cuda):
     """The last query row of a chunk is exactly a decode step over the same cache."""
     pw = wl.make_prefill_workload(n_requests=2, prefix_len=128, chunk_len=100, n_heads=8, n_kv_heads=2, head_dim=128)
