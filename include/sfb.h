@@ -233,8 +233,10 @@ SFB_API int sfb_cache_write(const SFBTensor* k_new, const SFBTensor* v_new, cons
  *
  * BF16 / F16 with D = 128 and bs = 16 run on the tcgen05 kernel; every other
  * shape takes the decode kernels with one row per query token.  `workspace`
- * (sfb_prefill_workspace_bytes) holds the status word and, for that second
- * route, 8 bytes per query token.  max_q_tokens >= the longest chunk. */
+ * (sfb_prefill_workspace_bytes) holds the status word, the counter the
+ * tcgen05 kernel's resident thread blocks draw their work items from (one
+ * workspace per call in flight) and, for that second route, 8 bytes per
+ * query token.  max_q_tokens >= the longest chunk. */
 SFB_API int64_t sfb_prefill_workspace_bytes(int64_t total_q_tokens);
 SFB_API int sfb_prefill_paged(const SFBTensor* q, const SFBTensor* k_cache, const SFBTensor* v_cache,
                               const SFBTensor* block_tables, const SFBTensor* cu_q, const SFBTensor* ctx_lens,

@@ -299,7 +299,9 @@ static int prefill_impl(const SFBTensor* q, const SFBTensor* k_cache, const SFBT
     if (T == 0 || R == 0 || max_q_tokens <= 0) return SFB_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (workspace && workspace_bytes < kWorkspaceHeader) workspace = nullptr;
-    if (workspace && clear_status) SFB_CUDA_CHECK(cudaMemsetAsync(workspace, 0, 4, st));
+    // word 0: status bits; word 4: the ticket the tensor-core kernel's thread blocks draw their work items from
+    if (workspace && clear_status) SFB_CUDA_CHECK(cudaMemsetAsync(workspace, 0, 32, st));
+    else if (workspace) SFB_CUDA_CHECK(cudaMemsetAsync(static_cast<char*>(workspace) + 16, 0, 4, st));
     const float sc = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
 
     PrefillLaunch p{};
@@ -315,6 +317,7 @@ static int prefill_impl(const SFBTensor* q, const SFBTensor* k_cache, const SFBT
     p.out_stride[0] = vo.stride[1]; p.out_stride[1] = vo.stride[2];
     for (int i = 0; i < 3; ++i) { p.k_stride[i] = vk.stride[i]; p.v_stride[i] = vv.stride[i]; }
     p.scale = sc; p.dtype = dtype; p.causal = causal != 0; p.status = static_cast<int*>(workspace);
+    p.ticket = workspace ? static_cast<int*>(workspace) + 4 : nullptr;
     const bool q_tma_ok = reinterpret_cast<uintptr_t>(vq.base) % 16 == 0 && (vq.stride[1] * e) % 16 == 0 && (vq.stride[2] * e) % 16 == 0;
     rc = q_tma_ok ? launch_prefill_tcgen05(p, st) : SFB_ERR_UNSUPPORTED;
     if (rc != SFB_ERR_UNSUPPORTED) return rc;

@@ -81,6 +81,7 @@ struct PrefillArgs {
     int q_blocks;             // 256-row query blocks of the longest chunk
     int n_items;              // q_blocks * n_heads * n_requests work items
     int out_vec8;             // output rows allow 32-byte stores
+    int* ticket;              // optional: zeroed counter the thread blocks draw item numbers from
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -258,13 +259,16 @@ struct Item {
     bool valid;
 };
 
-// Items are numbered heaviest first (the last query block of every request, all heads, then the block before ...); a thread
-// block takes items blockIdx.x, blockIdx.x + gridDim.x, ...  `idx` moves to the first item at or after it that has work.
-__device__ __forceinline__ Item find_item(const PrefillArgs& a, int& idx, const int* limit_max, bool report) {
+// Items are numbered heaviest first (the last query block of every request, all heads, then the block before ...).  A thread
+// block takes the next number from a ticket in the workspace (whichever block is free takes the heaviest item left: requests
+// of very different lengths still end together), or - without a workspace - the numbers blockIdx.x, blockIdx.x + gridDim.x, ...
+// `idx` moves on (through `next`) to the first item at or after it that has work.
+template <typename Next>
+__device__ __forceinline__ Item find_item(const PrefillArgs& a, int& idx, const int* limit_max, bool report, Next next) {
     Item it;
     it.valid = false;
     const int per_rank = a.n_heads * a.n_requests;
-    for (; idx < a.n_items; idx += gridDim.x) {
+    for (; idx < a.n_items; idx = next()) {
         const int rank = idx / per_rank, rem = idx - rank * per_rank;
         it.req = rem / a.n_heads;
         it.head = rem - it.req * a.n_heads;
@@ -313,7 +317,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         // whole block to reduce).  One row per thread of the first eight warps; the tiles' maxima go through shared memory.
         int idx = blockIdx.x;
         limit_max[0] = limit_max[1] = 1;
-        const Item it = find_item(a, idx, limit_max, false);
+        const Item it = find_item(a, idx, limit_max, false, [&] { return a.n_items; });
         __syncthreads();
         int my_limit = 0;
         if (threadIdx.x < 2 * kTileQ) {
@@ -511,11 +515,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             }
         } else if (warp == kSchedWarp) {
             // ============================ item scheduler ==========================
-            int idx = blockIdx.x;
+            int strided = blockIdx.x;
+            auto next = [&]() -> int {
+                if (!a.ticket) return strided += gridDim.x;
+                int v = 0;
+                if (lane == 0) v = atomicAdd(a.ticket, 1);
+                return __shfl_sync(0xffffffffu, v, 0);
+            };
+            int idx = a.ticket ? next() : strided;
             for (uint32_t n = 0;; ++n) {
                 const int slot = n & (kItemSlots - 1);
                 if (n >= kItemSlots && !mbar_wait(bar(B_ITEM_EMPTY + slot), (n / kItemSlots - 1) & 1)) { timed_out = true; break; }
-                const Item it = find_item(a, idx, limit_max, lane == 0);
+                const Item it = find_item(a, idx, limit_max, lane == 0, next);
                 if (lane == 0) {
                     int4* r = reinterpret_cast<int4*>(item_ring + slot * 16);
                     r[0] = make_int4(it.req, it.head, it.q_begin, it.q0);
@@ -525,7 +536,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                 }
                 __syncwarp();
                 if (!it.valid) break;  // the end-of-work record
-                idx += gridDim.x;
+                idx = next();
             }
         } else if (warp == kMmaWarp) {
             // ============================ MMA issuer ==============================
@@ -903,6 +914,7 @@ int launch_prefill_tcgen05(const PrefillLaunch& p, cudaStream_t stream) {
     if (n_items > 0x7fffffffLL) return SFB_ERR_UNSUPPORTED;
     a.n_items = (int)n_items;
     a.out_vec8 = !p.part_o && reinterpret_cast<uintptr_t>(p.out) % 32 == 0 && p.out_stride[0] % 16 == 0 && p.out_stride[1] % 16 == 0;
+    a.ticket = p.row_limits ? nullptr : p.ticket;  // with row limits block b runs item b
     const dim3 grid((unsigned)(p.row_limits ? n_items : std::min<int64_t>(n_items, sm_count())));
     if (a.bf16) {
         if (const int rc = allow_shared_memory_once(reinterpret_cast<const void*>(prefill_tcgen05_kernel<true>), kSmemBytes)) return rc;

@@ -279,6 +279,7 @@ struct PrefillLaunch {
     int dtype;
     int causal;
     int* status;
+    int* ticket;  // optional zeroed int: the resident thread blocks draw their work items from it
     // Shared-prefix mode (cu_q == nullptr): one pseudo-request of fixed_nq rows (row i = decode request i) over
     // fixed_ctx cached tokens; results go out as split partials, not as rows of `out`.
     int fixed_nq, fixed_ctx;
