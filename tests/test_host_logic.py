@@ -6,7 +6,7 @@ import torch
 
 from llm_compileforge_b200 import workloads as wl
 from llm_compileforge_b200.hal import B200Backend, OpExecutor
-from llm_compileforge_b200.tables import dense_block_tables, partition_by_request
+from llm_compileforge_b200.tables import dense_block_tables, partition_by_request, pick_chunk_tokens
 
 
 def test_dense_tables_follow_reference_rules():
@@ -27,6 +27,25 @@ def test_partition_is_contiguous_and_balanced():
     assert flat == list(range(512))
     loads = [sum(lengths[i] for i in p) for p in parts]
     assert max(loads) <= 1.15 * (sum(lengths) / 8)
+
+
+def test_split_size_fills_whole_waves():
+    """KV split of the decode kernel: large batches take the largest split that still makes about 1.4 waves of
+    (request, chunk) items on the 2 x 148 SM slots; a small batch the smallest split whose items fit one wave."""
+    slots = 2 * 148
+    items = lambda lens, c: sum(-(-n // c) for n in lens)
+    for shape, want in ((wl.C5, 2048), (wl.C3, 2048), (wl.C2, 640)):
+        lens = wl.config_lengths(shape)
+        c = pick_chunk_tokens(lens)
+        assert c == want and c % 16 == 0
+        assert items(lens, c) * 10 >= 14 * slots or items(lens, c) <= slots
+    assert pick_chunk_tokens([]) == 256 and pick_chunk_tokens([0, 0]) == 256
+    assert pick_chunk_tokens([100, 90, 7]) == 256          # a handful of short requests: one wave at the smallest split
+    assert pick_chunk_tokens([2000] * 200) == 512          # 800 items: 2.7 waves of 512-token items
+    lens = [3000] * 60                                     # under 1.4 waves even at 512: the first split with <= 296 items
+    c = pick_chunk_tokens(lens)
+    assert items(lens, c) <= slots and items(lens, c - 64) > slots
+    assert pick_chunk_tokens([8192] * 128, head_groups=4) == 2048
 
 
 def test_config_generators():
