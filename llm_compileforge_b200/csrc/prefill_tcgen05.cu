@@ -252,11 +252,16 @@ constexpr uint32_t kColO = 128;
 constexpr int kSoftmaxRegs = 104;
 constexpr int kOtherRegs = 64;
 
-// One work item: 256 query rows (two 128-row tiles) of one (request, query head).
+// One work item: 256 query rows (two 128-row tiles) of one (request, query head) - or, where a request's query block has no
+// second tile (a chunk of at most 128 rows, or its ragged end), the same 128 rows of two query heads that share a kv head:
+// both tensor-memory tile slots, softmax warp groups and the ping-pong stay in use, and the K / V stream serves two heads.
 struct Item {
     int req, head, q_begin, q0, n_q, ctx;
     int rows[2], tiles[2], n_tiles;
     bool valid;
+    bool pair;  // the query block has at most 128 rows: tile 1 is the same rows of the NEXT query head (same kv head)
+    __device__ __forceinline__ int row0(int t) const { return q0 + (pair ? 0 : t * kTileQ); }  // first chunk row of tile t
+    __device__ __forceinline__ int head_of(int t) const { return head + (pair ? t : 0); }
 };
 
 // Items are numbered heaviest first (the last query block of every request, all heads, then the block before ...).  A thread
@@ -267,6 +272,7 @@ template <typename Next>
 __device__ __forceinline__ Item find_item(const PrefillArgs& a, int& idx, const int* limit_max, bool report, Next next) {
     Item it;
     it.valid = false;
+    it.pair = false;
     const int per_rank = a.n_heads * a.n_requests;
     for (; idx < a.n_items; idx = next()) {
         const int rank = idx / per_rank, rem = idx - rank * per_rank;
@@ -284,11 +290,13 @@ __device__ __forceinline__ Item find_item(const PrefillArgs& a, int& idx, const 
         }
         it.ctx = ctx;
         it.q0 = qb * 2 * kTileQ;
+        it.pair = it.n_q - it.q0 <= kTileQ && (a.n_heads / a.n_kv_heads) % 2 == 0;
+        if (it.pair && (it.head & 1)) continue;  // the even head before it takes this one along
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
-            it.rows[t] = max(0, min(kTileQ, it.n_q - it.q0 - t * kTileQ));
-            const int last_pos = a.row_limits ? max(limit_max[t], 1) - 1
-                                 : a.causal   ? ctx - it.n_q + it.q0 + t * kTileQ + it.rows[t] - 1
+            it.rows[t] = max(0, min(kTileQ, it.n_q - it.row0(t)));
+            const int last_pos = a.row_limits ? max(limit_max[it.pair ? 0 : t], 1) - 1
+                                 : a.causal   ? ctx - it.n_q + it.row0(t) + it.rows[t] - 1
                                               : ctx - 1;
             it.tiles[t] = it.rows[t] > 0 ? last_pos / kTileKV + 1 : 0;
         }
@@ -372,7 +380,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         const int4 r0 = r[0], r1 = r[1], r2 = r[2];
         it.req = r0.x; it.head = r0.y; it.q_begin = r0.z; it.q0 = r0.w;
         it.n_q = r1.x; it.ctx = r1.y; it.rows[0] = r1.z; it.rows[1] = r1.w;
-        it.tiles[0] = r2.x; it.tiles[1] = r2.y; it.n_tiles = r2.z; it.valid = r2.w != 0;
+        it.tiles[0] = r2.x; it.tiles[1] = r2.y; it.n_tiles = r2.z; it.valid = (r2.w & 1) != 0; it.pair = (r2.w & 2) != 0;
         return true;
     };
     auto release_item = [&](uint32_t n) { mbar_arrive(bar(B_ITEM_EMPTY + (n & (kItemSlots - 1)))); };  // one lane per consumer warp
@@ -404,8 +412,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                 q_loaded |= 1u << t;
                 if (lane == 0) {
                     mbar_expect_tx(bar(B_Q_FULL + t), (with_k0 ? 2 : 1) * kTileBytes);
-                    tma_load_4d(q_s + t * kTileBytes, &qmap, bar(B_Q_FULL + t), it.q_begin + it.q0 + t * kTileQ, 0, it.head);
-                    tma_load_4d(q_s + t * kTileBytes + kSubBytes, &qmap, bar(B_Q_FULL + t), it.q_begin + it.q0 + t * kTileQ, 1, it.head);
+                    tma_load_4d(q_s + t * kTileBytes, &qmap, bar(B_Q_FULL + t), it.q_begin + it.row0(t), 0, it.head_of(t));
+                    tma_load_4d(q_s + t * kTileBytes + kSubBytes, &qmap, bar(B_Q_FULL + t), it.q_begin + it.row0(t), 1, it.head_of(t));
                 }
                 __syncwarp();
                 return true;
@@ -531,7 +539,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     int4* r = reinterpret_cast<int4*>(item_ring + slot * 16);
                     r[0] = make_int4(it.req, it.head, it.q_begin, it.q0);
                     r[1] = make_int4(it.n_q, it.ctx, it.rows[0], it.rows[1]);
-                    r[2] = make_int4(it.tiles[0], it.tiles[1], it.n_tiles, it.valid ? 1 : 0);
+                    r[2] = make_int4(it.tiles[0], it.tiles[1], it.n_tiles, (it.valid ? 1 : 0) | (it.pair ? 2 : 0));
                     mbar_arrive(bar(B_ITEM_FULL + slot));
                 }
                 __syncwarp();
@@ -748,8 +756,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             const int my_rows = my_t ? cur.rows[1] : cur.rows[0], my_tiles = my_t ? cur.tiles[1] : cur.tiles[0];
             if (my_tiles > 0) {
                 // last visible position of this thread's row; padding rows see everything
-                pos = (row < my_rows && a.causal) ? cur.ctx - cur.n_q + cur.q0 + my_t * kTileQ + row : cur.ctx - 1;
-                if (a.row_limits && row < my_rows) pos = min(max(a.row_limits[cur.q_begin + cur.q0 + my_t * kTileQ + row], 0), cur.ctx) - 1;
+                const int my_row = cur.row0(my_t) + row, my_head = cur.head_of(my_t);  // row of the request's chunk, query head
+                pos = (row < my_rows && a.causal) ? cur.ctx - cur.n_q + my_row : cur.ctx - 1;
+                if (a.row_limits && row < my_rows) pos = min(max(a.row_limits[cur.q_begin + my_row], 0), cur.ctx) - 1;
                 m_used = -INFINITY;
                 l = 0.f;
                 for (int j = 0; j < my_tiles && ok; ++j) ok = softmax_tile(j);
@@ -765,13 +774,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     if (a.part_o) {
                         // shared-prefix mode: this row is decode request `qrow`; its partial goes to the chunk slot right after
                         // the request's own chunks, in the decode kernel's format (unnormalised O, max in log2 units, sum)
-                        const int qrow = cur.q0 + my_t * kTileQ + row;
+                        const int qrow = my_row;
                         int64_t pslot = 0;
                         if (row_valid) {
                             int len = a.part_seq_lens[qrow];
                             if (len > a.part_max_tokens) len = a.part_max_tokens;
                             const int chunk = (max(0, len - cur.ctx) + a.part_chunk_tokens - 1) / a.part_chunk_tokens;
-                            pslot = ((int64_t)qrow * a.part_n_chunks + chunk) * a.n_heads + cur.head;
+                            pslot = ((int64_t)qrow * a.part_n_chunks + chunk) * a.n_heads + my_head;
                             if (hf == 0) {
                                 a.part_ml[pslot * 2] = m_used;
                                 a.part_ml[pslot * 2 + 1] = l_row;
@@ -790,8 +799,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                         }
                     } else {
                         const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-                        uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(cur.q_begin + cur.q0 + my_t * kTileQ + row) * a.out_stride[0] +
-                                        (int64_t)cur.head * a.out_stride[1] + hf * 64;
+                        uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(cur.q_begin + my_row) * a.out_stride[0] +
+                                        (int64_t)my_head * a.out_stride[1] + hf * 64;
 #pragma unroll 1
                         for (int ch = 0; ch < 2; ++ch) {
                             float o[32];

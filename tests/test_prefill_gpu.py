@@ -89,6 +89,33 @@ def test_prefill_multi_request_shared_prefix_and_generic_route(cuda):
             at += nq[r]
 
 
+@pytest.mark.parametrize("h,hkv", [(6, 2), (8, 8), (2, 1), (12, 3)])
+def test_tcgen05_prefill_single_tile_chunks_head_groups(cuda, h, hkv):
+    """Chunks of at most 128 rows: with an even number of query heads per kv head two heads share a work item (one per
+    tensor-memory tile slot); with an odd number (3 per kv head, or 1) every head runs alone with the second slot empty."""
+    g = torch.Generator().manual_seed(100 + h)
+    d = 128
+    nq = {"a": 77, "b": 128, "c": 3}
+    ctx = {"a": 500, "b": 128, "c": 1027}
+    blocks = {r: -(-c // 16) for r, c in ctx.items()}
+    nb = sum(blocks.values()) + 3
+    perm = torch.randperm(nb, generator=g).tolist()
+    tables, at = {}, 0
+    for r, n in blocks.items():
+        tables[r] = perm[at : at + n]
+        at += n
+    k = torch.randn((nb, 16, hkv, d), generator=g).to(torch.bfloat16)
+    v = torch.randn((nb, 16, hkv, d), generator=g).to(torch.bfloat16)
+    q = torch.randn((sum(nq.values()), h, d), generator=g).to(torch.bfloat16)
+    out = pkg.chunked_prefill(q.to(cuda), k.to(cuda), v.to(cuda), tables, ctx, nq)
+    at = 0
+    for r in tables:
+        want = torch.from_numpy(c_oracle.chunk_prefill(q[at : at + nq[r]].float().numpy(), k.float().numpy(), v.float().numpy(),
+                                                       np.array(tables[r], dtype=np.int32), ctx[r], 1 / math.sqrt(d)))
+        assert_half_close(out[r].cpu(), want, what=f"H {h}/{hkv} {r}")
+        at += nq[r]
+
+
 def test_prefill_many_ragged_items_per_thread_block(cuda):
     """More work items than SMs, of very different sizes: every resident thread block runs several items back to back (K / V
     stream, Q tiles and first score tile of the next item issued during the current one's last step), including requests whose
