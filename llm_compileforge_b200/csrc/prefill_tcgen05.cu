@@ -267,9 +267,10 @@ struct Item {
 // Items are numbered heaviest first (the last query block of every request, all heads, then the block before ...).  A thread
 // block takes the next number from a ticket in the workspace (whichever block is free takes the heaviest item left: requests
 // of very different lengths still end together), or - without a workspace - the numbers blockIdx.x, blockIdx.x + gridDim.x, ...
-// `idx` moves on (through `next`) to the first item at or after it that has work.
+// `idx` moves on (through `next`) to the first item at or after it that has work.  Called by a whole warp: with per-row limits
+// the tiles' lengths come from the largest limit of each tile's rows, a reduction over the warp.
 template <typename Next>
-__device__ __forceinline__ Item find_item(const PrefillArgs& a, int& idx, const int* limit_max, bool report, Next next) {
+__device__ __forceinline__ Item find_item(const PrefillArgs& a, int& idx, bool report, Next next) {
     Item it;
     it.valid = false;
     it.pair = false;
@@ -295,9 +296,12 @@ __device__ __forceinline__ Item find_item(const PrefillArgs& a, int& idx, const 
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
             it.rows[t] = max(0, min(kTileQ, it.n_q - it.row0(t)));
-            const int last_pos = a.row_limits ? max(limit_max[it.pair ? 0 : t], 1) - 1
-                                 : a.causal   ? ctx - it.n_q + it.row0(t) + it.rows[t] - 1
-                                              : ctx - 1;
+            int last_pos = a.causal ? ctx - it.n_q + it.row0(t) + it.rows[t] - 1 : ctx - 1;
+            if (a.row_limits) {
+                int longest = 0;
+                for (int r = threadIdx.x & 31; r < it.rows[t]; r += 32) longest = max(longest, min(max(a.row_limits[it.q_begin + it.row0(t) + r], 0), ctx));
+                last_pos = max(__reduce_max_sync(0xffffffffu, longest), 1) - 1;
+            }
             it.tiles[t] = it.rows[t] > 0 ? last_pos / kTileKV + 1 : 0;
         }
         it.n_tiles = max(it.tiles[0], it.tiles[1]);
@@ -317,29 +321,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
     uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + 6 * kTileBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
-    int* limit_max = reinterpret_cast<int*>(tmem_slot + 1);  // [2]: with row limits, the largest limit of each query tile
     float* xch = reinterpret_cast<float*>(tmem_slot + 4);
     int* item_ring = reinterpret_cast<int*>(xch + kXchFloats);  // [kItemSlots][16]
-    if (a.row_limits) {
-        // Row limits: the grid has one thread block per item (the tile counts depend on the rows' limits, which takes the
-        // whole block to reduce).  One row per thread of the first eight warps; the tiles' maxima go through shared memory.
-        int idx = blockIdx.x;
-        limit_max[0] = limit_max[1] = 1;
-        const Item it = find_item(a, idx, limit_max, false, [&] { return a.n_items; });
-        __syncthreads();
-        int my_limit = 0;
-        if (threadIdx.x < 2 * kTileQ) {
-            if (it.valid && idx == (int)blockIdx.x && it.q0 + (int)threadIdx.x < it.n_q)
-                my_limit = min(max(a.row_limits[it.q_begin + it.q0 + threadIdx.x], 0), it.ctx);
-            const int wmax = __reduce_max_sync(0xffffffffu, my_limit);
-            if (lane == 0) reinterpret_cast<int*>(xch)[warp] = wmax;
-        }
-        __syncthreads();
-        if (threadIdx.x < 2) {
-            const int* w = reinterpret_cast<const int*>(xch) + 4 * threadIdx.x;
-            limit_max[threadIdx.x] = max(max(w[0], w[1]), max(w[2], w[3]));
-        }
-    }
     const uint32_t q_s = base, k_s = base + 2 * kTileBytes, v_s = base + 4 * kTileBytes;
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -534,7 +517,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             for (uint32_t n = 0;; ++n) {
                 const int slot = n & (kItemSlots - 1);
                 if (n >= kItemSlots && !mbar_wait(bar(B_ITEM_EMPTY + slot), (n / kItemSlots - 1) & 1)) { timed_out = true; break; }
-                const Item it = find_item(a, idx, limit_max, lane == 0, next);
+                const Item it = find_item(a, idx, lane == 0, next);
                 if (lane == 0) {
                     int4* r = reinterpret_cast<int4*>(item_ring + slot * 16);
                     r[0] = make_int4(it.req, it.head, it.q_begin, it.q0);
@@ -915,16 +898,15 @@ int launch_prefill_tcgen05(const PrefillLaunch& p, cudaStream_t stream) {
     a.fixed_nq = p.fixed_nq; a.fixed_ctx = p.fixed_ctx; a.part_o = p.part_o; a.part_ml = p.part_ml;
     a.part_seq_lens = p.part_seq_lens; a.part_n_chunks = p.part_n_chunks; a.part_chunk_tokens = p.part_chunk_tokens;
     a.part_max_tokens = p.part_max_tokens;
-    // Work items (256 query rows of one head of one request) are spread over one resident thread block per SM; with per-row
-    // limits every item gets its own thread block (the tile counts then take a block-wide reduction at the start).
+    // Work items (256 query rows of one head of one request) are spread over one resident thread block per SM.
     a.q_blocks = (int)ceil_div(p.max_q_tokens, 2 * kTileQ);
     const int64_t n_items = (int64_t)a.q_blocks * p.n_heads * p.n_requests;
     if (n_items <= 0) return SFB_OK;
     if (n_items > 0x7fffffffLL) return SFB_ERR_UNSUPPORTED;
     a.n_items = (int)n_items;
     a.out_vec8 = !p.part_o && reinterpret_cast<uintptr_t>(p.out) % 32 == 0 && p.out_stride[0] % 16 == 0 && p.out_stride[1] % 16 == 0;
-    a.ticket = p.row_limits ? nullptr : p.ticket;  // with row limits block b runs item b
-    const dim3 grid((unsigned)(p.row_limits ? n_items : std::min<int64_t>(n_items, sm_count())));
+    a.ticket = p.ticket;
+    const dim3 grid((unsigned)std::min<int64_t>(n_items, sm_count()));
     if (a.bf16) {
         if (const int rc = allow_shared_memory_once(reinterpret_cast<const void*>(prefill_tcgen05_kernel<true>), kSmemBytes)) return rc;
         prefill_tcgen05_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(qmap, kmap, vmap, a);
