@@ -14,7 +14,7 @@
 // pipeline: the K / V tiles of consecutive items form a single stream through the two-slot rings, the next item's Q tiles
 // land as soon as the current item's last Q.K^T has read the old ones, and the next item's first Q.K^T is issued in the place
 // of the step's usual next score tile - the tensor pipe keeps running while the softmax warps write an item's rows out.
-// Twenty warps (five warpgroups):
+// Twelve warps (three warpgroups):
 //   warp 0    issues tcgen05.mma (one thread): S_t = Q_t K^T (128x128x128, both operands K-major in 128B-swizzled shared
 //             memory) and O_t += P_t V with P_t read from tensor memory and V as an MN-major shared-memory operand,
 //             alternating between the two query tiles so that one tile's MMAs run while the other's rows are in the softmax warps
@@ -23,15 +23,13 @@
 //   warp 2    TMA producer for V: eight [2 halves x 16 tokens x 128 B] boxes per tile; it also clears the V rows past the
 //             context in the last KV tile (a pool that was never zero-filled may hold NaN there, and 0 * NaN would reach O)
 //   warp 3    scheduler: works out each item's geometry (request offsets and lengths from global memory) ahead of time and
-//             hands it to the other nineteen warps through a four-slot ring in shared memory
-//   warps 4-19 softmax, eight warps per query tile, two threads per query row (64 key columns each; a warp can only reach its
-//             own 32 tensor-memory lanes, so warps w and w+4 share lanes and split the columns).  A thread reads its 64
-//             scores ONCE (tcgen05.ld into registers; the softmax warpgroups raise their register allowance with setmaxnreg,
-//             the first warpgroup lowers its own), swaps half-row maxima with its partner through shared memory under a
-//             64-thread named barrier (only when a barrier-wide OR says a row outgrew the rescale threshold), keeps running
-//             max / sum in log2 units, writes P as bf16/fp16 over its own S columns,
-//             rescales O in tensor memory only when the max grew by more than 2^8 (the stale max stays exact in fp32), adds
-//             the partial sums in the epilogue and writes O / l.
+//             hands it to the other warps through a four-slot ring in shared memory
+//   warps 4-11 softmax, one warpgroup per query tile, one thread per query row (warp w owns tensor-memory lanes 32*(w&3)..,
+//             its hardware window).  A thread reads its row's 128 scores ONCE (tcgen05.ld into registers; the softmax
+//             warpgroups raise their register allowance to 208 with setmaxnreg, the first warpgroup lowers its own), keeps
+//             running max / sum in log2 units - no exchange with other threads -, writes P as bf16/fp16 over the first half
+//             of its own S columns, rescales O in tensor memory only when the max grew by more than 2^8 (the stale max
+//             stays exact in fp32) and writes O / l at the end of the item.
 // Tensor memory: per query tile S|P (128 columns) and O (128) = 512 columns in all.
 // Bound: tensor pipe (4*D*Sq*Skv flops per head); every wait is bounded and reports SFB_STATUS_WAIT_TIMEOUT.
 
@@ -51,7 +49,7 @@ constexpr int kTileKV = 128;
 constexpr int kHeadDim = 128;
 constexpr int kSubBytes = kTileKV * 128;     // one [128 rows][128 B] swizzled sub-tile
 constexpr int kTileBytes = 2 * kSubBytes;    // D = 128 16-bit values = two sub-tiles
-constexpr int kThreads = 640;  // 2 x 8 softmax warps (one group per query tile) + a warpgroup with the TMA, MMA and fix-up warps
+constexpr int kThreads = 384;  // a warpgroup with the MMA, TMA and scheduler warps + one softmax warpgroup per query tile
 constexpr int kMmaWarp = 0, kTmaWarp = 1, kTmaWarpV = 2, kSchedWarp = 3, kFirstSoftmaxWarp = 4;
 constexpr uint32_t kSpin = 1u << 21;  // bounded waits: a stuck pipeline gives up (status bit) within about a second
 constexpr float kLog2e = 1.4426950408889634f;
@@ -228,7 +226,7 @@ enum {
     B_KV_FULL = 4,   // +step parity: V(g) and K(g+1) have landed (one arrival per producer warp)
     B_KV_EMPTY = 6,  // +step parity: every MMA that read them is complete
     B_S_FULL = 8,    // +query tile
-    B_P_FULL = 10,   // +query tile: P is in tensor memory (eight warps arrive)
+    B_P_FULL = 10,   // +query tile: P is in tensor memory (four warps arrive)
     B_PV_DONE = 12,  // +query tile: the item's last P.V product of the tile is complete
     B_V_FIXED = 14,  // the last KV tile's V rows past the context are cleared
     B_FINAL = 15,    // every MMA and every commit of this thread block is complete
@@ -236,20 +234,20 @@ enum {
     B_ITEM_EMPTY = 20,  // +ring slot: all nineteen consumer warps have read it
     B_COUNT = 24
 };
-constexpr int kItemSlots = 4, kItemConsumers = 19;  // K, V, MMA and sixteen softmax warps
-constexpr int kXchFloats = 2 * 2 * 2 * kTileQ;  // [exchange parity][query tile][column half][row]
-constexpr int kSmemBytes = 6 * kTileBytes + B_COUNT * 8 + 16 + kXchFloats * 4 + kItemSlots * 64 + 1024;  // 2 Q tiles, 2 K stages, 2 V stages
+constexpr int kItemSlots = 4, kItemConsumers = 10;  // the K producer, the MMA issuer and eight softmax warps
+constexpr int kSmemBytes = 6 * kTileBytes + B_COUNT * 8 + 16 + kItemSlots * 64 + 1024;  // 2 Q tiles, 2 K stages, 2 V stages
 
 // Tensor-memory columns of query tile t: S (fp32, 128 columns) at t*256, with P (16-bit pairs,
 // 64 columns) written over its first half once the row has been read; O (fp32) at t*256 + 128.
 constexpr uint32_t kColTile = 256;
 constexpr uint32_t kColO = 128;
 
-// Register allowances after the role split (five warpgroups of 128 threads; the kernel is compiled for
-// 65536 / 640 -> 96 registers per thread, and shared memory admits one thread block per SM, so the block may
-// grow into the rest of the register file): 4 * 128 * kSoftmaxRegs + 128 * kOtherRegs <= 640 * 96 - a split that
-// asks for more than the block owned at launch never returns from setmaxnreg.inc.
-constexpr int kSoftmaxRegs = 104;
+// Register allowances after the role split (three warpgroups of 128 threads; the kernel is compiled for
+// 65536 / 384 -> 168 registers per thread, and shared memory admits one thread block per SM):
+// 2 * 128 * kSoftmaxRegs + 128 * kOtherRegs <= 384 * 168 - a split that asks for more than the block owned at
+// launch never returns from setmaxnreg.inc.
+static_assert(2 * 128 * 208 + 128 * 64 <= 384 * 168, "register split exceeds the launch allocation");
+constexpr int kSoftmaxRegs = 208;
 constexpr int kOtherRegs = 64;
 
 // One work item: 256 query rows (two 128-row tiles) of one (request, query head) - or, where a request's query block has no
@@ -321,8 +319,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
     uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + 6 * kTileBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
-    float* xch = reinterpret_cast<float*>(tmem_slot + 4);
-    int* item_ring = reinterpret_cast<int*>(xch + kXchFloats);  // [kItemSlots][16]
+    int* item_ring = reinterpret_cast<int*>(tmem_slot + 4);  // [kItemSlots][16]
     const uint32_t q_s = base, k_s = base + 2 * kTileBytes, v_s = base + 4 * kTileBytes;
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -334,7 +331,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             mbar_init(bar(B_KV_FULL + s), 2);
             mbar_init(bar(B_KV_EMPTY + s), 1);
             mbar_init(bar(B_S_FULL + s), 1);
-            mbar_init(bar(B_P_FULL + s), 8);
+            mbar_init(bar(B_P_FULL + s), 4);
             mbar_init(bar(B_PV_DONE + s), 1);
         }
         mbar_init(bar(B_V_FIXED), 1);
@@ -570,7 +567,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     const uint32_t vb = v_lo + slot * (kTileBytes >> 4), s_tm = tmem + t * kColTile;
 #pragma unroll
                     for (int ks = 0; ks < 8; ++ks)
-                        mma_ts(s_tm + kColO, s_tm + (ks >> 2) * 64 + (ks & 3) * 8, vb + ks * (4096 >> 4), hi, idesc_pv, !first || ks > 0);
+                        mma_ts(s_tm + kColO, s_tm + ks * 8, vb + ks * (4096 >> 4), hi, idesc_pv, !first || ks > 0);
                     if (last) tc_commit(bar(B_PV_DONE + t));  // the epilogue waits for it
                 };
                 int g = 0;
@@ -616,85 +613,60 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         }
     } else {
         // ======================= softmax / correction / epilogue ==============
-        // Eight warps per query tile.  Warp w owns tensor-memory lanes 32*(w&3).. (its hardware window) and key
-        // columns 64*((w>>2)&1).. of its tile: two threads share a query row, swap their half-row maxima through
-        // shared memory (64-thread named barrier, slots alternate) in the steps where the barrier's OR says some row of the pair
-        // outgrew the rescale threshold, and keep partial sums that are only added up in the epilogue.
+        // Four warps per query tile, one thread per query row.  Warp w owns tensor-memory lanes 32*(w&3).. (its hardware
+        // window) and all 128 key columns of its rows.
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
-        const int my_t = (warp - kFirstSoftmaxWarp) >> 3;  // query tile of this 8-warp group
-        const int hf = ((warp - kFirstSoftmaxWarp) >> 2) & 1;
+        const int my_t = (warp - kFirstSoftmaxWarp) >> 2;  // query tile of this 4-warp group
         const int row = threadIdx.x & 127;
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        const uint32_t pair_bar = 1 + my_t * 4 + (warp & 3);  // named barrier of the two warps that share a lane window
         const float sl2 = a.scale * kLog2e;
-        const uint32_t s_addr = lane_addr + my_t * kColTile + hf * 64;  // this thread's 64 score columns
-        const uint32_t o_addr = lane_addr + my_t * kColTile + kColO + hf * 64;
-        uint32_t s_waits = 0, e_waits = 0, x_count = 0;
+        const uint32_t s_addr = lane_addr + my_t * kColTile;  // this thread's row: 128 score columns
+        const uint32_t o_addr = lane_addr + my_t * kColTile + kColO;
+        uint32_t s_waits = 0, e_waits = 0;
         float m_used = -INFINITY, l = 0.f;
         int pos = 0;
-
-        // both warps of a pair run the same waits in the same order, so they reach this barrier together or not at all
-        auto exchange = [&](float mine) -> float {
-            float* slot = xch + ((x_count & 1) * 2 + my_t) * 2 * kTileQ;
-            ++x_count;
-            slot[hf * kTileQ + row] = mine;
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-            return slot[(hf ^ 1) * kTileQ + row];
-        };
 
         auto softmax_tile = [&](int j) -> bool {
             if (!mbar_wait(bar(B_S_FULL + my_t), s_waits & 1)) return false;
             ++s_waits;
             tc_fence_after();
-            const int kv0 = j * kTileKV + hf * 64;
+            const int kv0 = j * kTileKV;
             // tcgen05.ld / st are warp-collective: the masked / unmasked choice must be uniform across the warp
-            const bool full = __all_sync(0xffffffffu, kv0 + 63 <= pos);
-            float s[64];
-            tmem_ld32_issue(s_addr, *reinterpret_cast<float(*)[32]>(s));
-            tmem_ld32_issue(s_addr + 32, *reinterpret_cast<float(*)[32]>(s + 32));
+            const bool full = __all_sync(0xffffffffu, kv0 + 127 <= pos);
+            float s[128];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32_issue(s_addr + 32 * c, *reinterpret_cast<float(*)[32]>(s + 32 * c));
             tmem_wait_ld();
-            float mx0 = -INFINITY, mx1 = -INFINITY;
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
             if (full) {
 #pragma unroll
-                for (int i = 0; i < 64; i += 4) {
+                for (int i = 0; i < 128; i += 8) {
                     mx0 = max3(mx0, s[i], s[i + 1]);
                     mx1 = max3(mx1, s[i + 2], s[i + 3]);
+                    mx2 = max3(mx2, s[i + 4], s[i + 5]);
+                    mx3 = max3(mx3, s[i + 6], s[i + 7]);
                 }
             } else {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
+                for (int i = 0; i < 128; ++i) {
                     if (kv0 + i > pos) s[i] = -INFINITY;  // exp2(-inf) = 0 below
                     mx0 = fmaxf(mx0, s[i]);
                 }
             }
-            // The row maximum is only needed when it moves the running maximum by more than the rescale threshold.  Whether
-            // any row of this warp pair needs that is an OR over the pair's 64 threads, taken in the named barrier itself
-            // (no shared memory); only then do the partners swap their half-row maxima.
-            const float mx_half = fmaxf(mx0, mx1);
-            bool grow = j == 0;
-            if (j > 0) {
-                uint32_t any;
-                asm volatile(
-                    "{\n .reg .pred p, q;\n setp.ne.u32 q, %2, 0;\n barrier.cta.red.or.pred p, %1, 64, q;\n selp.u32 %0, 1, 0, p;\n}\n"
-                    : "=r"(any)
-                    : "r"(pair_bar), "r"((uint32_t)(mx_half * sl2 > m_used + kRescaleThreshold))
-                    : "memory");
-                grow = any != 0;
-            }
-            if (grow) {
-                const float mx = fmaxf(mx_half, exchange(mx_half));
-                const float m_new = fmaxf(m_used, mx * sl2);
-                if (j == 0) {
-                    m_used = m_new;
-                } else {
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            const float m_new = fmaxf(m_used, mx * sl2);
+            if (j == 0) {
+                m_used = m_new;
+            } else {
+                const bool need = m_new > m_used + kRescaleThreshold;
+                if (__any_sync(0xffffffffu, need)) {
                     // O is only touched between P.V products.  The previous one is complete: this tile's S was committed by
                     // the same thread after it, and a commit covers everything that thread issued before.
-                    const bool need = m_new > m_used + kRescaleThreshold;  // the same for both threads of a row
                     const float f = need ? fast_exp2(m_used - m_new) : 1.f;
                     l *= f;
                     if (need) m_used = m_new;
 #pragma unroll 1
-                    for (int ch = 0; ch < 4; ++ch) {
+                    for (int ch = 0; ch < 8; ++ch) {
                         float o[16];
                         tmem_ld16(o_addr + ch * 16, o);
 #pragma unroll
@@ -704,13 +676,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     tmem_wait_st();
                 }
             }
-            // P (16-bit pairs, 32 columns) goes over the first half of this thread's own score columns;
-            // packed fp32 pairs: one FFMA2 scales and shifts two scores, one FADD2 adds two probabilities
+            // P (16-bit pairs, 64 columns) goes over the first half of this thread's own score columns
             const float neg_m = m_used == -INFINITY ? 0.f : -m_used;  // a row that sees nothing yet: every score is -inf, P = 0
             const float2 sl2v = make_float2(sl2, sl2), nmv = make_float2(neg_m, neg_m);
             float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
+            for (int ch = 0; ch < 4; ++ch) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -752,7 +723,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                 }
                 if (ok) {
                     tc_fence_after();
-                    const float l_row = l + exchange(l);
+                    const float l_row = l;
                     const bool row_valid = row < my_rows;
                     if (a.part_o) {
                         // shared-prefix mode: this row is decode request `qrow`; its partial goes to the chunk slot right after
@@ -764,17 +735,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                             if (len > a.part_max_tokens) len = a.part_max_tokens;
                             const int chunk = (max(0, len - cur.ctx) + a.part_chunk_tokens - 1) / a.part_chunk_tokens;
                             pslot = ((int64_t)qrow * a.part_n_chunks + chunk) * a.n_heads + my_head;
-                            if (hf == 0) {
-                                a.part_ml[pslot * 2] = m_used;
-                                a.part_ml[pslot * 2 + 1] = l_row;
-                            }
+                            a.part_ml[pslot * 2] = m_used;
+                            a.part_ml[pslot * 2 + 1] = l_row;
                         }
 #pragma unroll 1
-                        for (int ch = 0; ch < 2; ++ch) {
+                        for (int ch = 0; ch < 4; ++ch) {
                             float o[32];
                             tmem_ld32(o_addr + ch * 32, o);
                             if (row_valid) {
-                                float* dst = a.part_o + pslot * kHeadDim + hf * 64 + ch * 32;
+                                float* dst = a.part_o + pslot * kHeadDim + ch * 32;
 #pragma unroll
                                 for (int i = 0; i < 8; ++i)
                                     *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
@@ -783,9 +752,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     } else {
                         const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
                         uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + (int64_t)(cur.q_begin + my_row) * a.out_stride[0] +
-                                        (int64_t)my_head * a.out_stride[1] + hf * 64;
+                                        (int64_t)my_head * a.out_stride[1];
 #pragma unroll 1
-                        for (int ch = 0; ch < 2; ++ch) {
+                        for (int ch = 0; ch < 4; ++ch) {
                             float o[32];
                             tmem_ld32(o_addr + ch * 32, o);
                             if (row_valid) {
