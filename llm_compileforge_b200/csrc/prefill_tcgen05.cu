@@ -246,9 +246,9 @@ constexpr uint32_t kColO = 128;
 // 65536 / 384 -> 168 registers per thread, and shared memory admits one thread block per SM):
 // 2 * 128 * kSoftmaxRegs + 128 * kOtherRegs <= 384 * 168 - a split that asks for more than the block owned at
 // launch never returns from setmaxnreg.inc.
-static_assert(2 * 128 * 208 + 128 * 64 <= 384 * 168, "register split exceeds the launch allocation");
+static_assert(2 * 128 * 208 + 128 * 88 <= 384 * 168, "register split exceeds the launch allocation");
 constexpr int kSoftmaxRegs = 208;
-constexpr int kOtherRegs = 64;
+constexpr int kOtherRegs = 88;
 
 // One work item: 256 query rows (two 128-row tiles) of one (request, query head) - or, where a request's query block has no
 // second tile (a chunk of at most 128 rows, or its ragged end), the same 128 rows of two query heads that share a kv head:
